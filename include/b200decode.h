@@ -1,0 +1,107 @@
+/* C ABI of libb200decode.so: hand-written sm_100a kernels for the batch-1 W4A16 LLM decode step.
+ *
+ * Every entry point takes raw device pointers, plain ints and a CUDA stream (passed as void*; it is a
+ * cudaStream_t), launches on that stream without synchronising, allocates nothing and keeps no state, so the
+ * whole decode step can be captured into one CUDA graph. The return value is 0 on success or one of the
+ * negative B200_ERR_* codes; on an error nothing has been launched. Device pointers marked "16B" must be
+ * 16-byte aligned. All activations, weights scales and caches are fp16 unless stated.
+ *
+ * The first six functions replace, one for one, the raw-pointer launchers that the reference project
+ * declares in kernels/bindings.cpp:7-16 and wraps for Python in kernels/bindings.cpp:27-88. The remaining
+ * ones are additions (batching, head_dim 128, the bit-exactness probe, step glue).
+ */
+#ifndef B200DECODE_H_
+#define B200DECODE_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_ERR_ARG (-1)    /* null pointer, non-positive size, value out of range */
+#define B200_ERR_ALIGN (-2)  /* a pointer that must be 16-byte aligned is not */
+#define B200_ERR_SHAPE (-3)  /* a shape this library has no kernel for */
+#define B200_ERR_LAUNCH (-4) /* the CUDA runtime refused the launch (see b200_last_cuda_error) */
+#define B200_ERR_LIMIT (-5)  /* a size beyond a fixed capacity of the entry point */
+
+/* Library version (major * 100 + minor). */
+int b200_version(void);
+/* Static text for a B200_ERR_* code. */
+const char* b200_strerror(int code);
+/* Text of the CUDA error behind the last B200_ERR_LAUNCH on this host thread. */
+const char* b200_last_cuda_error(void);
+
+/* y[N] = dequant(W)[N,K] . x[K], fp32 accumulate.
+ * Replaces gemv_w4a16_launch (reference kernels/bindings.cpp:7-8, kernels/gemv_w4a16.cu:111-130).
+ * Wp: packed int32 [N, K/8] (16B), SZ: half2 (scale, zero) [N, K >> log2G], x: [K] (16B), y: [N].
+ * K % 32 == 0, group = 2^log2G >= 32 and divides K.
+ * stage 0 = plain one-thread-per-weight kernel. stage >= 1 with R in {1,2,4,8} and warps in 1..8 runs
+ * that rows-per-warp / warps-per-block configuration; any other R (use 0) lets the library choose by shape.
+ * pf is accepted for signature compatibility and ignored. */
+int b200_gemv_w4a16(int stage, int R, int warps, int pf, const void* Wp, const void* SZ, const void* x, void* y,
+                    int N, int K, int log2G, void* stream);
+
+/* XOR-reduce `bytes` of device memory with streaming 128-bit loads; the achieved GB/s is the library's own
+ * achievable-read-bandwidth figure. sink: 4 writable bytes. unroll: 1, 4 or 8.
+ * Replaces bw_read_launch (reference kernels/bindings.cpp:9, kernels/gemv_w4a16.cu:149-153). */
+int b200_bw_read(const void* p, size_t bytes, void* sink, int blocks, int threads, int unroll, void* stream);
+
+/* Paged split-K decode attention for one sequence, head_dim 64, followed by the combine step.
+ * Replaces paged_attention_launch (reference kernels/bindings.cpp:10-12, kernels/paged_attention.cu:429-461).
+ * q [n_q, 64]; kc, vc [pages, n_kv, 2^log2P, 64] (16B); bt int32 [pages]; pos int32 [1] on the device, context
+ * = pos + 1; PS = tokens per split; scratch o_part fp32 [n_q, max_splits, 64], m_part, l_part fp32
+ * [n_q, max_splits]; out [n_q, 64]. n_q / n_kv in {1,2,4,8}. Tokens beyond max_splits * PS are ignored.
+ * `version` (1..3 in the reference) is accepted and ignored: there is one implementation. */
+int b200_paged_attention(int version, const void* q, const void* kc, const void* vc, const int* bt, const int* pos,
+                         int n_q, int n_kv, int log2P, int PS, int max_splits, float* o_part, float* m_part,
+                         float* l_part, void* out, void* stream);
+
+/* x <- x + delta (fp16 add; delta may be NULL), out <- w * half(float(x) * rsqrt(mean(x^2) + eps)).
+ * Replaces add_rmsnorm_launch (reference kernels/bindings.cpp:13, kernels/fused_norm.cu:56-58).
+ * x, delta, w, out [H] (16B); H % 8 == 0, H <= 32768. */
+int b200_add_rmsnorm(void* x, const void* delta, const void* w, void* out, int H, float eps, void* stream);
+
+/* out[i] = half(silu(gu[i])) * gu[I + i].  gu [2I] (16B), out [I] (16B), I % 8 == 0.
+ * Replaces swiglu_launch (reference kernels/bindings.cpp:14, kernels/fused_swiglu.cu:23-26). */
+int b200_swiglu(const void* gu, void* out, int I, void* stream);
+
+/* Rotate-half RoPE on q (in place) and k of qkv [(n_q + 2 n_kv) * 64] at position *pos, then store k and v
+ * into page bt[pos >> log2P], slot pos & (P - 1) of the caches. cos_t, sin_t fp32 [max_pos, 32].
+ * Replaces rope_append_launch (reference kernels/bindings.cpp:15-16, kernels/rope_kv.cu:34-38). */
+int b200_rope_append(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt, void* kc,
+                     void* vc, int n_q, int n_kv, int log2P, void* stream);
+
+/* ---- additions: no counterpart among the reference's launchers ---- */
+
+/* Batched, head_dim-generic form of b200_paged_attention. q [B, n_q, D]; bt int32 [B, bt_stride]; pos int32 [B];
+ * o_part [B, n_q, max_splits, D]; m_part, l_part [B, n_q, max_splits]; out [B, n_q, D]. D in {64, 128}.
+ * The reference's Python binding hard-wires B = 1 and D = 64 (kernels/bindings.cpp:49-52). */
+int b200_paged_attention_batched(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
+                                 const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
+                                 float* o_part, float* m_part, float* l_part, void* out, void* stream);
+
+/* Batched, head_dim-generic form of b200_rope_append. qkv [B, (n_q + 2 n_kv) D]; bt [B, bt_stride]; pos [B];
+ * cos_t, sin_t fp32 [max_pos, D/2]. D even, D <= 256. */
+int b200_rope_append_batched(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt,
+                             int bt_stride, void* kc, void* vc, int B, int n_q, int n_kv, int D, int log2P,
+                             void* stream);
+
+/* out fp16 [N, K] (16B) = per-element dequantized weight, bit-identical to the quantizer's dequantize
+ * (reference runtime/quant.py:93-97). Used to prove the kernels read the packed format correctly. */
+int b200_dequant_w4a16(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, void* stream);
+
+/* x[H] = emb[tok[0], :]; tok is int64 [1] on the device (the reference's step does this with
+ * torch.index_select, runtime/model.py:218). emb, x 16B; H % 8 == 0. */
+int b200_embed_row(const void* emb, const long long* tok, void* x, int H, void* stream);
+
+/* tok[0] = index of the largest fp16 logit (lowest index on ties, NaNs skipped). If pos != NULL: when history
+ * != NULL, history[pos[0]] = tok[0] (int64 array long enough for every position); then pos[0] += 1.
+ * (torch.argmax and `pos += 1` in the reference's step, runtime/model.py:232-233.) */
+int b200_argmax(const void* logits, int V, long long* tok, int* pos, long long* history, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200DECODE_H_ */

@@ -1,0 +1,237 @@
+// The small operators of the decode step: residual add + RMSNorm, SwiGLU, RoPE + paged KV append, embedding
+// row fetch, greedy argmax, and the read-bandwidth probe. Each is a vector of a few KB, so launch latency
+// and the number of dependent memory round trips matter, not bandwidth: every kernel makes one pass with the
+// data held in registers between its phases.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace b200 {
+
+// ---- residual add + RMSNorm -----------------------------------------------------------------------------
+// Replaces add_rmsnorm_launch (reference kernels/fused_norm.cu:56-58). Rounding as in HF LlamaRMSNorm
+// (reference reference/ref_ops.py:15-20): x <- x +_fp16 delta (written back); h = half(float(x) * rsqrt(
+// mean(float(x)^2) + eps)); out = w *_fp16 h. One block; each thread keeps its 8-element chunks in
+// registers across the reduction, so x is read once.
+constexpr int kNormThreads = 512;
+constexpr int kNormMaxChunks = 8;  // H <= 512 * 8 * 8 = 32768
+
+__global__ void __launch_bounds__(kNormThreads)
+add_rmsnorm_kernel(half* __restrict__ x, const half* __restrict__ delta, const half* __restrict__ w,
+                   half* __restrict__ out, int H, float eps) {
+  __shared__ float part[kNormThreads / 32];
+  const int tid = threadIdx.x, nchunk = H >> 3;
+  uint4 xv[kNormMaxChunks];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kNormMaxChunks; ++c) {
+    const int i = tid + c * kNormThreads;
+    if (i < nchunk) {
+      uint4 v = reinterpret_cast<const uint4*>(x)[i];
+      if (delta) {
+        const uint4 d = reinterpret_cast<const uint4*>(delta)[i];
+        v.x = as_u32(__hadd2(as_h2(v.x), as_h2(d.x)));
+        v.y = as_u32(__hadd2(as_h2(v.y), as_h2(d.y)));
+        v.z = as_u32(__hadd2(as_h2(v.z), as_h2(d.z)));
+        v.w = as_u32(__hadd2(as_h2(v.w), as_h2(d.w)));
+        reinterpret_cast<uint4*>(x)[i] = v;
+      }
+      float f[8];
+      unpack8(v, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss = fmaf(f[k], f[k], ss);
+      xv[c] = v;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) part[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < kNormThreads / 32; ++k) tot += part[k];
+  const float r = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+  for (int c = 0; c < kNormMaxChunks; ++c) {
+    const int i = tid + c * kNormThreads;
+    if (i < nchunk) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + i);
+      const uint32_t xu[4] = {xv[c].x, xv[c].y, xv[c].z, xv[c].w}, wu[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __half22float2(as_h2(xu[k]));
+        o[k] = as_u32(__hmul2(as_h2(wu[k]), __floats2half2_rn(f.x * r, f.y * r)));
+      }
+      reinterpret_cast<uint4*>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int H, float eps,
+                                 cudaStream_t st) {
+  add_rmsnorm_kernel<<<1, kNormThreads, 0, st>>>((half*)x, (const half*)delta, (const half*)w, (half*)out, H, eps);
+  return cudaPeekAtLastError();
+}
+
+// ---- SwiGLU ---------------------------------------------------------------------------------------------
+// Replaces swiglu_launch (reference kernels/fused_swiglu.cu:23-26). gu = gate followed by up, [2I];
+// out[i] = half(silu_fp32(gate_i)) *_fp16 up_i (reference reference/ref_ops.py:23-27).
+__global__ void swiglu_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out,
+                              int nchunk) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nchunk) return;
+  const uint4 gv = gate[i], uv = up[i];
+  const uint32_t g[4] = {gv.x, gv.y, gv.z, gv.w}, u[4] = {uv.x, uv.y, uv.z, uv.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __half22float2(as_h2(g[k]));
+    const half2 s = __floats2half2_rn(f.x / (1.f + expf(-f.x)), f.y / (1.f + expf(-f.y)));
+    o[k] = as_u32(__hmul2(s, as_h2(u[k])));
+  }
+  out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+cudaError_t swiglu_dispatch(const void* gu, void* out, int I, cudaStream_t st) {
+  const int nchunk = I >> 3, threads = 128;
+  swiglu_kernel<<<(nchunk + threads - 1) / threads, threads, 0, st>>>(
+      (const uint4*)gu, (const uint4*)((const half*)gu + I), (uint4*)out, nchunk);
+  return cudaPeekAtLastError();
+}
+
+// ---- RoPE + paged KV append -----------------------------------------------------------------------------
+// Replaces rope_append_launch (reference kernels/rope_kv.cu:34-38), generalised from head_dim 64 to any even D
+// and to a batch of sequences. qkv [B, (n_q + 2 n_kv) D]; q is rotated in place, rotated k and untouched v
+// go to page bt[b, pos_b / P], slot pos_b % P of caches laid out [pages, n_kv, P, D]. cos/sin fp32
+// [max_pos, D/2]; pairs are (i, i + D/2) (reference reference/ref_ops.py:36-53). One block per head,
+// one thread per pair.
+__global__ void rope_append_kernel(half* __restrict__ qkv, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, const int* __restrict__ pos_ptr,
+                                   const int* __restrict__ bt, int bt_stride, half* __restrict__ kc,
+                                   half* __restrict__ vc, int n_q, int n_kv, int D, int log2P) {
+  const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, d2 = D >> 1;
+  const int pos = pos_ptr[b];
+  half* v = qkv + ((size_t)b * (n_q + 2 * n_kv) + head) * D;
+  const int page = bt[(size_t)b * bt_stride + (pos >> log2P)], slot = pos & ((1 << log2P) - 1);
+  if (head < n_q + n_kv) {
+    const float c = cos_t[(size_t)pos * d2 + i], s = sin_t[(size_t)pos * d2 + i];
+    const float a = __half2float(v[i]), bb = __half2float(v[i + d2]);
+    const half ra = __float2half(a * c - bb * s), rb = __float2half(bb * c + a * s);
+    half* dst = head < n_q ? v : kc + ((((size_t)page * n_kv + (head - n_q)) << log2P) + slot) * D;
+    dst[i] = ra;
+    dst[i + d2] = rb;
+  } else {
+    half* dst = vc + ((((size_t)page * n_kv + (head - n_q - n_kv)) << log2P) + slot) * D;
+    dst[i] = v[i];
+    dst[i + d2] = v[i + d2];
+  }
+}
+
+cudaError_t rope_append_dispatch(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt,
+                                 int bt_stride, void* kc, void* vc, int B, int n_q, int n_kv, int D, int log2P,
+                                 cudaStream_t st) {
+  rope_append_kernel<<<dim3(n_q + 2 * n_kv, B), D / 2, 0, st>>>((half*)qkv, cos_t, sin_t, pos, bt, bt_stride,
+                                                                (half*)kc, (half*)vc, n_q, n_kv, D, log2P);
+  return cudaPeekAtLastError();
+}
+
+// ---- embedding row fetch: x[H] = emb[tok[0], :] (tok is int64 on the device) ------------------------------
+// Stands in for the torch.index_select of the reference's step (runtime/model.py:218).
+__global__ void embed_row_kernel(const uint4* __restrict__ emb, const long long* __restrict__ tok,
+                                 uint4* __restrict__ x, int nchunk) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < nchunk) x[i] = emb[(size_t)tok[0] * nchunk + i];
+}
+
+cudaError_t embed_row_dispatch(const void* emb, const long long* tok, void* x, int H, cudaStream_t st) {
+  const int nchunk = H >> 3;
+  embed_row_kernel<<<(nchunk + 255) / 256, 256, 0, st>>>((const uint4*)emb, tok, (uint4*)x, nchunk);
+  return cudaPeekAtLastError();
+}
+
+// ---- greedy argmax over fp16 logits; lowest index wins ties; optionally advances pos -----------------------
+// Stands in for torch.argmax + `pos += 1` at the end of the reference's step (runtime/model.py:232-233).
+// With `history`, the chosen token is also stored at history[pos before the increment], so a run of graph
+// replays leaves its whole token stream on the device and the host need not read a token per step.
+// One block of 1024 threads; the order key packs (value, inverted index) so one max-reduction settles ties.
+DEVI unsigned long long argmax_key(half v, int idx) {
+  uint32_t b = (uint32_t)__half_as_ushort(v);
+  b = (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);  // monotone map of fp16 bits to unsigned order
+  return ((unsigned long long)b << 32) | (uint32_t)(0x7FFFFFFF - idx);
+}
+
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const half* __restrict__ logits, int V, long long* __restrict__ tok, int* __restrict__ pos,
+              long long* __restrict__ history) {
+  __shared__ unsigned long long part[32];
+  unsigned long long best = 0ull;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const half v = logits[i];
+    if (!__hisnan(v)) {
+      const unsigned long long k = argmax_key(v, i);
+      best = k > best ? k : best;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = part[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    if (threadIdx.x == 0) {
+      const long long t = (long long)(0x7FFFFFFF - (int)(best & 0xFFFFFFFFu));
+      tok[0] = t;
+      if (pos) {
+        const int p = pos[0];
+        if (history) history[p] = t;  // the token predicted after consuming position p
+        pos[0] = p + 1;
+      }
+    }
+  }
+}
+
+cudaError_t argmax_dispatch(const void* logits, int V, long long* tok, int* pos, long long* history,
+                            cudaStream_t st) {
+  argmax_kernel<<<1, 1024, 0, st>>>((const half*)logits, V, tok, pos, history);
+  return cudaPeekAtLastError();
+}
+
+// ---- read-bandwidth probe -------------------------------------------------------------------------------
+// Replaces bw_read_launch (reference kernels/gemv_w4a16.cu:149-153): XOR-reduces a buffer with the same
+// streaming loads the GEMV uses; the achieved GB/s is this library's own "achievable HBM read" figure.
+template <int UNROLL>
+__global__ void bw_read_kernel(const uint4* __restrict__ p, size_t n, uint32_t* sink) {
+  uint32_t a = 0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + (UNROLL - 1) * stride < n; i += UNROLL * stride) {
+    uint4 v[UNROLL];
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) v[k] = ld_stream(p + i + k * stride);
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) a ^= v[k].x ^ v[k].y ^ v[k].z ^ v[k].w;
+  }
+  for (; i < n; i += stride) {
+    const uint4 v = ld_stream(p + i);
+    a ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+  if (a == 0x5bd1e995u) *sink = a;  // keeps the loads alive; practically never true
+}
+
+cudaError_t bw_read_dispatch(const void* p, size_t bytes, void* sink, int blocks, int threads, int unroll,
+                             cudaStream_t st) {
+  const size_t n = bytes / 16;
+  if (unroll >= 8) bw_read_kernel<8><<<blocks, threads, 0, st>>>((const uint4*)p, n, (uint32_t*)sink);
+  else if (unroll >= 4) bw_read_kernel<4><<<blocks, threads, 0, st>>>((const uint4*)p, n, (uint32_t*)sink);
+  else bw_read_kernel<1><<<blocks, threads, 0, st>>>((const uint4*)p, n, (uint32_t*)sink);
+  return cudaPeekAtLastError();
+}
+
+}  // namespace b200

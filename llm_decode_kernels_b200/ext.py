@@ -1,0 +1,247 @@
+"""Loader and Python face of libb200decode.so.
+
+`load()` returns an object with the six operators of the reference's extension module `decode_kernels`
+(built by its runtime/ext.py:9-20, defined in kernels/bindings.cpp:90-98) under the same names, argument
+order and keyword names: gemv_w4a16, bw_read, paged_attention, add_rmsnorm, swiglu, rope_append. Each checks its
+tensors the way the reference binding does (contiguous CUDA tensors, dtypes, shapes, 16-byte alignment), then
+passes raw device pointers and the current torch CUDA stream to the C ABI declared in include/b200decode.h.
+Errors surface as RuntimeError before anything is launched. There is no fallback: if the library is missing,
+cannot be built, or a tensor is not on a CUDA device, the call raises.
+
+Additional operators (no counterpart in the reference): dequant_w4a16, paged_attention_batched,
+rope_append_batched, embed_row, argmax.
+"""
+import ctypes
+import math
+from ctypes import c_float, c_int, c_size_t, c_void_p
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_OPS = None
+LIB_PATH = Path(__file__).resolve().parent / "libb200decode.so"
+
+# name -> argtypes, exactly the declarations of include/b200decode.h (checked by tests/test_abi.py)
+SIGNATURES = {
+    "b200_gemv_w4a16": [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_void_p],
+    "b200_bw_read": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_paged_attention": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "b200_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p],
+    "b200_swiglu": [c_void_p, c_void_p, c_int, c_void_p],
+    "b200_rope_append": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                         c_void_p],
+    "b200_paged_attention_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                     c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "b200_rope_append_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_int, c_void_p],
+    "b200_dequant_w4a16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_embed_row": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "b200_argmax": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+}
+
+
+def load_library(build_if_missing=True):
+    """dlopen libb200decode.so (building it with nvcc first if it is absent) and declare its symbols."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not LIB_PATH.exists():
+        if not build_if_missing:
+            raise RuntimeError(f"{LIB_PATH} is missing; run `python -m llm_decode_kernels_b200.build`")
+        from . import build as _build
+        _build.build()
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError here = the library does not export a declared symbol
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    lib.b200_version.restype = c_int
+    lib.b200_strerror.restype = ctypes.c_char_p
+    lib.b200_strerror.argtypes = [c_int]
+    lib.b200_last_cuda_error.restype = ctypes.c_char_p
+    _LIB = lib
+    return lib
+
+
+def _ilog2_exact(v, what):
+    if v <= 0 or v & (v - 1):
+        raise RuntimeError(f"{what} must be a power of two, got {v}")
+    return v.bit_length() - 1
+
+
+def _cuda(t, name, dtype=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
+        raise RuntimeError(f"{name} must be a contiguous CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t
+
+
+def _aligned16(t, name):
+    if t.data_ptr() % 16:
+        raise RuntimeError(f"{name} must be 16B aligned")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Ops:
+    """The operator set. Every method launches on torch's current CUDA stream and returns None."""
+
+    def __init__(self, lib):
+        self.lib = lib
+
+    def _check(self, code, what):
+        if code != 0:
+            msg = self.lib.b200_strerror(code).decode()
+            if code == -4:
+                msg += ": " + self.lib.b200_last_cuda_error().decode()
+            raise RuntimeError(f"{what}: {msg}")
+
+    # ---- the reference's six operators ------------------------------------------------------------------
+    def gemv_w4a16(self, stage, R, warps, pf, packed, sz, x, y, group):
+        """y = dequant(packed, sz) @ x. packed int32 [N, K/8], sz fp16 [N, K/group, 2], x fp16 [K], y fp16 [N].
+        (stage, R, warps, pf): see b200_gemv_w4a16; pass R=0 for the library's own choice."""
+        _cuda(packed, "packed", torch.int32), _cuda(sz, "sz", torch.float16)
+        _cuda(x, "x", torch.float16), _cuda(y, "y", torch.float16)
+        N, K = packed.shape[0], packed.shape[1] * 8
+        if K % 32 or K % group:
+            raise RuntimeError("K must be a multiple of 32 and of the group size")
+        if group < 32:
+            raise RuntimeError("group must be >= 32")
+        if x.numel() != K or y.numel() != N or sz.shape[0] != N or sz.shape[1] != K // group:
+            raise RuntimeError("gemv_w4a16: inconsistent shapes")
+        _aligned16(packed, "packed"), _aligned16(x, "x")
+        self._check(self.lib.b200_gemv_w4a16(int(stage), int(R), int(warps), int(pf), packed.data_ptr(),
+                                             sz.data_ptr(), x.data_ptr(), y.data_ptr(), N, K,
+                                             _ilog2_exact(int(group), "group"), _stream()), "gemv_w4a16")
+
+    def bw_read(self, buf, sink, blocks, threads, unroll):
+        _cuda(buf, "buf"), _cuda(sink, "sink"), _aligned16(buf, "buf")
+        self._check(self.lib.b200_bw_read(buf.data_ptr(), buf.numel() * buf.element_size(), sink.data_ptr(),
+                                          int(blocks), int(threads), int(unroll), _stream()), "bw_read")
+
+    def paged_attention(self, q, kc, vc, bt, pos, part_size, o_part, m_part, l_part, out, version=2):
+        """One sequence, head_dim 64. q [n_q*64], caches [pages, n_kv, P, 64], bt int32 [pages], pos int32 [1],
+        scratch o_part fp32 [n_q, max_splits, 64], m_part/l_part fp32 [n_q, max_splits], out fp16 [n_q, 64]."""
+        for t, n in ((q, "q"), (kc, "kc"), (vc, "vc"), (out, "out")):
+            _cuda(t, n, torch.float16)
+        _cuda(bt, "bt", torch.int32), _cuda(pos, "pos", torch.int32)
+        for t, n in ((o_part, "o_part"), (m_part, "m_part"), (l_part, "l_part")):
+            _cuda(t, n, torch.float32)
+        if kc.dim() != 4 or kc.shape[3] != 64 or vc.shape != kc.shape:
+            raise RuntimeError("cache must be [pages, n_kv, P, 64]")
+        _aligned16(kc, "kc"), _aligned16(vc, "vc")
+        n_q, n_kv, P = q.numel() // 64, kc.shape[1], kc.shape[2]
+        if n_q % n_kv or n_q // n_kv not in (1, 2, 4, 8):
+            raise RuntimeError("heads-per-group must be 1/2/4/8")
+        if part_size <= 0:
+            raise RuntimeError("part_size must be > 0")
+        if not 1 <= version <= 3:
+            raise RuntimeError("attention version must be 1, 2 or 3")
+        max_splits = o_part.shape[1]
+        if o_part.shape[0] != n_q or m_part.shape[1] != max_splits or l_part.shape[1] != max_splits:
+            raise RuntimeError("split buffers have inconsistent shapes")
+        self._check(self.lib.b200_paged_attention(int(version), q.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                                  bt.data_ptr(), pos.data_ptr(), n_q, n_kv,
+                                                  _ilog2_exact(P, "page size"), int(part_size), max_splits,
+                                                  o_part.data_ptr(), m_part.data_ptr(), l_part.data_ptr(),
+                                                  out.data_ptr(), _stream()), "paged_attention")
+
+    def add_rmsnorm(self, x, delta, w, out, eps):
+        _cuda(x, "x", torch.float16), _cuda(w, "w", torch.float16), _cuda(out, "out", torch.float16)
+        if x.numel() % 8:
+            raise RuntimeError("H must be a multiple of 8")
+        _aligned16(x, "x"), _aligned16(w, "w"), _aligned16(out, "out")
+        d = 0
+        if delta is not None:
+            _cuda(delta, "delta", torch.float16), _aligned16(delta, "delta")
+            d = delta.data_ptr()
+        self._check(self.lib.b200_add_rmsnorm(x.data_ptr(), d, w.data_ptr(), out.data_ptr(), x.numel(), float(eps),
+                                              _stream()), "add_rmsnorm")
+
+    def swiglu(self, gu, out):
+        _cuda(gu, "gu", torch.float16), _cuda(out, "out", torch.float16)
+        if out.numel() % 8 or gu.numel() != 2 * out.numel():
+            raise RuntimeError("swiglu: gu must hold 2*I elements, I a multiple of 8")
+        _aligned16(gu, "gu"), _aligned16(out, "out")
+        self._check(self.lib.b200_swiglu(gu.data_ptr(), out.data_ptr(), out.numel(), _stream()), "swiglu")
+
+    def rope_append(self, qkv, cos_t, sin_t, pos, bt, kc, vc, n_q, n_kv):
+        _cuda(qkv, "qkv", torch.float16), _cuda(cos_t, "cos_t", torch.float32), _cuda(sin_t, "sin_t", torch.float32)
+        _cuda(kc, "kc", torch.float16), _cuda(vc, "vc", torch.float16)
+        _cuda(pos, "pos", torch.int32), _cuda(bt, "bt", torch.int32)
+        if qkv.numel() != (n_q + 2 * n_kv) * 64 or cos_t.shape[1] != 32:
+            raise RuntimeError("rope_append: head_dim must be 64 (use rope_append_batched for other sizes)")
+        self._check(self.lib.b200_rope_append(qkv.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), pos.data_ptr(),
+                                              bt.data_ptr(), kc.data_ptr(), vc.data_ptr(), int(n_q), int(n_kv),
+                                              _ilog2_exact(kc.shape[2], "page size"), _stream()), "rope_append")
+
+    # ---- additions ----------------------------------------------------------------------------------------
+    def paged_attention_batched(self, q, kc, vc, bt, pos, part_size, o_part, m_part, l_part, out):
+        """q [B, n_q, D]; bt int32 [B, max_pages]; pos int32 [B]; o_part [B, n_q, S, D]; m/l_part [B, n_q, S];
+        out [B, n_q, D]; D = 64 or 128."""
+        for t, n in ((q, "q"), (kc, "kc"), (vc, "vc"), (out, "out")):
+            _cuda(t, n, torch.float16)
+        _cuda(bt, "bt", torch.int32), _cuda(pos, "pos", torch.int32)
+        for t, n in ((o_part, "o_part"), (m_part, "m_part"), (l_part, "l_part")):
+            _cuda(t, n, torch.float32)
+        B, n_q, D = q.shape
+        if kc.dim() != 4 or kc.shape[3] != D or vc.shape != kc.shape:
+            raise RuntimeError("cache must be [pages, n_kv, P, D]")
+        if bt.dim() != 2 or bt.shape[0] != B or pos.numel() != B:
+            raise RuntimeError("bt must be [B, max_pages] and pos [B]")
+        S = o_part.shape[2]
+        if tuple(o_part.shape) != (B, n_q, S, D) or tuple(m_part.shape) != (B, n_q, S) or m_part.shape != l_part.shape:
+            raise RuntimeError("split buffers have inconsistent shapes")
+        _aligned16(kc, "kc"), _aligned16(vc, "vc")
+        self._check(self.lib.b200_paged_attention_batched(
+            q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bt.shape[1], pos.data_ptr(), B, n_q,
+            kc.shape[1], D, _ilog2_exact(kc.shape[2], "page size"), int(part_size), S, o_part.data_ptr(),
+            m_part.data_ptr(), l_part.data_ptr(), out.data_ptr(), _stream()), "paged_attention_batched")
+
+    def rope_append_batched(self, qkv, cos_t, sin_t, pos, bt, kc, vc, n_q, n_kv):
+        """qkv [B, (n_q + 2 n_kv) * D]; bt int32 [B, max_pages]; pos int32 [B]; D = 2 * cos_t.shape[1]."""
+        _cuda(qkv, "qkv", torch.float16), _cuda(cos_t, "cos_t", torch.float32), _cuda(sin_t, "sin_t", torch.float32)
+        _cuda(kc, "kc", torch.float16), _cuda(vc, "vc", torch.float16)
+        _cuda(pos, "pos", torch.int32), _cuda(bt, "bt", torch.int32)
+        B, D = qkv.shape[0], 2 * cos_t.shape[1]
+        if qkv.dim() != 2 or qkv.shape[1] != (n_q + 2 * n_kv) * D or kc.shape[3] != D or bt.shape[0] != B:
+            raise RuntimeError("rope_append_batched: inconsistent shapes")
+        self._check(self.lib.b200_rope_append_batched(
+            qkv.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), pos.data_ptr(), bt.data_ptr(), bt.shape[1],
+            kc.data_ptr(), vc.data_ptr(), B, int(n_q), int(n_kv), D, _ilog2_exact(kc.shape[2], "page size"),
+            _stream()), "rope_append_batched")
+
+    def dequant_w4a16(self, packed, sz, out, group):
+        _cuda(packed, "packed", torch.int32), _cuda(sz, "sz", torch.float16), _cuda(out, "out", torch.float16)
+        N, K = packed.shape[0], packed.shape[1] * 8
+        if tuple(out.shape) != (N, K) or K % group:
+            raise RuntimeError("dequant_w4a16: inconsistent shapes")
+        self._check(self.lib.b200_dequant_w4a16(packed.data_ptr(), sz.data_ptr(), out.data_ptr(), N, K,
+                                                _ilog2_exact(int(group), "group"), _stream()), "dequant_w4a16")
+
+    def embed_row(self, emb, tok, x):
+        _cuda(emb, "emb", torch.float16), _cuda(tok, "tok", torch.int64), _cuda(x, "x", torch.float16)
+        self._check(self.lib.b200_embed_row(emb.data_ptr(), tok.data_ptr(), x.data_ptr(), x.numel(), _stream()),
+                    "embed_row")
+
+    def argmax(self, logits, tok, pos=None, history=None):
+        """tok <- argmax(logits), lowest index on ties; with pos: history[pos] <- tok (if given), pos += 1."""
+        _cuda(logits, "logits", torch.float16), _cuda(tok, "tok", torch.int64)
+        p = _cuda(pos, "pos", torch.int32).data_ptr() if pos is not None else 0
+        h = _cuda(history, "history", torch.int64).data_ptr() if history is not None else 0
+        self._check(self.lib.b200_argmax(logits.data_ptr(), logits.numel(), tok.data_ptr(), p, h, _stream()),
+                    "argmax")
+
+
+def load(verbose=False):
+    """Return the operator set (reference runtime/ext.py:9). Raises if the library cannot be loaded."""
+    global _OPS
+    if _OPS is None:
+        _OPS = Ops(load_library())
+    return _OPS

@@ -1,0 +1,335 @@
+"""Batch-1 decode runtime for Llama-family models on the B200 kernels.
+
+Keeps the public surface of the reference's runtime/model.py: `DecodeConfig` (same fields and defaults,
+runtime/model.py:32-50) and `Model(hf_state, hf_config, cfg)` with prepare / capture / run_step / reset /
+teacher_force / generate / weight_bytes / kv_bytes_per_token (runtime/model.py:75-297). One decode step is
+
+    embed -> per layer [ add+RMSNorm -> qkv GEMV -> RoPE + paged-KV append -> paged attention (+combine) -> o GEMV
+                         -> add+RMSNorm -> gate|up GEMV -> SwiGLU -> down GEMV ]
+          -> add+RMSNorm -> LM-head GEMV -> argmax (written to the device token slot) -> pos += 1
+
+with the residual add of `down` deferred into the next layer's first norm, exactly as the reference orders it
+(runtime/model.py:216-233). Token id and position live in device memory and every kernel reads them through
+pointers, so the step is captured once as a CUDA graph and replayed for every token. Prefill is the same step,
+teacher-forced.
+
+This runtime has one backend: the CUDA kernels of libb200decode.so, all weights W4A16. `backend="ref"`,
+`weights="fp16"` and CPU devices are refused; the CPU restatement used for checking lives outside the package.
+"""
+import json
+import math
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import torch
+
+from . import ext
+from .quant import QuantLinear
+
+ROOT = Path(__file__).resolve().parent
+
+
+@dataclass
+class DecodeConfig:
+    weights: str = "int4"        # only "int4" (W4A16) exists in this runtime
+    group: int = 128
+    quant: str = "rtn"           # "rtn" | "clip" (RTN + per-group range clipping) | "pre" (use `qparams`, e.g. GPTQ)
+    qparams: dict = field(default=None, repr=False)  # "layers.{i}.{qkv,o,gu,down}" / "lm_head" -> (q, scale, zero)
+    lm_head: str = "auto"        # "auto" / "int4": INT4 head (the only kind here)
+    fused: bool = True           # False: residual add, RMSNorm and SwiGLU run as separate torch ops (ablation)
+    backend: str = "cuda"        # only "cuda"
+    max_ctx: int = 2048
+    page: int = 16
+    part_size: int = 0           # attention split size; 0 -> policy table, else a size that fills the SMs
+    attn_version: int = 0        # accepted for compatibility; the library has one attention kernel
+    gemv_stage: tuple = None     # (stage, R, warps, pf) forced everywhere; None -> the library's shape-based choice
+    autotune_path: str = str(ROOT / "configs" / "autotune.json")
+    attn_policy_path: str = str(ROOT / "configs" / "attn_policy.json")
+    shuffle_pages: bool = True
+    device: str = "cuda"
+    # ---- additions (defaults keep the reference behaviour) ----
+    seed: int = None             # seed of the page-table shuffle (None: torch's global generator)
+
+
+class Linear:
+    """One W4A16 projection in kernel format (reference runtime/model.py:56-72)."""
+
+    def __init__(self, w, cfg: DecodeConfig, key: str = None, keep_ref: bool = False):
+        self.N, self.K = w.shape
+        self.quant = True
+        pre = None
+        if cfg.quant == "pre":
+            pre = (cfg.qparams or {}).get(key)
+            assert pre is not None, f"no precomputed weights for {key}"
+        ql = QuantLinear(w.to(cfg.device), cfg.group, keep_ref=keep_ref, clip=cfg.quant == "clip", qsz=pre)
+        self.packed, self.sz = ql.packed.to(cfg.device), ql.sz.to(cfg.device)
+        self.w_ref = ql.w_ref
+        self.nbytes = ql.nbytes()
+
+
+def _rope_theta(c):
+    if getattr(c, "rope_theta", None) is not None:
+        return float(c.rope_theta)
+    rp = getattr(c, "rope_parameters", None)          # newer transformers keep it here
+    if isinstance(rp, dict) and "rope_theta" in rp:
+        return float(rp["rope_theta"])
+    return 10000.0
+
+
+class Model:
+    def __init__(self, hf_state: dict, hf_config, cfg: DecodeConfig):
+        if cfg.backend != "cuda":
+            raise ValueError("this runtime has only the CUDA backend; the CPU reference path is not part of it")
+        if cfg.weights != "int4" or cfg.lm_head not in ("auto", "int4"):
+            raise ValueError("this runtime is W4A16 only (weights='int4', INT4 LM head)")
+        if not str(cfg.device).startswith("cuda") or not torch.cuda.is_available():
+            raise RuntimeError("a CUDA device is required: there is no CPU fallback")
+        self.cfg = cfg
+        c = hf_config
+        self.H, self.L = c.hidden_size, c.num_hidden_layers
+        self.n_q, self.n_kv = c.num_attention_heads, c.num_key_value_heads
+        self.D = getattr(c, "head_dim", None) or self.H // self.n_q
+        self.I, self.V = c.intermediate_size, c.vocab_size
+        self.eps = c.rms_norm_eps
+        if self.D not in (64, 128):
+            raise ValueError(f"head_dim {self.D}: kernels exist for 64 and 128")
+        dev = cfg.device
+        self.K = ext.load()
+        sd = hf_state
+        g = lambda k: sd[k].to(dev).half()
+        self.emb = g("model.embed_tokens.weight").contiguous()
+        self.layers = []
+        for i in range(self.L):
+            p = f"model.layers.{i}."
+            wqkv = torch.cat([g(p + "self_attn.q_proj.weight"), g(p + "self_attn.k_proj.weight"),
+                              g(p + "self_attn.v_proj.weight")], 0)
+            wgu = torch.cat([g(p + "mlp.gate_proj.weight"), g(p + "mlp.up_proj.weight")], 0)
+            self.layers.append({
+                "ln1": g(p + "input_layernorm.weight").contiguous(),
+                "ln2": g(p + "post_attention_layernorm.weight").contiguous(),
+                "qkv": Linear(wqkv, cfg, f"layers.{i}.qkv"),
+                "o": Linear(g(p + "self_attn.o_proj.weight"), cfg, f"layers.{i}.o"),
+                "gu": Linear(wgu, cfg, f"layers.{i}.gu"),
+                "down": Linear(g(p + "mlp.down_proj.weight"), cfg, f"layers.{i}.down")})
+            del wqkv, wgu
+        self.norm_f = g("model.norm.weight").contiguous()
+        lm = sd["lm_head.weight"] if "lm_head.weight" in sd else sd["model.embed_tokens.weight"]
+        self.lm_head = Linear(lm.to(dev).half(), cfg, "lm_head")
+
+        # paged KV cache [L, 2, pages, n_kv, P, D]; one block table shared by all layers (one sequence)
+        self.n_pages = (cfg.max_ctx + cfg.page - 1) // cfg.page + 1
+        self.kv = torch.zeros(self.L, 2, self.n_pages, self.n_kv, cfg.page, self.D, dtype=torch.half, device=dev)
+        if cfg.shuffle_pages:
+            gen = torch.Generator().manual_seed(cfg.seed) if cfg.seed is not None else None
+            self.bt = torch.randperm(self.n_pages, generator=gen).int().to(dev)
+        else:
+            self.bt = torch.arange(self.n_pages).int().to(dev)
+        self.cos, self.sin = (t.to(dev) for t in rope_tables(cfg.max_ctx + 1, self.D, _rope_theta(c)))
+
+        # device-resident decode state and static activation buffers
+        h16 = dict(dtype=torch.half, device=dev)
+        self.tok = torch.zeros(1, dtype=torch.long, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.history = torch.zeros(cfg.max_ctx + 2, dtype=torch.long, device=dev)  # token chosen at each position
+        self.x = torch.empty(self.H, **h16)
+        self.normed = torch.empty(self.H, **h16)
+        self.qkv = torch.empty((self.n_q + 2 * self.n_kv) * self.D, **h16)
+        self.attn = torch.empty(self.n_q, self.D, **h16)
+        self.o = torch.empty(self.H, **h16)
+        self.gu = torch.empty(2 * self.I, **h16)
+        self.act = torch.empty(self.I, **h16)
+        self.down = torch.empty(self.H, **h16)
+        self.logits = torch.empty(self.V, **h16)
+        self.graph = None
+        self.host_pos = 0
+        self.set_attention_partition(cfg.max_ctx)
+
+    # ------------------------------------------------------------------ attention partitioning
+    def _policy(self):
+        p = Path(self.cfg.attn_policy_path)
+        return json.load(open(p)) if p.exists() else {}
+
+    def _policy_part_size(self, ctx_cap):
+        """Policy-table entry tuned at the largest context <= ctx_cap (reference runtime/model.py:164-172); with no
+        table, the smallest multiple of 32 tokens for which n_kv x splits still covers every SM about once."""
+        ents = [e for e in self._policy().get("policy", []) if e["max_ctx"] < (1 << 30)]
+        if ents:
+            below = [e for e in ents if e["max_ctx"] <= ctx_cap]
+            return (below[-1] if below else ents[0])["part_size"]
+        sms = torch.cuda.get_device_properties(self.cfg.device).multi_processor_count
+        want_splits = max(1, (2 * sms) // self.n_kv)
+        ps = 32 * max(1, math.ceil(ctx_cap / want_splits / 32))
+        return max(64, ps)
+
+    def set_attention_partition(self, ctx_cap, part_size=None):
+        """Choose the split size for contexts up to ctx_cap and size the split scratch; the attention grid is fixed at
+        ceil(ctx_cap / part_size) splits and surplus ones exit (reference runtime/model.py:140-151)."""
+        ps = part_size or self.cfg.part_size or self._policy_part_size(ctx_cap)
+        self.part_size = ps
+        self.max_splits = max(1, math.ceil(ctx_cap / ps))
+        self.ctx_cap = self.max_splits * ps   # attention ignores tokens past this; run_step enforces it
+        f32 = dict(dtype=torch.float32, device=self.cfg.device)
+        self.o_part = torch.empty(self.n_q, self.max_splits, self.D, **f32)
+        self.m_part = torch.empty(self.n_q, self.max_splits, **f32)
+        self.l_part = torch.empty(self.n_q, self.max_splits, **f32)
+        self.graph = None
+
+    def prepare(self, ctx_cap, use_graph=True, part_size=None):
+        """Configure attention for contexts <= ctx_cap and (re)capture the decode graph."""
+        assert ctx_cap <= self.cfg.max_ctx
+        self.set_attention_partition(ctx_cap, part_size)
+        if use_graph:
+            self.capture()
+
+    # ------------------------------------------------------------------ operators
+    def gemv_cfg(self, lin):
+        return self.cfg.gemv_stage if self.cfg.gemv_stage is not None else (2, 0, 0, 0)
+
+    def linear(self, lin: Linear, x, y):
+        s, r, w, pf = self.gemv_cfg(lin)
+        self.K.gemv_w4a16(s, r, w, pf, lin.packed, lin.sz, x, y, self.cfg.group)
+
+    def add_norm(self, delta, w):
+        if self.cfg.fused:
+            self.K.add_rmsnorm(self.x, delta, w, self.normed, self.eps)
+        else:  # the unfused op sequence, on the device (ablation)
+            if delta is not None:
+                self.x.add_(delta)
+            xf = self.x.float()
+            self.normed.copy_(w * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).half())
+
+    def swiglu(self):
+        if self.cfg.fused:
+            self.K.swiglu(self.gu, self.act)
+        else:
+            s = torch.nn.functional.silu(self.gu[: self.I].float()).half()
+            torch.mul(s, self.gu[self.I:], out=self.act)
+
+    def attention(self, li):
+        kc, vc = self.kv[li, 0], self.kv[li, 1]
+        if self.D == 64:
+            self.K.rope_append(self.qkv, self.cos, self.sin, self.pos, self.bt, kc, vc, self.n_q, self.n_kv)
+            self.K.paged_attention(self.qkv[: self.n_q * self.D], kc, vc, self.bt, self.pos, self.part_size,
+                                   self.o_part, self.m_part, self.l_part, self.attn, 3)
+        else:
+            self.K.rope_append_batched(self.qkv.view(1, -1), self.cos, self.sin, self.pos, self.bt.view(1, -1), kc, vc,
+                                       self.n_q, self.n_kv)
+            self.K.paged_attention_batched(self.qkv[: self.n_q * self.D].view(1, self.n_q, self.D), kc, vc,
+                                           self.bt.view(1, -1), self.pos, self.part_size, self.o_part.unsqueeze(0),
+                                           self.m_part.unsqueeze(0), self.l_part.unsqueeze(0),
+                                           self.attn.view(1, self.n_q, self.D))
+
+    # ------------------------------------------------------------------ decode step
+    def step(self):
+        """One token: reads self.tok / self.pos, writes self.logits, self.tok <- argmax, self.pos += 1."""
+        self.K.embed_row(self.emb, self.tok, self.x)
+        delta = None
+        for li, lw in enumerate(self.layers):
+            self.add_norm(delta, lw["ln1"])
+            self.linear(lw["qkv"], self.normed, self.qkv)
+            self.attention(li)
+            self.linear(lw["o"], self.attn.view(-1), self.o)
+            self.add_norm(self.o, lw["ln2"])
+            self.linear(lw["gu"], self.normed, self.gu)
+            self.swiglu()
+            self.linear(lw["down"], self.act, self.down)
+            delta = self.down
+        self.add_norm(delta, self.norm_f)
+        self.linear(self.lm_head, self.normed, self.logits)
+        self.K.argmax(self.logits, self.tok, self.pos, self.history)
+
+    def capture(self):
+        """Capture step() into a CUDA graph (two warm-up steps on a side stream first, as torch requires).
+        Warm-up runs at positions 0 and 1 (reference runtime/model.py:235-251); the token, position, history
+        entries and the KV page it touches are saved and put back, so capturing in mid-sequence loses nothing."""
+        saved_tok, saved_pos, saved_hist = self.tok.clone(), self.pos.clone(), self.history[:2].clone()
+        page0 = int(self.bt[0])
+        saved_kv = self.kv[:, :, page0].clone()
+        self.pos.zero_()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self.step()
+        torch.cuda.current_stream().wait_stream(s)
+        self.pos.zero_()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step()
+        self.tok.copy_(saved_tok)
+        self.pos.copy_(saved_pos)
+        self.history[:2].copy_(saved_hist)
+        self.kv[:, :, page0].copy_(saved_kv)
+        torch.cuda.synchronize()
+
+    def run_step(self, use_graph=True):
+        self.host_pos += 1
+        if self.host_pos > self.ctx_cap or self.host_pos > self.cfg.max_ctx:
+            raise RuntimeError(f"context {self.host_pos} exceeds the prepared attention cap "
+                               f"{min(self.ctx_cap, self.cfg.max_ctx)}; call prepare()")
+        if use_graph and self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step()
+
+    # ------------------------------------------------------------------ high level
+    def reset(self, pos=0):
+        self.pos.fill_(pos)
+        self.host_pos = pos
+
+    def teacher_force(self, tokens, use_graph=True, collect_logits=False):
+        """Feed tokens[i] at positions pos, pos+1, ...; returns logits [len, V] fp16 if requested."""
+        tokens = torch.as_tensor(tokens).long()
+        if tokens.device.type != "cuda":
+            tokens = (tokens.pin_memory() if tokens.numel() else tokens).to(self.tok.device, non_blocking=True)
+        out = torch.empty(len(tokens), self.V, dtype=torch.half, device=self.tok.device) if collect_logits else None
+        for i in range(len(tokens)):
+            self.tok.copy_(tokens[i:i + 1])
+            self.run_step(use_graph)
+            if collect_logits:
+                out[i].copy_(self.logits)
+        return out
+
+    def generate(self, prompt, n_new, use_graph=True):
+        """Greedy: teacher-force the prompt, then free-run. Returns the n_new token ids as a list, reading each
+        one back from the device as it is produced (reference runtime/model.py:278-286)."""
+        self.reset(0)
+        self.teacher_force(prompt, use_graph)
+        new = [int(self.tok)]
+        for _ in range(n_new - 1):
+            self.run_step(use_graph)
+            new.append(int(self.tok))
+        return new
+
+    def generate_on_device(self, prompt, n_new, use_graph=True):
+        """Same token stream as generate(), without a host read per token: the steps are queued back to back and
+        the tokens come from the device-side history afterwards. Returns an int64 CPU tensor [n_new]."""
+        self.reset(0)
+        self.teacher_force(prompt, use_graph)
+        for _ in range(n_new - 1):
+            self.run_step(use_graph)
+        first = len(prompt) - 1
+        return self.history[first:first + n_new].cpu()
+
+    # ------------------------------------------------------------------ byte accounting (for the roofline)
+    def weight_bytes(self):
+        b = sum(l[k].nbytes for l in self.layers for k in ("qkv", "o", "gu", "down"))
+        b += sum(l["ln1"].numel() * 2 + l["ln2"].numel() * 2 for l in self.layers)
+        return {"body": b, "lm_head": self.lm_head.nbytes, "embedding_row": self.H * 2}
+
+    def kv_bytes_per_token(self, ctx):
+        """KV bytes read by attention at context ctx plus the new K, V rows written, all layers."""
+        row = self.n_kv * self.D * 2
+        return self.L * (2 * row * ctx + 2 * row)
+
+    def bytes_per_token(self, ctx):
+        wb = self.weight_bytes()
+        return wb["body"] + wb["lm_head"] + wb["embedding_row"] + self.kv_bytes_per_token(ctx)
+
+
+def rope_tables(max_pos: int, head_dim: int = 64, theta: float = 10000.0, device="cpu"):
+    """cos / sin tables fp32 [max_pos, head_dim/2], angles computed in float64 (reference
+    reference/ref_ops.py:30-33); the layout rope_append reads."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64, device=device) / head_dim))
+    ang = torch.arange(max_pos, dtype=torch.float64, device=device)[:, None] * inv[None]
+    return ang.cos().float().contiguous(), ang.sin().float().contiguous()

@@ -27,18 +27,26 @@ class OracleLinear:
     """fp16 dequantized weight of one projection. Built either by quantizing `w` with the oracle's
     own quantizer (reference runtime/model.py:56-72) or from tensors already in kernel format."""
 
+    ROWS = 512  # rows are independent: work in row blocks so numpy temporaries stay cache-sized
+
     def __init__(self, w=None, group=128, clip=False, qsz=None, packed=None, sz=None):
-        if packed is not None:
-            q = Q.unpack(np.ascontiguousarray(packed))
-            szn = np.asarray(sz)
-            s, z = szn[..., 0], szn[..., 1]
-        elif qsz is not None:
-            q, s, z = (np.asarray(t) for t in qsz)
-        else:
-            q, s, z = Q.quantize(np.asarray(w), group, clip)
-        self.N, self.K = q.shape
-        self.nbytes = (self.K // 8) * self.N * 4 + s.size * 4
-        self.w_ref = torch.from_numpy(Q.dequantize(q, s, z, group))
+        n = (packed if packed is not None else qsz[0] if qsz is not None else w).shape[0]
+        out, n_sz = [], 0
+        for r0 in range(0, n, self.ROWS):
+            r = slice(r0, r0 + self.ROWS)
+            if packed is not None:
+                q = Q.unpack(np.ascontiguousarray(packed[r]))
+                szn = np.asarray(sz[r])
+                s, z = szn[..., 0], szn[..., 1]
+            elif qsz is not None:
+                q, s, z = (np.asarray(t[r]) for t in qsz)
+            else:
+                q, s, z = Q.quantize(np.asarray(w[r]), group, clip)
+            out.append(Q.dequantize(q, s, z, group))
+            n_sz += s.size
+        self.w_ref = torch.from_numpy(np.concatenate(out, axis=0))
+        self.N, self.K = self.w_ref.shape
+        self.nbytes = (self.K // 8) * self.N * 4 + n_sz * 4
 
 
 class OracleModel:
@@ -57,7 +65,9 @@ class OracleModel:
         self.cfg = cfg
         self.H, self.L = c.hidden_size, c.num_hidden_layers
         self.n_q, self.n_kv = c.num_attention_heads, c.num_key_value_heads
-        self.D = self.H // self.n_q
+        # the reference derives head_dim as hidden / heads (runtime/model.py:81); an explicit head_dim attribute,
+        # which it does not know, is honoured here for the head_dim-128 shapes
+        self.D = getattr(c, "head_dim", None) or self.H // self.n_q
         self.I, self.V = c.intermediate_size, c.vocab_size
         self.eps = c.rms_norm_eps
         sd = hf_state
