@@ -34,31 +34,9 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-TINYLLAMA = dict(hidden_size=2048, num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4,
-                 intermediate_size=5632, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0)
+from llm_decode_kernels_b200.shapes import TINYLLAMA, random_llama_state  # noqa: E402
+
 PROMPT_LEN, NEW_TOKENS, GROUP = 128, 256, 128
-
-
-def random_llama_state(c, device, seed, dtype=torch.float16, layers=None):
-    """HF-Llama-named random weights N(0, 0.02), norm weights 1 (LlamaConfig's initializer_range)."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    rn = lambda *s: (torch.randn(*s, generator=g, device=device) * 0.02).to(dtype)
-    H, I, V = c.hidden_size, c.intermediate_size, c.vocab_size
-    D = H // c.num_attention_heads
-    sd = {"model.embed_tokens.weight": rn(V, H), "model.norm.weight": torch.ones(H, dtype=dtype, device=device),
-          "lm_head.weight": rn(V, H)}
-    for i in range(c.num_hidden_layers if layers is None else layers):
-        p = f"model.layers.{i}."
-        sd[p + "input_layernorm.weight"] = torch.ones(H, dtype=dtype, device=device)
-        sd[p + "post_attention_layernorm.weight"] = torch.ones(H, dtype=dtype, device=device)
-        sd[p + "self_attn.q_proj.weight"] = rn(c.num_attention_heads * D, H)
-        sd[p + "self_attn.k_proj.weight"] = rn(c.num_key_value_heads * D, H)
-        sd[p + "self_attn.v_proj.weight"] = rn(c.num_key_value_heads * D, H)
-        sd[p + "self_attn.o_proj.weight"] = rn(H, c.num_attention_heads * D)
-        sd[p + "mlp.gate_proj.weight"] = rn(I, H)
-        sd[p + "mlp.up_proj.weight"] = rn(I, H)
-        sd[p + "mlp.down_proj.weight"] = rn(H, I)
-    return sd
 
 
 # ---------------------------------------------------------------------------------------------- clocks
