@@ -101,6 +101,55 @@ int b200_embed_row(const void* emb, const long long* tok, void* x, int H, void* 
  * (torch.argmax and `pos += 1` in the reference's step, runtime/model.py:232-233.) */
 int b200_argmax(const void* logits, int V, long long* tok, int* pos, long long* history, void* stream);
 
+/* ---- the whole decode step as one persistent kernel ----
+ * Replaces, for one token, the launch sequence of the reference's Model.step() (runtime/model.py:216-233): embedding
+ * row, per layer [add+RMSNorm, qkv GEMV, RoPE + KV append, attention, o GEMV, add+RMSNorm, gate|up GEMV, SwiGLU,
+ * down GEMV], final norm, LM-head GEMV, argmax into tok, history[pos] = tok, pos += 1. One cooperative launch of
+ * `grid` CTAs (one per SM); weights stream through shared-memory rings, CTAs exchange activations through `xchg`.
+ * The reference has no such entry point: there the step is ~225 launches issued from Python. */
+
+/* One decoder layer. An array of L of these lives in DEVICE memory. Matrix order in w[] / sz[]:
+ * 0 = [q;k;v] ((n_q + 2 n_kv) D x H), 1 = o (H x n_q D), 2 = [gate;up] (2I x H), 3 = down (H x I). */
+typedef struct b200_step_layer {
+  const void* w[4];  /* packed int32 [N, K/8] */
+  const void* sz[4]; /* half2 (scale, zero) [N, K/G] */
+  const void* ln1;   /* fp16 [H] */
+  const void* ln2;   /* fp16 [H] */
+  void* kc;          /* fp16 [pages, n_kv, P, D] */
+  void* vc;
+} b200_step_layer;
+
+/* Host-side description of a step; every pointer inside points to device memory. */
+typedef struct b200_step_desc {
+  const b200_step_layer* layers;
+  int L, H, I, n_q, n_kv, D, V, log2G, log2P;
+  float eps;
+  const void* emb;     /* fp16 [vocab, H] */
+  const void* norm_f;  /* fp16 [H] */
+  const void* w_head;  /* packed [V, H/8] */
+  const void* sz_head; /* half2 [V, H/G] */
+  const float* cos_t;  /* fp32 [max_pos, D/2] */
+  const float* sin_t;
+  const int* bt;       /* int32 block table of the sequence */
+  long long* tok;      /* int64 [1]: token to consume; receives the argmax */
+  int* pos;            /* int32 [1]: position of tok; incremented */
+  long long* history;  /* int64 [max positions] or NULL */
+  void* logits;        /* fp16 [V] */
+  void* xchg;          /* b200_decode_step_xchg_bytes() bytes, zeroed once by the caller, then owned by the step */
+  void* ctrl;          /* 16 bytes, zeroed once: {uint32 completed steps, int32 error, int32 abort, pad} */
+  int ctx_cap;         /* largest context (pos + 1) this launch may see */
+  int grid;            /* CTAs = SMs of the device */
+} b200_step_desc;
+
+/* Bytes of exchange memory a step of these dimensions needs. */
+size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D, int grid);
+
+/* Launch one step. B200_ERR_SHAPE if the dimensions do not fit the kernel's shared-memory plan (use the
+ * per-operator entry points then), B200_ERR_LIMIT if ctx_cap is beyond what the in-kernel attention holds.
+ * Waits inside the kernel are bounded: if one gives up, ctrl.error becomes non-zero (1 tag poll, 2 ring full,
+ * 3 ring empty) and the step's outputs are invalid; the caller checks it after synchronising. */
+int b200_decode_step(const b200_step_desc* d, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,6 +4,7 @@
 // fails on the host with a code instead of faulting on the device.
 #include "../../include/b200decode.h"
 #include "common.cuh"
+#include "decode_step.h"
 
 namespace b200 {
 cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, const void* SZ, const void* x, void* y,
@@ -147,6 +148,66 @@ int b200_embed_row(const void* emb, const long long* tok, void* x, int H, void* 
   REQUIRE(H % 8 == 0, B200_ERR_SHAPE);
   REQUIRE(aligned16(emb) && aligned16(x), B200_ERR_ALIGN);
   return finish(b200::embed_row_dispatch(emb, tok, x, H, S(stream)));
+}
+
+static inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
+
+size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D, int grid) {
+  const size_t per_layer = (size_t)(n_q + 2 * n_kv) * D + (size_t)n_q * D + H + I + H;
+  return (per_layer * L + (size_t)grid * 4) * sizeof(uint32_t);
+}
+
+int b200_decode_step(const b200_step_desc* d, void* stream) {
+  static_assert(sizeof(b200_step_layer) == sizeof(b200::StepLayer), "layer structs must match");
+  REQUIRE(d && d->layers && d->emb && d->norm_f && d->w_head && d->sz_head && d->cos_t && d->sin_t && d->bt &&
+              d->tok && d->pos && d->logits && d->xchg && d->ctrl,
+          B200_ERR_ARG);
+  REQUIRE(d->L > 0 && d->H > 0 && d->I > 0 && d->n_q > 0 && d->n_kv > 0 && d->V > 0 && d->grid > 0 && d->ctx_cap > 0,
+          B200_ERR_ARG);
+  REQUIRE(d->D == 64 || d->D == 128, B200_ERR_SHAPE);
+  REQUIRE(d->n_q % d->n_kv == 0 && d->log2G >= 5 && d->log2G <= 10 && d->log2P >= 0 && d->log2P < 16, B200_ERR_SHAPE);
+  const int n_att = d->n_q * d->D;
+  const int Ks[3] = {d->H, n_att, d->I};
+  int kmax = 0;
+  for (int K : Ks) {
+    // rows are copied with 16-byte-granular bulk copies: packed row and scale/zero row must both be multiples of 16 B
+    REQUIRE(K % 32 == 0 && K % (1 << d->log2G) == 0 && ((K >> d->log2G) % 4) == 0, B200_ERR_SHAPE);
+    kmax = K > kmax ? K : kmax;
+  }
+  REQUIRE(d->H % 8 == 0 && d->I % 8 == 0, B200_ERR_SHAPE);
+  REQUIRE(aligned16(d->emb) && aligned16(d->norm_f) && aligned16(d->w_head) && aligned16(d->sz_head) &&
+              aligned16(d->xchg) && aligned16(d->ctrl),
+          B200_ERR_ALIGN);
+  REQUIRE(d->ctx_cap <= 8192, B200_ERR_LIMIT);
+
+  b200::StepParams p = {};
+  p.layers = reinterpret_cast<const b200::StepLayer*>(d->layers);
+  p.L = d->L; p.H = d->H; p.I = d->I; p.n_q = d->n_q; p.n_kv = d->n_kv; p.D = d->D; p.V = d->V;
+  p.log2G = d->log2G; p.log2P = d->log2P; p.eps = d->eps;
+  p.emb = (const half*)d->emb; p.norm_f = (const half*)d->norm_f; p.w_head = d->w_head; p.sz_head = d->sz_head;
+  p.cos_t = d->cos_t; p.sin_t = d->sin_t; p.bt = d->bt; p.tok = d->tok; p.pos = d->pos; p.history = d->history;
+  p.logits = (half*)d->logits; p.xchg = (uint32_t*)d->xchg; p.ctrl = (b200::StepCtrl*)d->ctrl;
+  // shared-memory plan
+  const int nt = b200::decode_step_consumer_threads();
+  p.resid_bytes = align_up(2 * d->H, 128);
+  p.xin_bytes = align_up(2 * kmax, 128);
+  p.att_bytes = align_up((4 * d->D + 2 * nt + d->ctx_cap + 64) * 4, 128);
+  const int max_rowbytes = kmax / 2;
+  p.stage_w = align_up(2 * max_rowbytes > 16384 ? 2 * max_rowbytes : 16384, 128);
+  int max_sz = 0;
+  for (int K : Ks) {
+    const int rowbytes = K / 2, ups = p.stage_w / (2 * rowbytes) > 1 ? p.stage_w / (2 * rowbytes) : 1;
+    const int sz = 2 * ups * ((K >> d->log2G) * 4);
+    max_sz = sz > max_sz ? sz : max_sz;
+  }
+  p.stage_bytes = p.stage_w + align_up(max_sz, 128);
+  const size_t fixed = b200::decode_step_smem_fixed(p);
+  const size_t budget = 227 * 1024;
+  REQUIRE(fixed + 2 * (size_t)p.stage_bytes <= budget, B200_ERR_SHAPE);
+  int ns = (int)((budget - fixed) / p.stage_bytes);
+  if (ns > b200::decode_step_max_stages()) ns = b200::decode_step_max_stages();
+  p.ns = ns;
+  return finish(b200::decode_step_launch(p, d->grid, fixed + (size_t)ns * p.stage_bytes, S(stream)));
 }
 
 int b200_argmax(const void* logits, int V, long long* tok, int* pos, long long* history, void* stream) {

@@ -93,4 +93,12 @@ DEVI void unpack8(uint4 v, float* f) {
   }
 }
 
+// Order key for greedy argmax over fp16 logits: larger value wins, then the lower index. One max-reduction
+// over these keys settles value and tie-break together.
+DEVI unsigned long long argmax_key(half v, int idx) {
+  uint32_t b = (uint32_t)__half_as_ushort(v);
+  b = (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);  // monotone map of fp16 bits to unsigned order
+  return ((unsigned long long)b << 32) | (uint32_t)(0x7FFFFFFF - idx);
+}
+
 }  // namespace b200

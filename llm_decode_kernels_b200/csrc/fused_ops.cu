@@ -153,12 +153,6 @@ cudaError_t embed_row_dispatch(const void* emb, const long long* tok, void* x, i
 // With `history`, the chosen token is also stored at history[pos before the increment], so a run of graph
 // replays leaves its whole token stream on the device and the host need not read a token per step.
 // One block of 1024 threads; the order key packs (value, inverted index) so one max-reduction settles ties.
-DEVI unsigned long long argmax_key(half v, int idx) {
-  uint32_t b = (uint32_t)__half_as_ushort(v);
-  b = (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);  // monotone map of fp16 bits to unsigned order
-  return ((unsigned long long)b << 32) | (uint32_t)(0x7FFFFFFF - idx);
-}
-
 __global__ void __launch_bounds__(1024)
 argmax_kernel(const half* __restrict__ logits, int V, long long* __restrict__ tok, int* __restrict__ pos,
               long long* __restrict__ history) {

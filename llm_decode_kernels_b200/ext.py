@@ -43,6 +43,21 @@ SIGNATURES = {
 }
 
 
+class StepLayer(ctypes.Structure):
+    """b200_step_layer of include/b200decode.h (an array of these is copied to device memory)."""
+    _fields_ = [("w", c_void_p * 4), ("sz", c_void_p * 4), ("ln1", c_void_p), ("ln2", c_void_p), ("kc", c_void_p),
+                ("vc", c_void_p)]
+
+
+class StepDesc(ctypes.Structure):
+    """b200_step_desc of include/b200decode.h."""
+    _fields_ = [("layers", c_void_p), ("L", c_int), ("H", c_int), ("I", c_int), ("n_q", c_int), ("n_kv", c_int),
+                ("D", c_int), ("V", c_int), ("log2G", c_int), ("log2P", c_int), ("eps", c_float), ("emb", c_void_p),
+                ("norm_f", c_void_p), ("w_head", c_void_p), ("sz_head", c_void_p), ("cos_t", c_void_p),
+                ("sin_t", c_void_p), ("bt", c_void_p), ("tok", c_void_p), ("pos", c_void_p), ("history", c_void_p),
+                ("logits", c_void_p), ("xchg", c_void_p), ("ctrl", c_void_p), ("ctx_cap", c_int), ("grid", c_int)]
+
+
 def load_library(build_if_missing=True):
     """dlopen libb200decode.so (building it with nvcc first if it is absent) and declare its symbols."""
     global _LIB
@@ -58,6 +73,10 @@ def load_library(build_if_missing=True):
         fn = getattr(lib, name)          # AttributeError here = the library does not export a declared symbol
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.b200_decode_step.argtypes = [ctypes.POINTER(StepDesc), c_void_p]
+    lib.b200_decode_step.restype = c_int
+    lib.b200_decode_step_xchg_bytes.argtypes = [c_int] * 7
+    lib.b200_decode_step_xchg_bytes.restype = c_size_t
     lib.b200_version.restype = c_int
     lib.b200_strerror.restype = ctypes.c_char_p
     lib.b200_strerror.argtypes = [c_int]
@@ -237,6 +256,14 @@ class Ops:
         h = _cuda(history, "history", torch.int64).data_ptr() if history is not None else 0
         self._check(self.lib.b200_argmax(logits.data_ptr(), logits.numel(), tok.data_ptr(), p, h, _stream()),
                     "argmax")
+
+
+    def decode_step_xchg_bytes(self, L, H, I, n_q, n_kv, D, grid):
+        return int(self.lib.b200_decode_step_xchg_bytes(L, H, I, n_q, n_kv, D, grid))
+
+    def decode_step(self, desc: "StepDesc"):
+        """One whole decode step as one persistent kernel (b200_decode_step) on the current stream."""
+        self._check(self.lib.b200_decode_step(ctypes.byref(desc), _stream()), "decode_step")
 
 
 def load(verbose=False):

@@ -49,6 +49,12 @@ class DecodeConfig:
     device: str = "cuda"
     # ---- additions (defaults keep the reference behaviour) ----
     seed: int = None             # seed of the page-table shuffle (None: torch's global generator)
+    step_kernel: str = "auto"    # "persistent": the whole step is one kernel (b200_decode_step); "multi": one launch
+                                 # per operator, as the reference does; "auto": persistent when fused and the
+                                 # prepared context cap is within PERSISTENT_MAX_CTX
+
+
+PERSISTENT_MAX_CTX = 2048   # beyond this the in-kernel attention (one CTA per query head) stops paying off
 
 
 class Linear:
@@ -173,6 +179,55 @@ class Model:
         self.m_part = torch.empty(self.n_q, self.max_splits, **f32)
         self.l_part = torch.empty(self.n_q, self.max_splits, **f32)
         self.graph = None
+        self._setup_persistent_step()
+
+    def _setup_persistent_step(self):
+        """Describe the step for b200_decode_step: device array of per-layer pointers, exchange and control memory."""
+        import ctypes
+        mode = self.cfg.step_kernel
+        G = self.cfg.group
+        fits = all(k % 32 == 0 and k % G == 0 and (k // G) % 4 == 0 for k in (self.H, self.n_q * self.D, self.I))
+        self.persistent = mode == "persistent" or (mode == "auto" and self.cfg.fused and fits
+                                                   and self.ctx_cap <= PERSISTENT_MAX_CTX)
+        if mode == "persistent" and not fits:
+            raise ValueError("step_kernel='persistent' needs every K (hidden, heads*head_dim, intermediate) to hold a "
+                             "multiple of 4 quantization groups; use step_kernel='multi' for this shape")
+        if mode == "persistent" and not self.cfg.fused:
+            raise ValueError("step_kernel='persistent' computes the fused operators; it cannot run with fused=False")
+        if not self.persistent:
+            return
+        dev = self.cfg.device
+        if getattr(self, "_step_static", None) is None:
+            arr = (ext.StepLayer * self.L)()
+            for i, lw in enumerate(self.layers):
+                for k, name in enumerate(("qkv", "o", "gu", "down")):
+                    arr[i].w[k] = lw[name].packed.data_ptr()
+                    arr[i].sz[k] = lw[name].sz.data_ptr()
+                arr[i].ln1, arr[i].ln2 = lw["ln1"].data_ptr(), lw["ln2"].data_ptr()
+                arr[i].kc, arr[i].vc = self.kv[i, 0].data_ptr(), self.kv[i, 1].data_ptr()
+            host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
+            grid = torch.cuda.get_device_properties(dev).multi_processor_count
+            nbytes = self.K.decode_step_xchg_bytes(self.L, self.H, self.I, self.n_q, self.n_kv, self.D, grid)
+            self._step_static = {"layers": host.to(dev), "xchg": torch.zeros(nbytes, dtype=torch.uint8, device=dev),
+                                 "ctrl": torch.zeros(4, dtype=torch.int32, device=dev), "grid": grid}
+        st = self._step_static
+        d = ext.StepDesc()
+        d.layers = st["layers"].data_ptr()
+        d.L, d.H, d.I, d.n_q, d.n_kv, d.D, d.V = self.L, self.H, self.I, self.n_q, self.n_kv, self.D, self.V
+        d.log2G, d.log2P, d.eps = self.cfg.group.bit_length() - 1, self.cfg.page.bit_length() - 1, self.eps
+        d.emb, d.norm_f = self.emb.data_ptr(), self.norm_f.data_ptr()
+        d.w_head, d.sz_head = self.lm_head.packed.data_ptr(), self.lm_head.sz.data_ptr()
+        d.cos_t, d.sin_t, d.bt = self.cos.data_ptr(), self.sin.data_ptr(), self.bt.data_ptr()
+        d.tok, d.pos, d.history = self.tok.data_ptr(), self.pos.data_ptr(), self.history.data_ptr()
+        d.logits, d.xchg, d.ctrl = self.logits.data_ptr(), st["xchg"].data_ptr(), st["ctrl"].data_ptr()
+        d.ctx_cap, d.grid = min(self.ctx_cap, self.cfg.max_ctx + 1), st["grid"]
+        self._step_desc = d
+
+    def step_error(self):
+        """Code left by the persistent step kernel if one of its bounded waits gave up (0 = none). Synchronises."""
+        if not getattr(self, "persistent", False):
+            return 0
+        return int(self._step_static["ctrl"][1])
 
     def prepare(self, ctx_cap, use_graph=True, part_size=None):
         """Configure attention for contexts <= ctx_cap and (re)capture the decode graph."""
@@ -222,6 +277,9 @@ class Model:
     # ------------------------------------------------------------------ decode step
     def step(self):
         """One token: reads self.tok / self.pos, writes self.logits, self.tok <- argmax, self.pos += 1."""
+        if self.persistent:
+            self.K.decode_step(self._step_desc)
+            return
         self.K.embed_row(self.emb, self.tok, self.x)
         delta = None
         for li, lw in enumerate(self.layers):
