@@ -139,6 +139,7 @@ typedef struct b200_step_desc {
   void* ctrl;          /* 16 bytes, zeroed once: {uint32 completed steps, int32 error, int32 abort, pad} */
   int ctx_cap;         /* largest context (pos + 1) this launch may see */
   int grid;            /* CTAs = SMs of the device */
+  long long* trace;    /* NULL, or int64 [grid, 16 + 16 L]: per-CTA globaltimer (ns) at every phase boundary */
 } b200_step_desc;
 
 /* Bytes of exchange memory a step of these dimensions needs. */

@@ -171,14 +171,14 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
   int kmax = 0;
   for (int K : Ks) {
     // rows are copied with 16-byte-granular bulk copies: packed row and scale/zero row must both be multiples of 16 B
-    REQUIRE(K % 32 == 0 && K % (1 << d->log2G) == 0 && ((K >> d->log2G) % 4) == 0, B200_ERR_SHAPE);
+    REQUIRE(K % 128 == 0 && K % (1 << d->log2G) == 0 && ((K >> d->log2G) % 4) == 0, B200_ERR_SHAPE);
     kmax = K > kmax ? K : kmax;
   }
   REQUIRE(d->H % 8 == 0 && d->I % 8 == 0, B200_ERR_SHAPE);
   REQUIRE(aligned16(d->emb) && aligned16(d->norm_f) && aligned16(d->w_head) && aligned16(d->sz_head) &&
               aligned16(d->xchg) && aligned16(d->ctrl),
           B200_ERR_ALIGN);
-  REQUIRE(d->ctx_cap <= 8192, B200_ERR_LIMIT);
+  REQUIRE(d->ctx_cap <= (1 << 20), B200_ERR_LIMIT);
 
   b200::StepParams p = {};
   p.layers = reinterpret_cast<const b200::StepLayer*>(d->layers);
@@ -187,13 +187,31 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
   p.emb = (const half*)d->emb; p.norm_f = (const half*)d->norm_f; p.w_head = d->w_head; p.sz_head = d->sz_head;
   p.cos_t = d->cos_t; p.sin_t = d->sin_t; p.bt = d->bt; p.tok = d->tok; p.pos = d->pos; p.history = d->history;
   p.logits = (half*)d->logits; p.xchg = (uint32_t*)d->xchg; p.ctrl = (b200::StepCtrl*)d->ctrl;
+  p.trace = d->trace;
   // shared-memory plan
-  const int nt = b200::decode_step_consumer_threads();
+  const int ncw = b200::decode_step_consumer_warps();
   p.resid_bytes = align_up(2 * d->H, 128);
   p.xin_bytes = align_up(2 * kmax, 128);
-  p.att_bytes = align_up((4 * d->D + 2 * nt + d->ctx_cap + 64) * 4, 128);
+  p.xsum_bytes = align_up((kmax / 32) * 4, 128);
+  p.att_bytes = align_up((4 * d->D + ncw * d->D + 2 * ncw + 64) * 4, 128);
+  {
+    // partial sums of one slice: 2 rows per unit, one float per 1024-weight segment of each row
+    const int n_qkv = (d->n_q + 2 * d->n_kv) * d->D;
+    const int units[5] = {(n_qkv + 1) / 2, (d->H + 1) / 2, d->I, (d->H + 1) / 2, (d->V + 1) / 2};
+    const int ks[5] = {d->H, n_att, d->H, d->I, d->H};
+    int floats = 0;
+    for (int i = 0; i < 5; ++i) {
+      const int per_cta = (units[i] + d->grid - 1) / d->grid, segs = (ks[i] / 32 + 31) / 32;
+      floats = 2 * per_cta * segs > floats ? 2 * per_cta * segs : floats;
+    }
+    p.part_bytes = align_up(floats * 4, 128);
+  }
+  p.table_bytes = align_up(d->L * (int)sizeof(b200::StepLayer), 128);
+  REQUIRE(aligned16(d->layers), B200_ERR_ALIGN);
   const int max_rowbytes = kmax / 2;
   p.stage_w = align_up(2 * max_rowbytes > 16384 ? 2 * max_rowbytes : 16384, 128);
+  // attention copies whole KV pages into a stage: at least one page of K and of V must fit
+  REQUIRE(((4 * d->D) << d->log2P) <= p.stage_w, B200_ERR_SHAPE);
   int max_sz = 0;
   for (int K : Ks) {
     const int rowbytes = K / 2, ups = p.stage_w / (2 * rowbytes) > 1 ? p.stage_w / (2 * rowbytes) : 1;

@@ -4,26 +4,37 @@
 // while the same step as 225 separate launches (the reference's structure, runtime/model.py:216-233) costs ~900 us
 // of launch and pipeline-drain latency. Here one CTA per SM stays resident for the whole step:
 //
-//   * a producer warp streams this CTA's slice of every weight matrix, in the order the step consumes them, into a
-//     shared-memory ring with 1-D bulk async copies (cp.async.bulk + mbarrier transaction counts). Weights do not
-//     depend on activations, so the producer runs ahead of the computation by the depth of the ring and HBM
-//     never idles while CTAs wait for each other;
+//   * a producer warp streams this CTA's slice of every weight matrix - and, on the CTAs that do attention, the K/V
+//     pages of their head - in the order the step consumes them, into a shared-memory ring with 1-D bulk async
+//     copies (cp.async.bulk + mbarrier transaction counts). Neither weights nor cached K/V depend on this step's
+//     activations, so the producer runs ahead of the computation by the depth of the ring and HBM never idles
+//     while CTAs wait for each other;
 //   * 16 consumer warps do the arithmetic out of the ring: one warp per pair of output rows, x staged once per
-//     phase in shared memory (pre-scaled for dot_word), fp32 accumulation, warp-shuffle reduction;
+//     phase in shared memory, fp32 accumulation, warp-shuffle reduction;
 //   * CTAs exchange activation vectors through global memory WITHOUT grid barriers: every fp16 result is stored
 //     as a 32-bit word (tag << 16 | value) whose tag is this step's epoch; a consumer polls the words it needs until
 //     all carry the current tag. One store + one load crosses the chip instead of fence + atomic + poll + load.
 //     Every CTA keeps its own copy of the residual stream in shared memory and redoes the (tiny) residual add and
 //     RMSNorm, so those never touch global memory.
 //
+// Inner product without per-weight dequantization. A nibble masked in place is an fp16 SUBNORMAL: bits 0..3 of a
+// half are q * 2^-24, bits 4..7 are q * 2^-20. So (word & 0x000F000F) and (word & 0x00F000F0) are ready-made half2
+// operands; one shift by 8 exposes the other four nibbles. x is staged multiplied by 2^s (pairs under the low mask)
+// or 2^(s-4) (pairs under the high mask), s chosen per phase from max|x| so nothing overflows, which makes every
+// product q * x * 2^(s-24). With xsum = sum of x over a 32-weight chunk,
+//     sum (q - z) * scale * x = scale * (2^(24-s) * sum q x'  -  z * xsum),
+// so the zero point costs one FMA per chunk instead of one subtraction per weight: 9 integer/half2 operations per
+// 8 weights in the loop. The per-element weight this stands for is the format's dequantized weight
+// (dequant_w4a16 in gemv_w4a16.cu proves the format bit-exactly).
+//
 // Phases per layer (the reference's operator order, with the same rounding points as its fused kernels):
-//   A  resid += down[l-1] (layer 0: resid = embedding row);  xin = RMSNorm(resid) * ln1;  qkv = Wqkv xin
-//   B  attention: CTA h < n_q takes query head h: RoPE on q and k, append k, v to the paged cache, softmax(q K^T) V
-//      over the cache plus the new token
+//   A  resid += down[l-1] (layer 0: resid = embedding row);  x = RMSNorm(resid) * ln1;  qkv = Wqkv x
+//   B  attention: CTA h < n_q takes query head h: RoPE on q and k, append k, v to the paged cache, then per-warp
+//      online softmax over the cached tokens (from the ring) plus the new token, merged once across warps
 //   C  o = Wo attn
-//   D  resid += o;  xin = RMSNorm(resid) * ln2;  act = SwiGLU(Wgate xin, Wup xin)   (gate row i and up row i on one warp)
+//   D  resid += o;  x = RMSNorm(resid) * ln2;  act = SwiGLU(Wgate x, Wup x)   (gate row i and up row i on one warp)
 //   E  down = Wdown act
-// then resid += down;  xin = RMSNorm(resid) * norm_f;  logits = Whead xin;  per-CTA argmax candidates; CTA 0 merges
+// then resid += down;  x = RMSNorm(resid) * norm_f;  logits = Whead x;  per-CTA argmax candidates; CTA 0 merges
 // them (lowest index wins ties), writes tok, history[pos], pos + 1 and the new epoch.
 //
 // Every wait (mbarrier or tag poll) is bounded. A wait that runs out records a code in StepCtrl::error, raises an
@@ -43,8 +54,9 @@ constexpr int kThreads = kNT + 32;          // + producer warp
 constexpr int kMaxStages = 16;
 constexpr int kSpinLimit = 1 << 18;         // polls / try_waits before a wait gives up (tens of milliseconds)
 constexpr int kHeaderBytes = 1024;
+constexpr int kMaxKvTokens = 64;            // cached tokens per ring stage in attention (16 warps x 4 tokens)
 
-enum : int { ERR_POLL = 1, ERR_FULL = 2, ERR_EMPTY = 3, ERR_DRAIN = 4 };
+enum : int { ERR_POLL = 1, ERR_FULL = 2, ERR_EMPTY = 3 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------------
 DEVI uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -95,12 +107,9 @@ DEVI uint4 ld_poll4(const uint32_t* p) {
   asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
   return r;
 }
-DEVI uint2 ld_poll2(const uint32_t* p) {
-  uint2 r;
-  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
-  return r;
+DEVI void st_tagged(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-DEVI void st_tagged(uint32_t* p, uint32_t v) { asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 DEVI void st_tagged2(uint32_t* p, uint32_t a, uint32_t b) {
   asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }
@@ -110,10 +119,12 @@ struct Cta {
   uint64_t* full;
   uint64_t* empty;
   volatile int* abort;   // shared-memory flag, CTA-wide
-  float* red;            // kNCW + 16 floats of reduction scratch
+  float* red;            // 2 * kNCW floats of reduction scratch
   half* resid;           // [H] residual stream, private copy
-  uint4* xin;            // [Kmax / 8] activations of the running GEMV, pre-scaled for dot_word
+  uint4* xin;            // [Kmax / 8] activations of the running GEMV, scaled, 16-byte chunks swizzled (see swz)
+  float* xsum;           // [Kmax / 32] sum of the unscaled activations of each 32-weight chunk
   float* att;            // attention scratch
+  float* part;           // [rows of the largest slice][segments] partial dot products of the running GEMV
   uint8_t* ring;
   StepCtrl* ctrl;
   uint32_t tagw;         // (tag << 16)
@@ -152,49 +163,83 @@ DEVI uint2 poll4(const Cta& c, const uint32_t* p) {
   return make_uint2((v.x & 0xFFFFu) | (v.y << 16), (v.z & 0xFFFFu) | (v.w << 16));
 }
 
-DEVI float consumer_sum(const Cta& c, float v, int tid) {
-  v = warp_sum(v);
-  if ((tid & 31) == 0) c.red[tid >> 5] = v;
+// Block-wide (consumer threads) sum and max in one barrier pair.
+DEVI void consumer_sum_max(const Cta& c, float s, float m, int tid, float& s_all, float& m_all) {
+  s = warp_sum(s);
+  m = warp_max(m);
+  if ((tid & 31) == 0) { c.red[tid >> 5] = s; c.red[kNCW + (tid >> 5)] = m; }
   consumer_sync();
-  float t = 0.f;
+  float ts = 0.f, tm = 0.f;
 #pragma unroll
-  for (int k = 0; k < kNCW; ++k) t += c.red[k];
+  for (int k = 0; k < kNCW; ++k) { ts += c.red[k]; tm = fmaxf(tm, c.red[kNCW + k]); }
   consumer_sync();
-  return t;
-}
-DEVI float consumer_max(const Cta& c, float v, int tid) {
-  v = warp_max(v);
-  if ((tid & 31) == 0) c.red[tid >> 5] = v;
-  consumer_sync();
-  float t = -CUDART_INF_F;
-#pragma unroll
-  for (int k = 0; k < kNCW; ++k) t = fmaxf(t, c.red[k]);
-  consumer_sync();
-  return t;
-}
-
-// 4 activations (2 x half2) -> the pre-scaled form dot_word expects: pair 0 times 1/16, pair 1 times 1/256.
-DEVI uint2 prescale4(uint2 v) {
-  const half2 c_lo = __float2half2_rn(1.0f / 16.0f), c_hi = __float2half2_rn(1.0f / 256.0f);
-  return make_uint2(as_u32(__hmul2(as_h2(v.x), c_lo)), as_u32(__hmul2(as_h2(v.y), c_hi)));
+  s_all = ts;
+  m_all = tm;
 }
 
 // ---- x staging ---------------------------------------------------------------------------------------------------
-// xin <- prescale(E[0..n)), E tagged. n % 4 == 0.
-DEVI void stage_x_plain(const Cta& c, const uint32_t* E, int n, int tid) {
-  uint2* xo = reinterpret_cast<uint2*>(c.xin);
-  for (int g = tid; g < (n >> 2); g += kNT) xo[g] = prescale4(poll4(c, E + 4 * g));
+// 16-byte chunk ci of x lives at swz(ci): a lane of the GEMV reads the four consecutive chunks 4u..4u+3 for its
+// weight chunk u = lane, and without the swizzle those reads would be 64 bytes apart across lanes (4-way conflicts).
+DEVI int swz(int ci) { return (ci & ~3) | ((ci & 3) ^ ((ci >> 3) & 3)); }
+
+struct XScale { half2 lo, hi; float resc; };
+// Power-of-two staging scale from max|x|: x * 2^s stays below 2^15.
+DEVI XScale scale_for(float xmax) {
+  int s = 14 - ilogbf(fmaxf(xmax, 1e-30f));
+  s = max(-10, min(15, s));
+  XScale r;
+  r.lo = __float2half2_rn(exp2f((float)s));
+  r.hi = __float2half2_rn(exp2f((float)(s - 4)));
+  r.resc = exp2f((float)(24 - s));
+  return r;
+}
+
+// Store granule g (4 activations as 2 x half2, unscaled) scaled into xin and add its sum into xsum (8 granules of
+// consecutive threads make one 32-weight chunk).
+DEVI void put_granule(const Cta& c, int g, uint2 v, const XScale& sc, int tid) {
+  const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
+  float s = (a.x + a.y) + (b.x + b.y);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  if ((tid & 7) == 0) c.xsum[g >> 3] = s;
+  uint2 o;
+  o.x = as_u32(__hmul2(as_h2(v.x), sc.lo));
+  o.y = as_u32(__hmul2(as_h2(v.y), sc.hi));
+  reinterpret_cast<uint2*>(c.xin)[2 * swz(g >> 1) + (g & 1)] = o;
+}
+
+DEVI float absmax4(uint2 v) {
+  const float2 a = __half22float2(__habs2(as_h2(v.x))), b = __half22float2(__habs2(as_h2(v.y)));
+  return fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y));
+}
+
+// x <- E[0..n) (tagged). n % 32 == 0. Returns the factor that undoes the staging scale.
+DEVI float stage_x_plain(const Cta& c, const uint32_t* E, int n, int tid) {
+  uint2* raw = reinterpret_cast<uint2*>(c.xin);   // pass 1 parks the unscaled granules at their final place
+  float mx = 0.f;
+  for (int g = tid; g < (n >> 2); g += kNT) {
+    const uint2 v = poll4(c, E + 4 * g);
+    raw[2 * swz(g >> 1) + (g & 1)] = v;
+    mx = fmaxf(mx, absmax4(v));
+  }
+  float dummy, xmax;
+  consumer_sum_max(c, 0.f, mx, tid, dummy, xmax);
+  const XScale sc = scale_for(xmax);
+  for (int g = tid; g < (n >> 2); g += kNT) put_granule(c, g, raw[2 * swz(g >> 1) + (g & 1)], sc, tid);
   consumer_sync();
+  return sc.resc;
 }
 
 // resid <- resid + delta (delta tagged; or resid <- emb row when E == nullptr), then
-// xin <- prescale(w * half(float(resid) * rsqrt(mean(resid^2) + eps))).  H % 4 == 0.
-DEVI void stage_x_norm(const Cta& c, const uint32_t* E, const half* emb_row, const half* w, int H, float eps,
-                       int tid) {
+// x <- w * half(float(resid) * rsqrt(mean(resid^2) + eps)).  H % 32 == 0.
+DEVI float stage_x_norm(const Cta& c, const uint32_t* E, const half* emb_row, const half* w, int H, float eps,
+                        int tid) {
   uint2* rs = reinterpret_cast<uint2*>(c.resid);
   const uint2* wg = reinterpret_cast<const uint2*>(w);
-  float ss = 0.f;
+  float ss = 0.f, mw = 0.f;
   for (int g = tid; g < (H >> 2); g += kNT) {
+    const uint2 wv = __ldg(wg + g);   // issued before the poll: its latency hides behind the wait
     uint2 r;
     if (E) {
       const uint2 d = poll4(c, E + 4 * g);
@@ -207,10 +252,12 @@ DEVI void stage_x_norm(const Cta& c, const uint32_t* E, const half* emb_row, con
     rs[g] = r;
     const float2 a = __half22float2(as_h2(r.x)), b = __half22float2(as_h2(r.y));
     ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(b.x, b.x, fmaf(b.y, b.y, ss))));
+    mw = fmaxf(mw, absmax4(make_uint2(as_u32(__hmul2(as_h2(r.x), as_h2(wv.x))), as_u32(__hmul2(as_h2(r.y), as_h2(wv.y))))));
   }
-  const float tot = consumer_sum(c, ss, tid);
+  float tot, mwall;
+  consumer_sum_max(c, ss, mw, tid, tot, mwall);
   const float rinv = rsqrtf(tot / (float)H + eps);
-  uint2* xo = reinterpret_cast<uint2*>(c.xin);
+  const XScale sc = scale_for(mwall * rinv * 1.01f);
   for (int g = tid; g < (H >> 2); g += kNT) {
     const uint2 r = rs[g];   // this thread's own writes
     const uint2 wv = __ldg(wg + g);
@@ -218,9 +265,15 @@ DEVI void stage_x_norm(const Cta& c, const uint32_t* E, const half* emb_row, con
     uint2 o;
     o.x = as_u32(__hmul2(as_h2(wv.x), __floats2half2_rn(a.x * rinv, a.y * rinv)));
     o.y = as_u32(__hmul2(as_h2(wv.y), __floats2half2_rn(b.x * rinv, b.y * rinv)));
-    xo[g] = prescale4(o);
+    put_granule(c, g, o, sc, tid);
   }
   consumer_sync();
+  return sc.resc;
+}
+
+// One entry point for both kinds of staging (a single call site keeps a single copy of the code).
+DEVI float stage_x(const Cta& c, const uint32_t* E, const half* emb_row, const half* nw, int n, float eps, int tid) {
+  return nw ? stage_x_norm(c, E, emb_row, nw, n, eps, tid) : stage_x_plain(c, E, n, tid);
 }
 
 // ---- GEMV phase -----------------------------------------------------------------------------------------------------
@@ -274,105 +327,167 @@ DEVI void produce(const Cta& c, const Mat& m, const Slice& s, int& it, int lane)
   }
 }
 
-// Two rows against xin; returns both fp32 dot products in every lane.
-DEVI void dot_two_rows(const Cta& c, const uint4* w0, const uint4* w1, const half2* z0, const half2* z1, int U,
-                       int log2G, int lane, float& y0, float& y1) {
-  const half2 k1024 = __float2half2_rn(1024.f), k16 = __float2half2_rn(16.f), zero2 = __float2half2_rn(0.f);
-  float a0 = 0.f, a1 = 0.f;
-#pragma unroll 2
-  for (int u = lane; u < U; u += 32) {
-    const uint4 wa = w0[u], wb = w1[u];
-    const uint4 xa = c.xin[4 * u], xb = c.xin[4 * u + 1], xc = c.xin[4 * u + 2], xd = c.xin[4 * u + 3];
-    const int g = (u << 5) >> log2G;
-    const half2 sa = z0[g], sb = z1[g];
-    {
-      const half2 z2 = __half2half2(__high2half(sa));
-      const half2 zl = __hadd2(z2, k1024), zh = __hfma2(z2, k16, k1024);
-      const half2 p0 = dot_word(wa.x, xa.x, xa.y, xa.z, xa.w, zl, zh, zero2);
-      const half2 p1 = dot_word(wa.y, xb.x, xb.y, xb.z, xb.w, zl, zh, zero2);
-      const half2 p2 = dot_word(wa.z, xc.x, xc.y, xc.z, xc.w, zl, zh, zero2);
-      const half2 p3 = dot_word(wa.w, xd.x, xd.y, xd.z, xd.w, zl, zh, zero2);
-      const float2 f = __half22float2(__hadd2(__hadd2(p0, p1), __hadd2(p2, p3)));
-      a0 = fmaf(f.x + f.y, __low2float(sa), a0);
-    }
-    {
-      const half2 z2 = __half2half2(__high2half(sb));
-      const half2 zl = __hadd2(z2, k1024), zh = __hfma2(z2, k16, k1024);
-      const half2 p0 = dot_word(wb.x, xa.x, xa.y, xa.z, xa.w, zl, zh, zero2);
-      const half2 p1 = dot_word(wb.y, xb.x, xb.y, xb.z, xb.w, zl, zh, zero2);
-      const half2 p2 = dot_word(wb.z, xc.x, xc.y, xc.z, xc.w, zl, zh, zero2);
-      const half2 p3 = dot_word(wb.w, xd.x, xd.y, xd.z, xd.w, zl, zh, zero2);
-      const float2 f = __half22float2(__hadd2(__hadd2(p0, p1), __hadd2(p2, p3)));
-      a1 = fmaf(f.x + f.y, __low2float(sb), a1);
+// Cached tokens per attention ring stage: K rows in the first half of the stage, V rows in the second.
+DEVI int kv_tokens_per_stage(const StepParams& p) {
+  int t = min(kMaxKvTokens, p.stage_w / (4 * p.D));
+  return t & ~((1 << p.log2P) - 1);
+}
+
+// Producer: the cached K/V rows [0, pos) of one kv head, page by page. Whole pages are copied; rows at or beyond
+// pos in the last page are ignored by the consumer.
+DEVI void produce_kv(const Cta& c, const StepParams& p, const StepLayer& ly, int kvh, int pos, int& it, int lane) {
+  const int tps = kv_tokens_per_stage(p), pps = tps >> p.log2P;
+  const uint32_t page_bytes = (uint32_t)(p.D * 2) << p.log2P;
+  const int nst = (pos + tps - 1) / tps;
+  for (int st = 0; st < nst; ++st, ++it) {
+    const int slot = it % c.ns;
+    const uint32_t parity = ((it / c.ns) & 1) ^ 1;
+    if (!wait_bar(c, &c.empty[slot], parity, ERR_EMPTY)) return;
+    const int pg0 = st * pps, npg = min(pps, ((pos + (1 << p.log2P) - 1) >> p.log2P) - pg0);
+    uint8_t* dst = c.ring + (size_t)slot * c.stage_bytes;
+    if (lane == 0) mbar_expect_tx(&c.full[slot], 2 * npg * page_bytes);
+    __syncwarp();
+    if (lane < npg) {
+      const size_t off = ((size_t)p.bt[pg0 + lane] * p.n_kv + kvh) * page_bytes;
+      bulk_g2s(dst + lane * page_bytes, reinterpret_cast<const uint8_t*>(ly.kc) + off, page_bytes, &c.full[slot]);
+      bulk_g2s(dst + (size_t)tps * p.D * 2 + lane * page_bytes, reinterpret_cast<const uint8_t*>(ly.vc) + off,
+               page_bytes, &c.full[slot]);
     }
   }
-  y0 = warp_sum(a0) * kDotWordRescale;
-  y1 = warp_sum(a1) * kDotWordRescale;
+}
+
+// One packed word (8 weights) of each of two rows against the 8 staged activations x = (x01, x23, x45, x67).
+// Four independent half2 accumulators per row (one per nibble position): short chains, so fp16 rounding stays small
+// and the FMAs of one word do not wait on each other.
+DEVI void fma_word2(uint32_t wa, uint32_t wb, uint4 x, half2* a, half2* b) {
+  const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+  a[0] = __hfma2(as_h2(wa & 0x000F000Fu), as_h2(x.x), a[0]);
+  b[0] = __hfma2(as_h2(wb & 0x000F000Fu), as_h2(x.x), b[0]);
+  a[1] = __hfma2(as_h2(wa & 0x00F000F0u), as_h2(x.y), a[1]);
+  b[1] = __hfma2(as_h2(wb & 0x00F000F0u), as_h2(x.y), b[1]);
+  a[2] = __hfma2(as_h2(wa8 & 0x000F000Fu), as_h2(x.z), a[2]);
+  b[2] = __hfma2(as_h2(wb8 & 0x000F000Fu), as_h2(x.z), b[2]);
+  a[3] = __hfma2(as_h2(wa8 & 0x00F000F0u), as_h2(x.w), a[3]);
+  b[3] = __hfma2(as_h2(wb8 & 0x00F000F0u), as_h2(x.w), b[3]);
+}
+
+// One 32-weight chunk (u) of two rows against the staged x: this lane's share of both dot products.
+DEVI void chunk_two_rows(const Cta& c, const uint4* w0, const uint4* w1, const half2* z0, const half2* z1, int u,
+                         int log2G, float resc, float& p0, float& p1) {
+  const half2 zero2 = __float2half2_rn(0.f);
+  const uint4 wa = w0[u], wb = w1[u];
+  const int sw = (u >> 1) & 3;
+  const uint4 x0 = c.xin[4 * u + (0 ^ sw)], x1 = c.xin[4 * u + (1 ^ sw)], x2 = c.xin[4 * u + (2 ^ sw)],
+              x3 = c.xin[4 * u + (3 ^ sw)];
+  const float xs = c.xsum[u];
+  const int g = (u << 5) >> log2G;
+  const float2 sa = __half22float2(z0[g]), sb = __half22float2(z1[g]);   // (scale, zero)
+  half2 a[4] = {zero2, zero2, zero2, zero2}, b[4] = {zero2, zero2, zero2, zero2};
+  fma_word2(wa.x, wb.x, x0, a, b);
+  fma_word2(wa.y, wb.y, x1, a, b);
+  fma_word2(wa.z, wb.z, x2, a, b);
+  fma_word2(wa.w, wb.w, x3, a, b);
+  const float2 fa0 = __half22float2(__hadd2(a[0], a[2])), fa1 = __half22float2(__hadd2(a[1], a[3]));
+  const float2 fb0 = __half22float2(__hadd2(b[0], b[2])), fb1 = __half22float2(__hadd2(b[1], b[3]));
+  p0 = sa.x * fmaf((fa0.x + fa0.y) + (fa1.x + fa1.y), resc, -sa.y * xs);
+  p1 = sb.x * fmaf((fb0.x + fb0.y) + (fb1.x + fb1.y), resc, -sb.y * xs);
+}
+
+// Sum p0 over the warp and p1 over the warp with 6 shuffles instead of 10: the first exchange leaves the lower
+// half-warp holding p0 partials and the upper one p1 partials. Result: lane 0 has sum p0, lane 16 has sum p1.
+DEVI float reduce_pair(float p0, float p1, int lane) {
+  const bool up = lane & 16;
+  float v = up ? p1 : p0;
+  v += __shfl_xor_sync(0xffffffffu, up ? p0 : p1, 16);
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
 }
 
 enum : int { OUT_TAGGED = 0, OUT_SWIGLU = 1, OUT_LOGITS = 2 };
 
-// Consumer side of one matrix slice. OUT_TAGGED: E[row] <- tagged y. OUT_SWIGLU: E[i] <- tagged
-// half(silu(gate_i)) * up_i. OUT_LOGITS: logits[row] <- y, and (best, best_idx) track this warp's maximum.
-template <int OUT>
-DEVI void consume(const Cta& c, const Mat& m, const Slice& s, int log2G, int& it, uint32_t* E, half* logits,
-                  unsigned long long& best, int warp, int lane) {
-  const int U = m.K >> 5;
+// Consumer side of one matrix slice. The work of the slice is cut into tasks (unit = pair of rows, segment = 32
+// consecutive 32-weight chunks, i.e. 1024 weights of each row); tasks go round robin to the 16 warps, so even a
+// slice of a dozen rows keeps every warp busy and no warp walks a whole row alone. Per task the warp leaves two
+// partial sums in shared memory (c.part); after one barrier per slice, thread i finishes unit i: it adds the
+// segments in a fixed order (deterministic) and emits the output.
+//   OUT_TAGGED: E[row] <- tagged y.  OUT_SWIGLU: E[i] <- tagged half(silu(gate_i)) * up_i.
+//   OUT_LOGITS: logits[row] <- y, and `best` tracks this thread's maximum.
+DEVI void consume(const Cta& c, const Mat& m, const Slice& s, int log2G, float resc, int& it, const int OUT,
+                  uint32_t* E, half* logits, unsigned long long& best, int tid) {
+  const int warp = tid >> 5, lane = tid & 31;
+  const int U = m.K >> 5, segs = (U + 31) >> 5;
   for (int st = 0; st < s.nstages; ++st, ++it) {
     const int slot = it % c.ns;
     const bool ok = wait_bar(c, &c.full[slot], (it / c.ns) & 1, ERR_FULL);
     const int u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups), nu = u1 - u0;
     const uint8_t* base = c.ring + (size_t)slot * c.stage_bytes;
     if (ok) {
-      for (int j = (warp - (st * s.ups) % kNCW + kNCW) % kNCW; j < nu; j += kNCW) {   // unit -> warp round robin across stages
-        int slot0, slot1, row0, row1;
-        if (m.gu) { slot0 = j; slot1 = nu + j; row0 = u0 + j; row1 = m.N + u0 + j; }
-        else { slot0 = 2 * j; row0 = 2 * (u0 + j); row1 = row0 + 1; slot1 = row1 < m.N ? slot0 + 1 : slot0; }
-        float y0, y1;
-        dot_two_rows(c, reinterpret_cast<const uint4*>(base + (size_t)slot0 * s.rowbytes),
-                     reinterpret_cast<const uint4*>(base + (size_t)slot1 * s.rowbytes),
-                     reinterpret_cast<const half2*>(base + c.sz_off + (size_t)slot0 * s.szrow),
-                     reinterpret_cast<const half2*>(base + c.sz_off + (size_t)slot1 * s.szrow), U, log2G, lane, y0,
-                     y1);
-        if (lane == 0) {
-          const half h0 = __float2half(y0), h1 = __float2half(y1);
-          if (OUT == OUT_SWIGLU) {
-            const float gf = __half2float(h0);
-            const half sl = __float2half(gf / (1.f + expf(-gf)));
-            st_tagged(E + row0, c.tagw | (uint32_t)__half_as_ushort(__hmul(sl, h1)));
-          } else if (OUT == OUT_TAGGED) {
-            if (row1 < m.N) st_tagged2(E + row0, c.tagw | (uint32_t)__half_as_ushort(h0),
-                                       c.tagw | (uint32_t)__half_as_ushort(h1));
-            else st_tagged(E + row0, c.tagw | (uint32_t)__half_as_ushort(h0));
-          } else {
-            logits[row0] = h0;
-            if (!__hisnan(h0)) { const unsigned long long k = argmax_key(h0, row0); best = k > best ? k : best; }
-            if (row1 < m.N) {
-              logits[row1] = h1;
-              if (!__hisnan(h1)) { const unsigned long long k = argmax_key(h1, row1); best = k > best ? k : best; }
-            }
-          }
-        }
+      const int gt0 = (u0 - s.ub) * segs;   // index of this stage's first task within the slice
+      for (int t = ((warp - gt0) % kNCW + kNCW) % kNCW; t < nu * segs; t += kNCW) {
+        const int j = t / segs, k = t - j * segs, u = 32 * k + lane;
+        int slot0, slot1;
+        if (m.gu) { slot0 = j; slot1 = nu + j; }
+        else { slot0 = 2 * j; slot1 = 2 * (u0 + j) + 1 < m.N ? slot0 + 1 : slot0; }
+        float p0 = 0.f, p1 = 0.f;
+        if (u < U)
+          chunk_two_rows(c, reinterpret_cast<const uint4*>(base + (size_t)slot0 * s.rowbytes),
+                         reinterpret_cast<const uint4*>(base + (size_t)slot1 * s.rowbytes),
+                         reinterpret_cast<const half2*>(base + c.sz_off + (size_t)slot0 * s.szrow),
+                         reinterpret_cast<const half2*>(base + c.sz_off + (size_t)slot1 * s.szrow), u, log2G, resc, p0,
+                         p1);
+        const float v = reduce_pair(p0, p1, lane);
+        if ((lane & 15) == 0) c.part[((u0 - s.ub + j) * 2 + (lane >> 4)) * segs + k] = v;
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&c.empty[slot]);
   }
+  consumer_sync();
+  for (int i = tid; i < s.ue - s.ub; i += kNT) {
+    float y0 = 0.f, y1 = 0.f;
+    for (int k = 0; k < segs; ++k) { y0 += c.part[(2 * i) * segs + k]; y1 += c.part[(2 * i + 1) * segs + k]; }
+    const half h0 = __float2half(y0), h1 = __float2half(y1);
+    const int unit = s.ub + i;
+    if (OUT == OUT_SWIGLU) {
+      const float gf = __half2float(h0);
+      const half sl = __float2half(gf / (1.f + expf(-gf)));
+      st_tagged(E + unit, c.tagw | (uint32_t)__half_as_ushort(__hmul(sl, h1)));
+    } else {
+      const int row0 = 2 * unit, row1 = row0 + 1;
+      if (OUT == OUT_TAGGED) {
+        if (row1 < m.N) st_tagged2(E + row0, c.tagw | (uint32_t)__half_as_ushort(h0),
+                                   c.tagw | (uint32_t)__half_as_ushort(h1));
+        else st_tagged(E + row0, c.tagw | (uint32_t)__half_as_ushort(h0));
+      } else {
+        logits[row0] = h0;
+        if (!__hisnan(h0)) { const unsigned long long key = argmax_key(h0, row0); best = key > best ? key : best; }
+        if (row1 < m.N) {
+          logits[row1] = h1;
+          if (!__hisnan(h1)) { const unsigned long long key = argmax_key(h1, row1); best = key > best ? key : best; }
+        }
+      }
+    }
+  }
 }
 
 // ---- attention for one query head -------------------------------------------------------------------------------------
-// All consumer threads of the CTA. q, k, v of this step come from the tagged qkv exchange; tokens 0..pos-1 from the cache.
+// All consumer threads of the CTA. q, k, v of this step come from the tagged qkv exchange, tokens 0..pos-1 from ring
+// stages filled by produce_kv. Lane (t = lane >> 3, c = lane & 7) of warp w owns token slot 4 w + t of a stage and
+// dims [c D/8, (c+1) D/8) of it; each warp keeps a private online-softmax state, merged once at the end.
 template <int D>
 DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly, const uint32_t* Eqkv, uint32_t* Eattn,
-                         int h, int pos, int tid) {
-  constexpr int D2 = D / 2, G4 = D / 4;
+                         int h, int pos, float cs, float sn, int page_new, int& it, int tid) {
+  constexpr int D2 = D / 2, G4 = D / 4, DPL = D / 8;
+  const int warp = tid >> 5, lane = tid & 31, ts = lane >> 3, ch = lane & 7;
   const int hpg = p.n_q / p.n_kv, kvh = h / hpg;
-  float* qf = c.att;                       // [D] rotated q * scale
-  half* knew = reinterpret_cast<half*>(c.att + D);        // [D] rotated k of this step
-  half* vnew = knew + D;                                   // [D]
-  half* raw = vnew + D;                                    // [3 D] un-rotated q, k, v
-  float* part = c.att + 4 * D;             // [NTG][D] partial outputs
-  float* sc = part + (kNT / D2) * D;       // [ctx] scores, then probabilities
+  float* qf = c.att;                                         // [D] rotated q * 1/sqrt(D)
+  half* knew = reinterpret_cast<half*>(c.att + D);           // [D] rotated k of this step
+  half* vnew = knew + D;                                     // [D]
+  half* raw = vnew + D;                                      // [3 D] un-rotated q, k, v
+  float* wo = c.att + 4 * D;                                 // [kNCW][D] per-warp outputs
+  float* wm = wo + kNCW * D;                                 // [kNCW] per-warp max
+  float* wl = wm + kNCW;                                     // [kNCW] per-warp sum
   const int pmask = (1 << p.log2P) - 1;
 
   if (tid < 3 * G4) {
@@ -381,80 +496,111 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
     reinterpret_cast<uint2*>(raw)[tid] = poll4(c, Eqkv + (size_t)head * D + 4 * g);
   }
   consumer_sync();
-  const int page_new = p.bt[pos >> p.log2P], slot_new = pos & pmask;
-  if (tid < D) {
-    const int i = tid % D2;
-    const float cs = p.cos_t[(size_t)pos * D2 + i], sn = p.sin_t[(size_t)pos * D2 + i];
-    const half* src = raw + (tid < D2 ? 0 : D);           // threads [0, D2): q pair i; [D2, D): k pair i
-    const float a = __half2float(src[i]), b = __half2float(src[i + D2]);
-    const half ra = __float2half(a * cs - b * sn), rb = __float2half(b * cs + a * sn);
-    if (tid < D2) {
-      const float scale = rsqrtf((float)D);
-      qf[i] = __half2float(ra) * scale;
-      qf[i + D2] = __half2float(rb) * scale;
+  if (tid < 2 * D) {
+    const int slot_new = pos & pmask;
+    const size_t row_new = ((((size_t)page_new * p.n_kv + kvh) << p.log2P) + slot_new) * D;
+    if (tid < D) {
+      const int i = tid % D2;
+      const half* src = raw + (tid < D2 ? 0 : D);           // threads [0, D2): q pair i; [D2, D): k pair i
+      const float a = __half2float(src[i]), b = __half2float(src[i + D2]);
+      const half ra = __float2half(a * cs - b * sn), rb = __float2half(b * cs + a * sn);
+      if (tid < D2) {
+        const float scale = rsqrtf((float)D);
+        qf[i] = __half2float(ra) * scale;
+        qf[i + D2] = __half2float(rb) * scale;
+      } else {
+        knew[i] = ra;
+        knew[i + D2] = rb;
+        if (h % hpg == 0) { ly.kc[row_new + i] = ra; ly.kc[row_new + i + D2] = rb; }
+      }
     } else {
-      knew[i] = ra;
-      knew[i + D2] = rb;
-      if (h % hpg == 0) {
-        half* dst = ly.kc + ((((size_t)page_new * p.n_kv + kvh) << p.log2P) + slot_new) * D;
-        dst[i] = ra;
-        dst[i + D2] = rb;
+      const int i = tid - D;
+      const half v = raw[2 * D + i];
+      vnew[i] = v;
+      if (h % hpg == 0) ly.vc[row_new + i] = v;
+    }
+  }
+  consumer_sync();
+
+  float qreg[DPL];
+#pragma unroll
+  for (int d = 0; d < DPL; ++d) qreg[d] = qf[ch * DPL + d];
+  float m = -CUDART_INF_F, l = 0.f, acc[DPL];
+#pragma unroll
+  for (int d = 0; d < DPL; ++d) acc[d] = 0.f;
+
+  // fold one token (K row kp, V row vp, both this lane's DPL dims) into the warp's state; `valid` per token slot
+  auto fold = [&](const half* kp, const half* vp, bool valid) {
+    float kf[DPL], s = 0.f;
+#pragma unroll
+    for (int d8 = 0; d8 < DPL; d8 += 8) unpack8(*reinterpret_cast<const uint4*>(kp + d8), kf + d8);
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) s = fmaf(kf[d], qreg[d], s);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    s = valid ? s : -CUDART_INF_F;
+    float mw = fmaxf(s, __shfl_xor_sync(0xffffffffu, s, 8));
+    mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, 16));
+    const float mn = fmaxf(m, mw);
+    if (mn == -CUDART_INF_F) return;           // nothing valid yet in this warp (warp-uniform)
+    const float alpha = __expf(m - mn), pr = __expf(s - mn);
+    m = mn;
+    l = l * alpha + pr;
+    float vf[DPL];
+#pragma unroll
+    for (int d8 = 0; d8 < DPL; d8 += 8) unpack8(*reinterpret_cast<const uint4*>(vp + d8), vf + d8);
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc[d] = fmaf(pr, vf[d], acc[d] * alpha);
+  };
+
+  const int tps = kv_tokens_per_stage(p);
+  const int nst = (pos + tps - 1) / tps;
+  for (int st = 0; st < nst; ++st, ++it) {
+    const int slot = it % c.ns;
+    const bool ok = wait_bar(c, &c.full[slot], (it / c.ns) & 1, ERR_FULL);
+    const half* kbase = reinterpret_cast<const half*>(c.ring + (size_t)slot * c.stage_bytes);
+    const half* vbase = kbase + (size_t)tps * D;
+    const int nt = min(tps, pos - st * tps);
+    if (ok) {
+      for (int j0 = 4 * warp; j0 < nt; j0 += 4 * kNCW) {
+        const int j = j0 + ts;
+        const int jj = min(j, nt - 1);
+        fold(kbase + (size_t)jj * D + ch * DPL, vbase + (size_t)jj * D + ch * DPL, j < nt);
       }
     }
-  } else if (tid < 2 * D) {
-    const int i = tid - D;
-    const half v = raw[2 * D + i];
-    vnew[i] = v;
-    if (h % hpg == 0) ly.vc[((((size_t)page_new * p.n_kv + kvh) << p.log2P) + slot_new) * D + i] = v;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&c.empty[slot]);
   }
-  consumer_sync();
+  if (warp == 0) fold(knew + ch * DPL, vnew + ch * DPL, ts == 0);   // the token of this step
 
-  // scores: one token per thread
-  float mx = -CUDART_INF_F;
-  for (int t = tid; t <= pos; t += kNT) {
-    const uint4* kp = t == pos ? reinterpret_cast<const uint4*>(knew)
-                               : reinterpret_cast<const uint4*>(
-                                     ly.kc + ((((size_t)p.bt[t >> p.log2P] * p.n_kv + kvh) << p.log2P) + (t & pmask)) * D);
-    float s = 0.f;
+  // merge: token slots inside the warp, then the warps
+  float lw = l;
+  lw += __shfl_xor_sync(0xffffffffu, lw, 8);
+  lw += __shfl_xor_sync(0xffffffffu, lw, 16);
 #pragma unroll
-    for (int ch = 0; ch < D / 8; ++ch) {
-      float kf[8];
-      unpack8(kp[ch], kf);
-      const float4 qa = *reinterpret_cast<const float4*>(qf + 8 * ch), qb = *reinterpret_cast<const float4*>(qf + 8 * ch + 4);
-      s = fmaf(kf[0], qa.x, fmaf(kf[1], qa.y, fmaf(kf[2], qa.z, fmaf(kf[3], qa.w, s))));
-      s = fmaf(kf[4], qb.x, fmaf(kf[5], qb.y, fmaf(kf[6], qb.z, fmaf(kf[7], qb.w, s))));
-    }
-    sc[t] = s;
-    mx = fmaxf(mx, s);
+  for (int d = 0; d < DPL; ++d) {
+    acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 8);
+    acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 16);
   }
-  const float M = consumer_max(c, mx, tid);
-  float ls = 0.f;
-  for (int t = tid; t <= pos; t += kNT) {
-    const float e = __expf(sc[t] - M);
-    sc[t] = e;
-    ls += e;
+  if (ts == 0) {
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) wo[warp * D + ch * DPL + d] = acc[d];
+    if (ch == 0) { wm[warp] = m; wl[warp] = lw; }
   }
-  const float Lsum = consumer_sum(c, ls, tid);   // its barriers also publish sc[]
-
-  // output: thread (token group tg, dim pair dp)
-  constexpr int NTG = kNT / D2;
-  const int dp = tid % D2, tg = tid / D2;
-  float o0 = 0.f, o1 = 0.f;
-  for (int t = tg; t <= pos; t += NTG) {
-    const half* vp = t == pos ? vnew : ly.vc + ((((size_t)p.bt[t >> p.log2P] * p.n_kv + kvh) << p.log2P) + (t & pmask)) * D;
-    const float2 vf = __half22float2(*reinterpret_cast<const half2*>(vp + 2 * dp));
-    const float pr = sc[t];
-    o0 = fmaf(pr, vf.x, o0);
-    o1 = fmaf(pr, vf.y, o1);
-  }
-  part[tg * D + 2 * dp] = o0;
-  part[tg * D + 2 * dp + 1] = o1;
   consumer_sync();
   if (tid < D) {
-    float o = 0.f;
+    float M = -CUDART_INF_F;
 #pragma unroll
-    for (int k = 0; k < NTG; ++k) o += part[k * D + tid];
-    st_tagged(Eattn + (size_t)h * D + tid, c.tagw | (uint32_t)__half_as_ushort(__float2half(o / Lsum)));
+    for (int w = 0; w < kNCW; ++w) M = fmaxf(M, wm[w]);
+    float o = 0.f, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < kNCW; ++w) {
+      const float a = __expf(wm[w] - M);   // a warp that saw no token: e^(-inf) = 0
+      o = fmaf(a, wo[w * D + tid], o);
+      L = fmaf(a, wl[w], L);
+    }
+    st_tagged(Eattn + (size_t)h * D + tid, c.tagw | (uint32_t)__half_as_ushort(__float2half(o / L)));
   }
   consumer_sync();
 }
@@ -462,6 +608,7 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
 }  // namespace
 
 // ---- the kernel ------------------------------------------------------------------------------------------------------
+template <int D>
 __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_constant__ StepParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   Cta c;
@@ -471,8 +618,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   c.red = reinterpret_cast<float*>(smem + 2 * kMaxStages * 8 + 16);
   c.resid = reinterpret_cast<half*>(smem + kHeaderBytes);
   c.xin = reinterpret_cast<uint4*>(smem + kHeaderBytes + p.resid_bytes);
-  c.att = reinterpret_cast<float*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes);
-  c.ring = smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.att_bytes;
+  c.xsum = reinterpret_cast<float*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes);
+  c.att = reinterpret_cast<float*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes);
+  c.part = reinterpret_cast<float*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes + p.att_bytes);
+  // the per-layer pointer table, copied once from global memory: every phase starts from these pointers, and a
+  // global load in front of each would put an L2 round trip on the critical path ~10 times per layer
+  StepLayer* lys = reinterpret_cast<StepLayer*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes +
+                                                p.att_bytes + p.part_bytes);
+  c.ring = smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes + p.att_bytes + p.part_bytes + p.table_bytes;
   c.ctrl = p.ctrl;
   c.ns = p.ns;
   c.stage_bytes = p.stage_bytes;
@@ -485,9 +638,16 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     *c.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(p.layers);
+    uint4* dst = reinterpret_cast<uint4*>(lys);
+    for (int i = tid; i < p.L * (int)(sizeof(StepLayer) / 16); i += kThreads) dst[i] = __ldg(src + i);
+  }
   __syncthreads();
   const uint32_t epoch = ((volatile StepCtrl*)p.ctrl)->epoch + 1u;
   c.tagw = ((epoch % 65535u) + 1u) << 16;
+  const int pos = p.pos[0];
+  const int hpg = p.n_q / p.n_kv;
 
   const int n_qkv = (p.n_q + 2 * p.n_kv) * p.D, n_att = p.n_q * p.D;
   const int per_layer = n_qkv + n_att + p.H + p.I + p.H;   // exchange words per layer
@@ -496,20 +656,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     // ================= producer =================
     int it = 0;
     for (int l = 0; l < p.L && !*c.abort; ++l) {
-      const StepLayer& ly = p.layers[l];
+      const StepLayer& ly = lys[l];
       const Mat mats[4] = {{(const uint8_t*)ly.w[0], (const uint8_t*)ly.sz[0], n_qkv, p.H, 0},
                            {(const uint8_t*)ly.w[1], (const uint8_t*)ly.sz[1], p.H, n_att, 0},
                            {(const uint8_t*)ly.w[2], (const uint8_t*)ly.sz[2], p.I, p.H, 1},
                            {(const uint8_t*)ly.w[3], (const uint8_t*)ly.sz[3], p.H, p.I, 0}};
+      produce(c, mats[0], slice_of(mats[0], p.log2G, p.stage_w, cta, ncta), it, lane);
+      for (int h = cta; h < p.n_q && !*c.abort; h += ncta) produce_kv(c, p, ly, h / hpg, pos, it, lane);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) produce(c, mats[k], slice_of(mats[k], p.log2G, p.stage_w, cta, ncta), it, lane);
+      for (int k = 1; k < 4; ++k)
+        if (!*c.abort) produce(c, mats[k], slice_of(mats[k], p.log2G, p.stage_w, cta, ncta), it, lane);
     }
     if (!*c.abort) {
       const Mat head = {(const uint8_t*)p.w_head, (const uint8_t*)p.sz_head, p.V, p.H, 0};
       produce(c, head, slice_of(head, p.log2G, p.stage_w, cta, ncta), it, lane);
     }
-    // Leave only when every copy issued has landed: a stage is either consumed (its empty barrier completes) or,
-    // if the consumers stopped, still full; waiting on the full barriers of the last `ns` stages covers both.
+    // Leave only when every copy issued has landed. On the normal path the consumers have waited on every full
+    // barrier already; on abort, wait (bounded) for the full barriers of the stages still in the ring.
     if (*c.abort) {
       for (int k = max(0, it - c.ns); k < it; ++k) {
         const int slot = k % c.ns;
@@ -521,62 +684,91 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   }
 
   // ================= consumers =================
+  long long* tr = p.trace ? p.trace + (size_t)cta * (16 + 16 * p.L) : nullptr;
+  int tri = 0;
+#define TRACE()                                              \
+  do {                                                       \
+    if (tr && tid == 0) {                                    \
+      long long t_;                                          \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+      tr[tri++] = t_;                                        \
+    }                                                        \
+  } while (0)
+  TRACE();
   int it = 0;
   unsigned long long best = 0ull;
-  const int pos = p.pos[0];
   const half* emb_row = p.emb + (size_t)p.tok[0] * p.H;
-  for (int l = 0; l < p.L; ++l) {
-    const StepLayer& ly = p.layers[l];
+  // RoPE factors and the page of this step's token depend only on pos: fetch them now, off the critical path
+  float rope_c = 0.f, rope_s = 0.f;
+  int page_new = 0;
+  if (cta < p.n_q) {
+    page_new = p.bt[pos >> p.log2P];
+    if (tid < p.D) {
+      rope_c = p.cos_t[(size_t)pos * (p.D >> 1) + tid % (p.D >> 1)];
+      rope_s = p.sin_t[(size_t)pos * (p.D >> 1) + tid % (p.D >> 1)];
+    }
+  }
+  // One loop body serves every GEMV of the step (4 per layer, then the LM head as "phase 0 of layer L"): the kernel
+  // keeps a single copy of the staging, GEMV and attention code, which keeps the loop inside the instruction cache.
+  const Mat head = {(const uint8_t*)p.w_head, (const uint8_t*)p.sz_head, p.V, p.H, 0};
+#pragma unroll 1
+  for (int step = 0; step <= 4 * p.L; ++step) {
+    const int l = step >> 2, ph = step & 3;
+    const bool is_head = l == p.L;
+    const StepLayer& ly = lys[is_head ? 0 : l];
     uint32_t* E = p.xchg + (size_t)l * per_layer;
     uint32_t *Eqkv = E, *Eatt = E + n_qkv, *Eo = Eatt + n_att, *Eact = Eo + p.H, *Edown = Eact + p.I;
-    const Mat m_qkv = {(const uint8_t*)ly.w[0], (const uint8_t*)ly.sz[0], n_qkv, p.H, 0};
-    const Mat m_o = {(const uint8_t*)ly.w[1], (const uint8_t*)ly.sz[1], p.H, n_att, 0};
-    const Mat m_gu = {(const uint8_t*)ly.w[2], (const uint8_t*)ly.sz[2], p.I, p.H, 1};
-    const Mat m_dn = {(const uint8_t*)ly.w[3], (const uint8_t*)ly.sz[3], p.H, p.I, 0};
-
-    // A
-    stage_x_norm(c, l == 0 ? nullptr : p.xchg + (size_t)(l - 1) * per_layer + (per_layer - p.H), emb_row, ly.ln1, p.H,
-                 p.eps, tid);
-    if (consumer_sync_or(*c.abort)) return;
-    consume<OUT_TAGGED>(c, m_qkv, slice_of(m_qkv, p.log2G, p.stage_w, cta, ncta), p.log2G, it, Eqkv, nullptr, best,
-                        warp, lane);
-    if (consumer_sync_or(*c.abort)) return;
-    // B
-    for (int h = cta; h < p.n_q; h += ncta) {
-      if (p.D == 64) attention_head<64>(c, p, ly, Eqkv, Eatt, h, pos, tid);
-      else attention_head<128>(c, p, ly, Eqkv, Eatt, h, pos, tid);
-      if (consumer_sync_or(*c.abort)) return;
+    Mat m;
+    const uint32_t* Ein;
+    const half* nw = nullptr;   // norm weight: non-null selects "residual add + RMSNorm" staging
+    uint32_t* Eout;
+    int out = OUT_TAGGED, n_in = p.H;
+    if (ph == 0) {
+      Ein = l == 0 ? nullptr : E - p.H;   // down of the previous layer: the last H words of its block
+      nw = is_head ? p.norm_f : ly.ln1;
+      m = is_head ? head : Mat{(const uint8_t*)ly.w[0], (const uint8_t*)ly.sz[0], n_qkv, p.H, 0};
+      Eout = Eqkv;
+      out = is_head ? OUT_LOGITS : OUT_TAGGED;
+    } else if (ph == 1) {
+      Ein = Eatt; n_in = n_att;
+      m = Mat{(const uint8_t*)ly.w[1], (const uint8_t*)ly.sz[1], p.H, n_att, 0};
+      Eout = Eo;
+    } else if (ph == 2) {
+      Ein = Eo; nw = ly.ln2;
+      m = Mat{(const uint8_t*)ly.w[2], (const uint8_t*)ly.sz[2], p.I, p.H, 1};
+      Eout = Eact; out = OUT_SWIGLU;
+    } else {
+      Ein = Eact; n_in = p.I;
+      m = Mat{(const uint8_t*)ly.w[3], (const uint8_t*)ly.sz[3], p.H, p.I, 0};
+      Eout = Edown;
     }
-    // C
-    stage_x_plain(c, Eatt, n_att, tid);
+    const float resc = stage_x(c, Ein, emb_row, nw, n_in, p.eps, tid);
+    TRACE();
+    consume(c, m, slice_of(m, p.log2G, p.stage_w, cta, ncta), p.log2G, resc, it, out, Eout, p.logits, best, tid);
+    if (is_head) break;
     if (consumer_sync_or(*c.abort)) return;
-    consume<OUT_TAGGED>(c, m_o, slice_of(m_o, p.log2G, p.stage_w, cta, ncta), p.log2G, it, Eo, nullptr, best, warp,
-                        lane);
-    if (consumer_sync_or(*c.abort)) return;
-    // D
-    stage_x_norm(c, Eo, nullptr, ly.ln2, p.H, p.eps, tid);
-    if (consumer_sync_or(*c.abort)) return;
-    consume<OUT_SWIGLU>(c, m_gu, slice_of(m_gu, p.log2G, p.stage_w, cta, ncta), p.log2G, it, Eact, nullptr, best, warp,
-                        lane);
-    if (consumer_sync_or(*c.abort)) return;
-    // E
-    stage_x_plain(c, Eact, p.I, tid);
-    if (consumer_sync_or(*c.abort)) return;
-    consume<OUT_TAGGED>(c, m_dn, slice_of(m_dn, p.log2G, p.stage_w, cta, ncta), p.log2G, it, Edown, nullptr, best,
-                        warp, lane);
-    if (consumer_sync_or(*c.abort)) return;
+    TRACE();
+    if (ph == 0) {
+      for (int h = cta; h < p.n_q; h += ncta) {
+        attention_head<D>(c, p, ly, Eqkv, Eatt, h, pos, rope_c, rope_s, page_new, it, tid);
+        if (consumer_sync_or(*c.abort)) return;
+      }
+      TRACE();
+    }
   }
-  // final norm, LM head, argmax
-  stage_x_norm(c, p.xchg + (size_t)(p.L - 1) * per_layer + (per_layer - p.H), nullptr, p.norm_f, p.H, p.eps, tid);
-  if (consumer_sync_or(*c.abort)) return;
-  const Mat head = {(const uint8_t*)p.w_head, (const uint8_t*)p.sz_head, p.V, p.H, 0};
-  consume<OUT_LOGITS>(c, head, slice_of(head, p.log2G, p.stage_w, cta, ncta), p.log2G, it, nullptr, p.logits, best,
-                      warp, lane);
-  // this CTA's candidate: max over its warps' lane-0 keys
+  // this CTA's candidate: max over its threads' keys
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(c.att);
+  {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+  }
   if (lane == 0) keys[warp] = best;
   if (consumer_sync_or(*c.abort)) return;
-  uint32_t* Earg = p.xchg + (size_t)p.L * per_layer;   // [ncta][4] words: (tag|idx lo16, tag|idx hi16, tag|value, tag)
+  TRACE();
+  uint32_t* Earg = p.xchg + (size_t)p.L * per_layer;   // [ncta][4] words: idx low 16, idx high 16, value key, valid
   if (tid == 0) {
     unsigned long long b = 0ull;
     for (int k = 0; k < kNCW; ++k) b = keys[k] > b ? keys[k] : b;
@@ -589,7 +781,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   if (cta == 0) {
     unsigned long long b = 0ull;
     for (int k = tid; k < ncta; k += kNT) {
-      const uint2 v = poll4(c, Earg + 4 * k);   // halves: idx lo, idx hi, value key, valid
+      const uint2 v = poll4(c, Earg + 4 * k);
       const uint32_t idx = v.x, val = v.y & 0xFFFFu, valid = v.y >> 16;
       if (valid) {
         const unsigned long long key = ((unsigned long long)val << 32) | (uint32_t)(0x7FFFFFFFu - idx);
@@ -610,23 +802,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
       if (p.history) p.history[pos] = t;
       p.pos[0] = pos + 1;
       p.ctrl->epoch = epoch;
+      TRACE();
     }
   }
+#undef TRACE
 }
 
 size_t decode_step_smem_fixed(const StepParams& p) {
-  return (size_t)kHeaderBytes + p.resid_bytes + p.xin_bytes + p.att_bytes;
+  return (size_t)kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes + p.att_bytes + p.part_bytes + p.table_bytes;
 }
 int decode_step_threads() { return kThreads; }
 int decode_step_max_stages() { return kMaxStages; }
-int decode_step_consumer_threads() { return kNT; }
+int decode_step_consumer_warps() { return kNCW; }
 
 cudaError_t decode_step_launch(const StepParams& p, int grid, size_t smem, cudaStream_t st) {
   static int configured_for = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_for != dev) {
-    cudaError_t e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(decode_step_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(decode_step_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     configured_for = dev;
   }
@@ -640,7 +836,8 @@ cudaError_t decode_step_launch(const StepParams& p, int grid, size_t smem, cudaS
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, decode_step_kernel, p);
+  return p.D == 64 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<64>, p)
+                   : cudaLaunchKernelEx(&cfg, decode_step_kernel<128>, p);
 }
 
 }  // namespace b200

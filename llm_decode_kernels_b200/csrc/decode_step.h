@@ -42,14 +42,15 @@ struct StepParams {
   half* logits;
   uint32_t* xchg;
   StepCtrl* ctrl;
+  long long* trace;   // optional [grid][16 + 16 L] phase timestamps (ns)
   // shared-memory plan, computed on the host
-  int resid_bytes, xin_bytes, att_bytes, stage_w, stage_bytes, ns;
+  int resid_bytes, xin_bytes, xsum_bytes, att_bytes, part_bytes, table_bytes, stage_w, stage_bytes, ns;
 };
 
 size_t decode_step_smem_fixed(const StepParams& p);
 int decode_step_threads();
 int decode_step_max_stages();
-int decode_step_consumer_threads();
+int decode_step_consumer_warps();
 cudaError_t decode_step_launch(const StepParams& p, int grid, size_t smem, cudaStream_t st);
 
 }  // namespace b200

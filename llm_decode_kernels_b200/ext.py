@@ -55,7 +55,7 @@ class StepDesc(ctypes.Structure):
                 ("D", c_int), ("V", c_int), ("log2G", c_int), ("log2P", c_int), ("eps", c_float), ("emb", c_void_p),
                 ("norm_f", c_void_p), ("w_head", c_void_p), ("sz_head", c_void_p), ("cos_t", c_void_p),
                 ("sin_t", c_void_p), ("bt", c_void_p), ("tok", c_void_p), ("pos", c_void_p), ("history", c_void_p),
-                ("logits", c_void_p), ("xchg", c_void_p), ("ctrl", c_void_p), ("ctx_cap", c_int), ("grid", c_int)]
+                ("logits", c_void_p), ("xchg", c_void_p), ("ctrl", c_void_p), ("ctx_cap", c_int), ("grid", c_int), ("trace", c_void_p)]
 
 
 def load_library(build_if_missing=True):

@@ -186,7 +186,7 @@ class Model:
         import ctypes
         mode = self.cfg.step_kernel
         G = self.cfg.group
-        fits = all(k % 32 == 0 and k % G == 0 and (k // G) % 4 == 0 for k in (self.H, self.n_q * self.D, self.I))
+        fits = all(k % 128 == 0 and k % G == 0 and (k // G) % 4 == 0 for k in (self.H, self.n_q * self.D, self.I))
         self.persistent = mode == "persistent" or (mode == "auto" and self.cfg.fused and fits
                                                    and self.ctx_cap <= PERSISTENT_MAX_CTX)
         if mode == "persistent" and not fits:

@@ -7,7 +7,7 @@
 gemv: `copies` distinct quantized matrices (together larger than the 126 MB L2) are multiplied in turn, so every
       launch streams its weights from HBM. attn: batched paged attention over a KV pool larger than L2.
 step: a TinyLlama-shape decoder cut to `layers` layers decodes a few tokens eagerly (no graph), so every kernel of
-      the decode step shows up as its own launch. Everything is a few hundred MB on the device and ends in seconds.
+      the decode step shows up as its own launch (--step-kernel persistent: one decode_step_kernel launch per token). Everything is a few hundred MB on the device and ends in seconds.
 """
 import argparse
 
@@ -56,7 +56,7 @@ def probe_step(a):
     from .model import DecodeConfig, Model
     from .shapes import TINYLLAMA, config, random_llama_state
     c = config(TINYLLAMA, num_hidden_layers=a.layers)
-    m = Model(random_llama_state(c, "cuda", 0), c, DecodeConfig(max_ctx=256, seed=0))
+    m = Model(random_llama_state(c, "cuda", 0), c, DecodeConfig(max_ctx=256, seed=0, step_kernel=a.step_kernel))
     m.prepare(256, use_graph=False)
     m.reset(0)
     m.teacher_force(list(range(1, a.tokens + 1)), use_graph=False)
@@ -76,5 +76,6 @@ if __name__ == "__main__":
     ap.add_argument("--part", type=int, default=256)
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--tokens", type=int, default=4)
+    ap.add_argument("--step-kernel", default="multi", choices=["multi", "persistent"])
     a = ap.parse_args()
     {"gemv": probe_gemv, "attn": probe_attn, "step": probe_step}[a.op](a)
