@@ -75,6 +75,11 @@ int b200_rope_append(void* qkv, const float* cos_t, const float* sin_t, const in
 
 /* ---- additions: no counterpart among the reference's launchers ---- */
 
+/* Like b200_bw_read, but through the path the persistent step kernel uses: each of `blocks` CTAs streams its share
+ * of the buffer into a shared-memory ring of `stages` x `stage_bytes` with 1-D bulk async copies. stage_bytes a
+ * multiple of 128, stage_bytes * stages <= 226 KB. *sink becomes 0xdead000x if a bounded wait inside gives up. */
+int b200_bw_read_bulk(const void* p, size_t bytes, void* sink, int blocks, int stage_bytes, int stages, void* stream);
+
 /* Batched, head_dim-generic form of b200_paged_attention. q [B, n_q, D]; bt int32 [B, bt_stride]; pos int32 [B];
  * o_part [B, n_q, max_splits, D]; m_part, l_part [B, n_q, max_splits]; out [B, n_q, D]. D in {64, 128}.
  * The reference's Python binding hard-wires B = 1 and D = 64 (kernels/bindings.cpp:49-52). */
@@ -108,11 +113,11 @@ int b200_argmax(const void* logits, int V, long long* tok, int* pos, long long* 
  * `grid` CTAs (one per SM); weights stream through shared-memory rings, CTAs exchange activations through `xchg`.
  * The reference has no such entry point: there the step is ~225 launches issued from Python. */
 
-/* One decoder layer. An array of L of these lives in DEVICE memory. Matrix order in w[] / sz[]:
+/* One decoder layer. An array of L of these lives in DEVICE memory. Matrix order in w[]:
  * 0 = [q;k;v] ((n_q + 2 n_kv) D x H), 1 = o (H x n_q D), 2 = [gate;up] (2I x H), 3 = down (H x I). */
 typedef struct b200_step_layer {
-  const void* w[4];  /* packed int32 [N, K/8] */
-  const void* sz[4]; /* half2 (scale, zero) [N, K/G] */
+  const void* w[4];  /* the matrix in stream layout, made by b200_decode_step_repack (same size as packed + sz) */
+  const void* sz[4]; /* unused (the stream layout carries scale/zero); set to NULL */
   const void* ln1;   /* fp16 [H] */
   const void* ln2;   /* fp16 [H] */
   void* kc;          /* fp16 [pages, n_kv, P, D] */
@@ -126,8 +131,8 @@ typedef struct b200_step_desc {
   float eps;
   const void* emb;     /* fp16 [vocab, H] */
   const void* norm_f;  /* fp16 [H] */
-  const void* w_head;  /* packed [V, H/8] */
-  const void* sz_head; /* half2 [V, H/G] */
+  const void* w_head;  /* LM head [V, H] in stream layout (b200_decode_step_repack) */
+  const void* sz_head; /* unused; NULL */
   const float* cos_t;  /* fp32 [max_pos, D/2] */
   const float* sin_t;
   const int* bt;       /* int32 block table of the sequence */
@@ -141,6 +146,15 @@ typedef struct b200_step_desc {
   int grid;            /* CTAs = SMs of the device */
   long long* trace;    /* NULL, or int64 [grid, 16 + 16 L]: per-CTA globaltimer (ns) at every phase boundary */
 } b200_step_desc;
+
+/* Rearrange one quantized matrix for the step kernel ("stream layout"): out (N * (K/2 + 4 K/G) bytes, 16B) receives,
+ * CTA slice after CTA slice and ring stage after ring stage, each stage's packed rows followed by their (scale, zero)
+ * rows, so that the kernel's producer fetches a stage with ONE bulk copy. Wp int32 [N, K/8], SZ half2 [N, K/G] are
+ * the quantizer's tensors and are not modified. gate_up != 0: the matrix is [gate; up] (N = 2I rows) and row i is
+ * paired with row I + i. kmax = max(H, n_q D, I) of the model and grid = the CTA count b200_decode_step will be
+ * launched with; both fix the stage size and must match the launch. K % 128 == 0 and (K/G) % 4 == 0. */
+int b200_decode_step_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up, int kmax,
+                            int grid, void* stream);
 
 /* Bytes of exchange memory a step of these dimensions needs. */
 size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D, int grid);

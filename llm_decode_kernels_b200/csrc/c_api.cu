@@ -22,6 +22,10 @@ cudaError_t argmax_dispatch(const void* logits, int V, long long* tok, int* pos,
                             cudaStream_t st);
 cudaError_t bw_read_dispatch(const void* p, size_t bytes, void* sink, int blocks, int threads, int unroll,
                              cudaStream_t st);
+cudaError_t bw_read_bulk_dispatch(const void* p, size_t bytes, void* sink, int blocks, int stage_bytes, int stages,
+                                  cudaStream_t st);
+cudaError_t repack_stream_dispatch(const void* W, const void* SZ, void* out, int N, int K, int log2G, int gu, int ncta,
+                                   int stage_w, cudaStream_t st);
 cudaError_t paged_attention_dispatch(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
                                      const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS,
                                      int max_splits, float* o_part, float* m_part, float* l_part, void* out,
@@ -79,6 +83,14 @@ int b200_bw_read(const void* p, size_t bytes, void* sink, int blocks, int thread
   REQUIRE(p && sink && bytes >= 16 && blocks > 0 && threads > 0 && threads <= 1024, B200_ERR_ARG);
   REQUIRE(aligned16(p), B200_ERR_ALIGN);
   return finish(b200::bw_read_dispatch(p, bytes, sink, blocks, threads, unroll, S(stream)));
+}
+
+int b200_bw_read_bulk(const void* p, size_t bytes, void* sink, int blocks, int stage_bytes, int stages, void* stream) {
+  REQUIRE(p && sink && blocks > 0 && stage_bytes >= 1024 && stages >= 2 && stages <= 32, B200_ERR_ARG);
+  REQUIRE(stage_bytes % 128 == 0 && (size_t)stage_bytes * stages + 512 <= 227 * 1024, B200_ERR_SHAPE);
+  REQUIRE(bytes >= (size_t)stage_bytes * blocks, B200_ERR_ARG);
+  REQUIRE(aligned16(p), B200_ERR_ALIGN);
+  return finish(b200::bw_read_bulk_dispatch(p, bytes, sink, blocks, stage_bytes, stages, S(stream)));
 }
 
 int b200_paged_attention_batched(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
@@ -151,6 +163,19 @@ int b200_embed_row(const void* emb, const long long* tok, void* x, int H, void* 
 }
 
 static inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
+// Bytes of packed rows one ring stage of the step kernel holds: at least two rows of the widest matrix.
+static inline int step_stage_w(int kmax) { return align_up(kmax > 16384 ? kmax : 16384, 128); }
+
+int b200_decode_step_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up, int kmax,
+                            int grid, void* stream) {
+  REQUIRE(Wp && SZ && out && N > 0 && K > 0 && grid > 0 && kmax >= K, B200_ERR_ARG);
+  REQUIRE(K % 128 == 0 && log2G >= 5 && log2G <= 10 && K % (1 << log2G) == 0 && ((K >> log2G) % 4) == 0,
+          B200_ERR_SHAPE);
+  REQUIRE(!gate_up || N % 2 == 0, B200_ERR_SHAPE);
+  REQUIRE(aligned16(Wp) && aligned16(SZ) && aligned16(out), B200_ERR_ALIGN);
+  return finish(b200::repack_stream_dispatch(Wp, SZ, out, N, K, log2G, gate_up ? 1 : 0, grid, step_stage_w(kmax),
+                                             S(stream)));
+}
 
 size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D, int grid) {
   const size_t per_layer = (size_t)(n_q + 2 * n_kv) * D + (size_t)n_q * D + H + I + H;
@@ -159,7 +184,7 @@ size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D
 
 int b200_decode_step(const b200_step_desc* d, void* stream) {
   static_assert(sizeof(b200_step_layer) == sizeof(b200::StepLayer), "layer structs must match");
-  REQUIRE(d && d->layers && d->emb && d->norm_f && d->w_head && d->sz_head && d->cos_t && d->sin_t && d->bt &&
+  REQUIRE(d && d->layers && d->emb && d->norm_f && d->w_head && d->cos_t && d->sin_t && d->bt &&
               d->tok && d->pos && d->logits && d->xchg && d->ctrl,
           B200_ERR_ARG);
   REQUIRE(d->L > 0 && d->H > 0 && d->I > 0 && d->n_q > 0 && d->n_kv > 0 && d->V > 0 && d->grid > 0 && d->ctx_cap > 0,
@@ -175,7 +200,7 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
     kmax = K > kmax ? K : kmax;
   }
   REQUIRE(d->H % 8 == 0 && d->I % 8 == 0, B200_ERR_SHAPE);
-  REQUIRE(aligned16(d->emb) && aligned16(d->norm_f) && aligned16(d->w_head) && aligned16(d->sz_head) &&
+  REQUIRE(aligned16(d->emb) && aligned16(d->norm_f) && aligned16(d->w_head) &&
               aligned16(d->xchg) && aligned16(d->ctrl),
           B200_ERR_ALIGN);
   REQUIRE(d->ctx_cap <= (1 << 20), B200_ERR_LIMIT);
@@ -208,8 +233,7 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
   }
   p.table_bytes = align_up(d->L * (int)sizeof(b200::StepLayer), 128);
   REQUIRE(aligned16(d->layers), B200_ERR_ALIGN);
-  const int max_rowbytes = kmax / 2;
-  p.stage_w = align_up(2 * max_rowbytes > 16384 ? 2 * max_rowbytes : 16384, 128);
+  p.stage_w = step_stage_w(kmax);
   // attention copies whole KV pages into a stage: at least one page of K and of V must fit
   REQUIRE(((4 * d->D) << d->log2P) <= p.stage_w, B200_ERR_SHAPE);
   int max_sz = 0;

@@ -129,7 +129,7 @@ struct Cta {
   StepCtrl* ctrl;
   uint32_t tagw;         // (tag << 16)
   int ns;                // ring stages
-  int stage_bytes, sz_off;
+  int stage_bytes;
 };
 
 DEVI void raise(const Cta& c, int code) {
@@ -142,6 +142,7 @@ DEVI void raise(const Cta& c, int code) {
 
 // Wait for a ring barrier phase. Returns false (and raises) if the bound is hit or the step is already aborting.
 DEVI bool wait_bar(const Cta& c, uint64_t* bar, uint32_t parity, int code) {
+#pragma unroll 1
   for (int i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*c.abort) return false;
@@ -277,9 +278,10 @@ DEVI float stage_x(const Cta& c, const uint32_t* E, const half* emb_row, const h
 }
 
 // ---- GEMV phase -----------------------------------------------------------------------------------------------------
+// A weight matrix in "stream layout" (see repack_stream_kernel): for every CTA, for every ring stage of its slice,
+// the packed rows of the stage followed by their (scale, zero) rows, contiguous - one bulk copy per stage.
 struct Mat {
-  const uint8_t* w;    // packed int4 rows, K/2 bytes each
-  const uint8_t* sz;   // (scale, zero) half2 per group, ng * 4 bytes per row
+  const uint8_t* stream;
   int N, K;            // N rows (for gate|up: N = I units, rows i and I + i)
   int gu;              // 1: gate|up pairing
 };
@@ -299,30 +301,21 @@ DEVI Slice slice_of(const Mat& m, int log2G, int stage_w, int cta, int ncta) {
   return s;
 }
 
-// Producer: issue every stage of one matrix slice. `it` is the running stage counter of the whole step.
+// Producer: issue every stage of one matrix slice (one copy each; a bulk copy costs ~0.2 us to issue whatever its
+// size, so several small copies per stage would make the producer the bottleneck). `it` is the running stage
+// counter of the step.
 DEVI void produce(const Cta& c, const Mat& m, const Slice& s, int& it, int lane) {
+  const size_t rowall = (size_t)s.rowbytes + s.szrow;
   for (int st = 0; st < s.nstages; ++st, ++it) {
     const int slot = it % c.ns;
     const uint32_t parity = ((it / c.ns) & 1) ^ 1;   // a fresh barrier passes the first round
     if (!wait_bar(c, &c.empty[slot], parity, ERR_EMPTY)) return;
     if (lane == 0) {
       const int u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups);
-      uint8_t* dst = c.ring + (size_t)slot * c.stage_bytes;
-      if (m.gu) {
-        const int nu = u1 - u0;
-        const uint32_t wb = nu * s.rowbytes, sb = nu * s.szrow;
-        mbar_expect_tx(&c.full[slot], 2 * (wb + sb));
-        bulk_g2s(dst, m.w + (size_t)u0 * s.rowbytes, wb, &c.full[slot]);
-        bulk_g2s(dst + wb, m.w + (size_t)(m.N + u0) * s.rowbytes, wb, &c.full[slot]);
-        bulk_g2s(dst + c.sz_off, m.sz + (size_t)u0 * s.szrow, sb, &c.full[slot]);
-        bulk_g2s(dst + c.sz_off + sb, m.sz + (size_t)(m.N + u0) * s.szrow, sb, &c.full[slot]);
-      } else {
-        const int r0 = 2 * u0, r1 = min(m.N, 2 * u1);
-        const uint32_t wb = (r1 - r0) * s.rowbytes, sb = (r1 - r0) * s.szrow;
-        mbar_expect_tx(&c.full[slot], wb + sb);
-        bulk_g2s(dst, m.w + (size_t)r0 * s.rowbytes, wb, &c.full[slot]);
-        bulk_g2s(dst + c.sz_off, m.sz + (size_t)r0 * s.szrow, sb, &c.full[slot]);
-      }
+      const int r0 = 2 * u0, r1 = m.gu ? 2 * u1 : min(m.N, 2 * u1);   // gate|up: two rows per unit, always
+      const uint32_t bytes = (uint32_t)((r1 - r0) * rowall);
+      mbar_expect_tx(&c.full[slot], bytes);
+      bulk_g2s(c.ring + (size_t)slot * c.stage_bytes, m.stream + (size_t)r0 * rowall, bytes, &c.full[slot]);
     }
   }
 }
@@ -422,6 +415,7 @@ DEVI void consume(const Cta& c, const Mat& m, const Slice& s, int log2G, float r
     const bool ok = wait_bar(c, &c.full[slot], (it / c.ns) & 1, ERR_FULL);
     const int u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups), nu = u1 - u0;
     const uint8_t* base = c.ring + (size_t)slot * c.stage_bytes;
+    const uint8_t* szbase = base + (size_t)((m.gu ? 2 * u1 : min(m.N, 2 * u1)) - 2 * u0) * s.rowbytes;
     if (ok) {
       const int gt0 = (u0 - s.ub) * segs;   // index of this stage's first task within the slice
       for (int t = ((warp - gt0) % kNCW + kNCW) % kNCW; t < nu * segs; t += kNCW) {
@@ -433,8 +427,8 @@ DEVI void consume(const Cta& c, const Mat& m, const Slice& s, int log2G, float r
         if (u < U)
           chunk_two_rows(c, reinterpret_cast<const uint4*>(base + (size_t)slot0 * s.rowbytes),
                          reinterpret_cast<const uint4*>(base + (size_t)slot1 * s.rowbytes),
-                         reinterpret_cast<const half2*>(base + c.sz_off + (size_t)slot0 * s.szrow),
-                         reinterpret_cast<const half2*>(base + c.sz_off + (size_t)slot1 * s.szrow), u, log2G, resc, p0,
+                         reinterpret_cast<const half2*>(szbase + (size_t)slot0 * s.szrow),
+                         reinterpret_cast<const half2*>(szbase + (size_t)slot1 * s.szrow), u, log2G, resc, p0,
                          p1);
         const float v = reduce_pair(p0, p1, lane);
         if ((lane & 15) == 0) c.part[((u0 - s.ub + j) * 2 + (lane >> 4)) * segs + k] = v;
@@ -629,7 +623,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   c.ctrl = p.ctrl;
   c.ns = p.ns;
   c.stage_bytes = p.stage_bytes;
-  c.sz_off = p.stage_w;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x, ncta = gridDim.x;
 
@@ -657,10 +650,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     int it = 0;
     for (int l = 0; l < p.L && !*c.abort; ++l) {
       const StepLayer& ly = lys[l];
-      const Mat mats[4] = {{(const uint8_t*)ly.w[0], (const uint8_t*)ly.sz[0], n_qkv, p.H, 0},
-                           {(const uint8_t*)ly.w[1], (const uint8_t*)ly.sz[1], p.H, n_att, 0},
-                           {(const uint8_t*)ly.w[2], (const uint8_t*)ly.sz[2], p.I, p.H, 1},
-                           {(const uint8_t*)ly.w[3], (const uint8_t*)ly.sz[3], p.H, p.I, 0}};
+      const Mat mats[4] = {{(const uint8_t*)ly.w[0], n_qkv, p.H, 0},
+                           {(const uint8_t*)ly.w[1], p.H, n_att, 0},
+                           {(const uint8_t*)ly.w[2], p.I, p.H, 1},
+                           {(const uint8_t*)ly.w[3], p.H, p.I, 0}};
       produce(c, mats[0], slice_of(mats[0], p.log2G, p.stage_w, cta, ncta), it, lane);
       for (int h = cta; h < p.n_q && !*c.abort; h += ncta) produce_kv(c, p, ly, h / hpg, pos, it, lane);
 #pragma unroll
@@ -668,7 +661,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
         if (!*c.abort) produce(c, mats[k], slice_of(mats[k], p.log2G, p.stage_w, cta, ncta), it, lane);
     }
     if (!*c.abort) {
-      const Mat head = {(const uint8_t*)p.w_head, (const uint8_t*)p.sz_head, p.V, p.H, 0};
+      const Mat head = {(const uint8_t*)p.w_head, p.V, p.H, 0};
       produce(c, head, slice_of(head, p.log2G, p.stage_w, cta, ncta), it, lane);
     }
     // Leave only when every copy issued has landed. On the normal path the consumers have waited on every full
@@ -710,7 +703,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   }
   // One loop body serves every GEMV of the step (4 per layer, then the LM head as "phase 0 of layer L"): the kernel
   // keeps a single copy of the staging, GEMV and attention code, which keeps the loop inside the instruction cache.
-  const Mat head = {(const uint8_t*)p.w_head, (const uint8_t*)p.sz_head, p.V, p.H, 0};
+  const Mat head = {(const uint8_t*)p.w_head, p.V, p.H, 0};
 #pragma unroll 1
   for (int step = 0; step <= 4 * p.L; ++step) {
     const int l = step >> 2, ph = step & 3;
@@ -726,20 +719,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     if (ph == 0) {
       Ein = l == 0 ? nullptr : E - p.H;   // down of the previous layer: the last H words of its block
       nw = is_head ? p.norm_f : ly.ln1;
-      m = is_head ? head : Mat{(const uint8_t*)ly.w[0], (const uint8_t*)ly.sz[0], n_qkv, p.H, 0};
+      m = is_head ? head : Mat{(const uint8_t*)ly.w[0], n_qkv, p.H, 0};
       Eout = Eqkv;
       out = is_head ? OUT_LOGITS : OUT_TAGGED;
     } else if (ph == 1) {
       Ein = Eatt; n_in = n_att;
-      m = Mat{(const uint8_t*)ly.w[1], (const uint8_t*)ly.sz[1], p.H, n_att, 0};
+      m = Mat{(const uint8_t*)ly.w[1], p.H, n_att, 0};
       Eout = Eo;
     } else if (ph == 2) {
       Ein = Eo; nw = ly.ln2;
-      m = Mat{(const uint8_t*)ly.w[2], (const uint8_t*)ly.sz[2], p.I, p.H, 1};
+      m = Mat{(const uint8_t*)ly.w[2], p.I, p.H, 1};
       Eout = Eact; out = OUT_SWIGLU;
     } else {
       Ein = Eact; n_in = p.I;
-      m = Mat{(const uint8_t*)ly.w[3], (const uint8_t*)ly.sz[3], p.H, p.I, 0};
+      m = Mat{(const uint8_t*)ly.w[3], p.H, p.I, 0};
       Eout = Edown;
     }
     const float resc = stage_x(c, Ein, emb_row, nw, n_in, p.eps, tid);
@@ -838,6 +831,45 @@ cudaError_t decode_step_launch(const StepParams& p, int grid, size_t smem, cudaS
   cfg.numAttrs = 1;
   return p.D == 64 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<64>, p)
                    : cudaLaunchKernelEx(&cfg, decode_step_kernel<128>, p);
+}
+
+// ---- stream layout ----------------------------------------------------------------------------------------------------
+// Rearranges one matrix (packed rows + scale/zero rows, the format of the quantizer) into the order the step kernel's
+// producers read it: the slice of CTA 0 first, then CTA 1, ...; inside a slice one block per ring stage, made of the
+// stage's packed rows followed by the same rows' (scale, zero) entries (gate|up: gate rows, up rows, gate sz, up sz).
+// Every row contributes K/2 + 4 K/G bytes wherever it lands, so a stage's block starts at
+// (index of its first row in slice order) * (K/2 + 4 K/G). One block per source row, one thread per 16-byte piece.
+__global__ void repack_stream_kernel(const uint8_t* __restrict__ W, const uint8_t* __restrict__ SZ,
+                                     uint8_t* __restrict__ out, int N, int K, int log2G, int gu, int ncta, int stage_w) {
+  const int rb = K >> 1, sb = (K >> log2G) << 2, pieces = (rb + sb) >> 4;
+  const int r = blockIdx.x;   // source row
+  const Mat m = {nullptr, gu ? N / 2 : N, K, gu};
+  const int units = gu ? m.N : (m.N + 1) >> 1;
+  const int u = gu ? (r < m.N ? r : r - m.N) : r >> 1;
+  const int base = units / ncta, rem = units % ncta, bnd = rem * (base + 1);
+  const int cta = u < bnd ? u / (base + 1) : rem + (u - bnd) / max(base, 1);
+  const Slice s = slice_of(m, log2G, stage_w, cta, ncta);
+  const int st = (u - s.ub) / s.ups, u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups);
+  const size_t rowall = (size_t)rb + sb;
+  int slot, nrows;
+  if (gu) { nrows = 2 * (u1 - u0); slot = (r < m.N ? 0 : u1 - u0) + (u - u0); }
+  else { nrows = min(m.N, 2 * u1) - 2 * u0; slot = r - 2 * u0; }
+  uint8_t* blk = out + (size_t)(2 * u0) * rowall;
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+    const int off = i << 4;
+    if (off < rb)
+      *reinterpret_cast<uint4*>(blk + (size_t)slot * rb + off) = *reinterpret_cast<const uint4*>(W + (size_t)r * rb + off);
+    else
+      *reinterpret_cast<uint4*>(blk + (size_t)nrows * rb + (size_t)slot * sb + (off - rb)) =
+          *reinterpret_cast<const uint4*>(SZ + (size_t)r * sb + (off - rb));
+  }
+}
+
+cudaError_t repack_stream_dispatch(const void* W, const void* SZ, void* out, int N, int K, int log2G, int gu, int ncta,
+                                   int stage_w, cudaStream_t st) {
+  repack_stream_kernel<<<N, 128, 0, st>>>((const uint8_t*)W, (const uint8_t*)SZ, (uint8_t*)out, N, K, log2G, gu, ncta,
+                                          stage_w);
+  return cudaPeekAtLastError();
 }
 
 }  // namespace b200

@@ -229,3 +229,82 @@ cudaError_t bw_read_dispatch(const void* p, size_t bytes, void* sink, int blocks
 }
 
 }  // namespace b200
+
+// ---- read-bandwidth probe through a bulk-copy ring -------------------------------------------------------------
+// Same question as bw_read, asked of the path the persistent step kernel uses: one elected thread per CTA streams
+// the CTA's share of the buffer into a shared-memory ring with cp.async.bulk (mbarrier transaction counts), the
+// other warps touch one word of every stage and release it. Waits are bounded: a wait that runs out sets *sink to
+// 0xdead0000 + code and the CTA stops.
+namespace b200 {
+namespace {
+DEVI uint32_t probe_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+DEVI bool probe_wait(uint64_t* bar, uint32_t parity) {
+  for (int i = 0; i < (1 << 20); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(probe_smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+}  // namespace
+
+__global__ void __launch_bounds__(160, 1)
+bw_read_bulk_kernel(const uint8_t* __restrict__ p, size_t bytes, uint32_t* sink, int stage_bytes, int ns) {
+  extern __shared__ __align__(128) uint8_t ring_smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring_smem);
+  uint64_t* empty = full + 32;
+  uint8_t* ring = ring_smem + 512;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int i = 0; i < ns; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(probe_smem_u32(&full[i])), "r"(1));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(probe_smem_u32(&empty[i])), "r"(4));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const size_t nstage_total = bytes / stage_bytes;
+  const size_t per = nstage_total / gridDim.x;           // stages per CTA (remainder ignored)
+  const uint8_t* src = p + (size_t)blockIdx.x * per * stage_bytes;
+  if (warp == 4) {
+    if (lane == 0) {
+      for (size_t it = 0; it < per; ++it) {
+        const int slot = (int)(it % ns);
+        if (!probe_wait(&empty[slot], (uint32_t)(((it / ns) & 1) ^ 1))) { *sink = 0xdead0003u; return; }
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(probe_smem_u32(&full[slot])),
+                     "r"(stage_bytes)
+                     : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         probe_smem_u32(ring + (size_t)slot * stage_bytes)),
+                     "l"(src + it * stage_bytes), "r"(stage_bytes), "r"(probe_smem_u32(&full[slot]))
+                     : "memory");
+      }
+    }
+    return;
+  }
+  uint32_t a = 0;
+  for (size_t it = 0; it < per; ++it) {
+    const int slot = (int)(it % ns);
+    if (!probe_wait(&full[slot], (uint32_t)((it / ns) & 1))) { *sink = 0xdead0002u; return; }
+    a ^= reinterpret_cast<const uint32_t*>(ring + (size_t)slot * stage_bytes)[tid];
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(probe_smem_u32(&empty[slot])) : "memory");
+  }
+  if (a == 0x5bd1e995u) *sink = a;
+}
+
+cudaError_t bw_read_bulk_dispatch(const void* p, size_t bytes, void* sink, int blocks, int stage_bytes, int stages,
+                                  cudaStream_t st) {
+  const size_t smem = 512 + (size_t)stage_bytes * stages;
+  cudaError_t e = cudaFuncSetAttribute(bw_read_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess) return e;
+  bw_read_bulk_kernel<<<blocks, 160, smem, st>>>((const uint8_t*)p, bytes, (uint32_t*)sink, stage_bytes, stages);
+  return cudaPeekAtLastError();
+}
+}  // namespace b200

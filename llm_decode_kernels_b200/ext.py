@@ -27,6 +27,7 @@ SIGNATURES = {
     "b200_gemv_w4a16": [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_void_p],
     "b200_bw_read": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_bw_read_bulk": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_paged_attention": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p],
@@ -75,6 +76,9 @@ def load_library(build_if_missing=True):
         fn.restype = c_int
     lib.b200_decode_step.argtypes = [ctypes.POINTER(StepDesc), c_void_p]
     lib.b200_decode_step.restype = c_int
+    lib.b200_decode_step_repack.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                            c_void_p]
+    lib.b200_decode_step_repack.restype = c_int
     lib.b200_decode_step_xchg_bytes.argtypes = [c_int] * 7
     lib.b200_decode_step_xchg_bytes.restype = c_size_t
     lib.b200_version.restype = c_int
@@ -143,6 +147,11 @@ class Ops:
         _cuda(buf, "buf"), _cuda(sink, "sink"), _aligned16(buf, "buf")
         self._check(self.lib.b200_bw_read(buf.data_ptr(), buf.numel() * buf.element_size(), sink.data_ptr(),
                                           int(blocks), int(threads), int(unroll), _stream()), "bw_read")
+
+    def bw_read_bulk(self, buf, sink, blocks, stage_bytes, stages):
+        _cuda(buf, "buf"), _cuda(sink, "sink"), _aligned16(buf, "buf")
+        self._check(self.lib.b200_bw_read_bulk(buf.data_ptr(), buf.numel() * buf.element_size(), sink.data_ptr(),
+                                               int(blocks), int(stage_bytes), int(stages), _stream()), "bw_read_bulk")
 
     def paged_attention(self, q, kc, vc, bt, pos, part_size, o_part, m_part, l_part, out, version=2):
         """One sequence, head_dim 64. q [n_q*64], caches [pages, n_kv, P, 64], bt int32 [pages], pos int32 [1],
@@ -260,6 +269,16 @@ class Ops:
 
     def decode_step_xchg_bytes(self, L, H, I, n_q, n_kv, D, grid):
         return int(self.lib.b200_decode_step_xchg_bytes(L, H, I, n_q, n_kv, D, grid))
+
+    def decode_step_repack(self, packed, sz, group, gate_up, kmax, grid):
+        """Stream-layout copy of one quantized matrix for decode_step (b200_decode_step_repack). Returns uint8."""
+        _cuda(packed, "packed", torch.int32), _cuda(sz, "sz", torch.float16)
+        N, K = packed.shape[0], packed.shape[1] * 8
+        out = torch.empty(N * (K // 2 + 4 * (K // group)), dtype=torch.uint8, device=packed.device)
+        self._check(self.lib.b200_decode_step_repack(packed.data_ptr(), sz.data_ptr(), out.data_ptr(), N, K,
+                                                     _ilog2_exact(int(group), "group"), int(bool(gate_up)), int(kmax),
+                                                     int(grid), _stream()), "decode_step_repack")
+        return out
 
     def decode_step(self, desc: "StepDesc"):
         """One whole decode step as one persistent kernel (b200_decode_step) on the current stream."""

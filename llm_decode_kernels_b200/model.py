@@ -198,25 +198,33 @@ class Model:
             return
         dev = self.cfg.device
         if getattr(self, "_step_static", None) is None:
+            grid = torch.cuda.get_device_properties(dev).multi_processor_count
+            kmax = max(self.H, self.n_q * self.D, self.I)
+            # a second copy of every matrix in the order the kernel's producers stream it (one bulk copy per stage)
+            streams = [{name: self.K.decode_step_repack(lw[name].packed, lw[name].sz, self.cfg.group, name == "gu", kmax,
+                                                        grid) for name in ("qkv", "o", "gu", "down")}
+                       for lw in self.layers]
+            head_stream = self.K.decode_step_repack(self.lm_head.packed, self.lm_head.sz, self.cfg.group, False, kmax,
+                                                    grid)
             arr = (ext.StepLayer * self.L)()
             for i, lw in enumerate(self.layers):
                 for k, name in enumerate(("qkv", "o", "gu", "down")):
-                    arr[i].w[k] = lw[name].packed.data_ptr()
-                    arr[i].sz[k] = lw[name].sz.data_ptr()
+                    arr[i].w[k] = streams[i][name].data_ptr()
+                    arr[i].sz[k] = 0
                 arr[i].ln1, arr[i].ln2 = lw["ln1"].data_ptr(), lw["ln2"].data_ptr()
                 arr[i].kc, arr[i].vc = self.kv[i, 0].data_ptr(), self.kv[i, 1].data_ptr()
             host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
-            grid = torch.cuda.get_device_properties(dev).multi_processor_count
             nbytes = self.K.decode_step_xchg_bytes(self.L, self.H, self.I, self.n_q, self.n_kv, self.D, grid)
             self._step_static = {"layers": host.to(dev), "xchg": torch.zeros(nbytes, dtype=torch.uint8, device=dev),
-                                 "ctrl": torch.zeros(4, dtype=torch.int32, device=dev), "grid": grid}
+                                 "ctrl": torch.zeros(4, dtype=torch.int32, device=dev), "grid": grid,
+                                 "streams": streams, "head_stream": head_stream}
         st = self._step_static
         d = ext.StepDesc()
         d.layers = st["layers"].data_ptr()
         d.L, d.H, d.I, d.n_q, d.n_kv, d.D, d.V = self.L, self.H, self.I, self.n_q, self.n_kv, self.D, self.V
         d.log2G, d.log2P, d.eps = self.cfg.group.bit_length() - 1, self.cfg.page.bit_length() - 1, self.eps
         d.emb, d.norm_f = self.emb.data_ptr(), self.norm_f.data_ptr()
-        d.w_head, d.sz_head = self.lm_head.packed.data_ptr(), self.lm_head.sz.data_ptr()
+        d.w_head, d.sz_head = st["head_stream"].data_ptr(), 0
         d.cos_t, d.sin_t, d.bt = self.cos.data_ptr(), self.sin.data_ptr(), self.bt.data_ptr()
         d.tok, d.pos, d.history = self.tok.data_ptr(), self.pos.data_ptr(), self.history.data_ptr()
         d.logits, d.xchg, d.ctrl = self.logits.data_ptr(), st["xchg"].data_ptr(), st["ctrl"].data_ptr()
