@@ -5,6 +5,7 @@
 #include "../../include/b200decode.h"
 #include "common.cuh"
 #include "decode_step.h"
+#include <stdlib.h>
 
 namespace b200 {
 cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, const void* SZ, const void* x, void* y,
@@ -164,7 +165,7 @@ int b200_embed_row(const void* emb, const long long* tok, void* x, int H, void* 
 
 static inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 // Bytes of packed rows one ring stage of the step kernel holds: at least two rows of the widest matrix.
-static inline int step_stage_w(int kmax) { return align_up(kmax > 16384 ? kmax : 16384, 128); }
+static inline int step_stage_w(int kmax) { return align_up(kmax > 32768 ? kmax : 32768, 128); }
 
 int b200_decode_step_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up, int kmax,
                             int grid, void* stream) {
@@ -213,6 +214,10 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
   p.cos_t = d->cos_t; p.sin_t = d->sin_t; p.bt = d->bt; p.tok = d->tok; p.pos = d->pos; p.history = d->history;
   p.logits = (half*)d->logits; p.xchg = (uint32_t*)d->xchg; p.ctrl = (b200::StepCtrl*)d->ctrl;
   p.trace = d->trace;
+  {
+    const char* dbg = getenv("B200_STEP_DEBUG");   // timing experiments only; see decode_step.h
+    p.debug = dbg ? atoi(dbg) : 0;
+  }
   // shared-memory plan
   const int ncw = b200::decode_step_consumer_warps();
   p.resid_bytes = align_up(2 * d->H, 128);

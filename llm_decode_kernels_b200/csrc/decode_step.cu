@@ -53,7 +53,7 @@ constexpr int kNT = kNCW * 32;              // consumer threads
 constexpr int kThreads = kNT + 32;          // + producer warp
 constexpr int kMaxStages = 16;
 constexpr int kSpinLimit = 1 << 18;         // polls / try_waits before a wait gives up (tens of milliseconds)
-constexpr int kHeaderBytes = 1024;
+constexpr int kHeaderBytes = 2048;
 constexpr int kMaxKvTokens = 64;            // cached tokens per ring stage in attention (16 warps x 4 tokens)
 
 enum : int { ERR_POLL = 1, ERR_FULL = 2, ERR_EMPTY = 3 };
@@ -129,6 +129,7 @@ struct Cta {
   StepCtrl* ctrl;
   uint32_t tagw;         // (tag << 16)
   int ns;                // ring stages
+  int nopoll;            // debug: take exchange words as they are (timing experiments only)
   int stage_bytes;
 };
 
@@ -141,11 +142,14 @@ DEVI void raise(const Cta& c, int code) {
 }
 
 // Wait for a ring barrier phase. Returns false (and raises) if the bound is hit or the step is already aborting.
-DEVI bool wait_bar(const Cta& c, uint64_t* bar, uint32_t parity, int code) {
+// `nap` nanoseconds of sleep follow every failed attempt: a waiting warp must not eat the issue slots of the warps
+// it shares a scheduler with (the producer waits for most of the step).
+DEVI bool wait_bar(const Cta& c, uint64_t* bar, uint32_t parity, int code, unsigned nap = 0) {
 #pragma unroll 1
   for (int i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*c.abort) return false;
+    if (nap) __nanosleep(nap);
   }
   raise(c, code);
   return false;
@@ -155,7 +159,7 @@ DEVI bool wait_bar(const Cta& c, uint64_t* bar, uint32_t parity, int code) {
 DEVI uint2 poll4(const Cta& c, const uint32_t* p) {
   uint4 v = ld_poll4(p);
   int spins = 0;
-  while ((((v.x ^ c.tagw) | (v.y ^ c.tagw) | (v.z ^ c.tagw) | (v.w ^ c.tagw)) >> 16) != 0) {
+  while (!c.nopoll && ((((v.x ^ c.tagw) | (v.y ^ c.tagw) | (v.z ^ c.tagw) | (v.w ^ c.tagw)) >> 16) != 0)) {
     if (*c.abort) break;
     if (++spins > kSpinLimit) { raise(c, ERR_POLL); break; }
     if ((spins & 255) == 0 && ((volatile StepCtrl*)c.ctrl)->abort) { *c.abort = 1; break; }
@@ -288,6 +292,32 @@ struct Mat {
 
 struct Slice { int ub, ue, ups, nstages, rowbytes, szrow; };
 
+// Position in the ring. Stages are used strictly in order by producer and consumers alike, so a slot index and a
+// parity bit that flips on wrap-around replace a stage counter (and the divisions by the ring size it would need).
+struct RingPos {
+  int slot;
+  uint32_t parity;
+  int count;   // stages passed (the producer's abort path needs it)
+};
+DEVI void advance(RingPos& r, int ns) {
+  ++r.count;
+  if (++r.slot == ns) { r.slot = 0; r.parity ^= 1u; }
+}
+
+// How the consumer warps split a matrix with rows of K weights: see consume().
+struct WarpMap { int segs, sper, seg0, group, rank, upsmod; };
+DEVI WarpMap warp_map(int K, int ups, int warp) {
+  WarpMap w;
+  const int U = K >> 5;
+  w.segs = (U + 31) >> 5;
+  w.sper = (w.segs + kNCW - 1) / kNCW;
+  w.seg0 = w.sper == 1 ? warp % w.segs : warp;
+  w.group = w.sper == 1 ? (kNCW - w.seg0 + w.segs - 1) / w.segs : 1;
+  w.rank = w.sper == 1 ? warp / w.segs : 0;
+  w.upsmod = ups % w.group;
+  return w;
+}
+
 DEVI Slice slice_of(const Mat& m, int log2G, int stage_w, int cta, int ncta) {
   Slice s;
   s.rowbytes = m.K >> 1;
@@ -304,12 +334,11 @@ DEVI Slice slice_of(const Mat& m, int log2G, int stage_w, int cta, int ncta) {
 // Producer: issue every stage of one matrix slice (one copy each; a bulk copy costs ~0.2 us to issue whatever its
 // size, so several small copies per stage would make the producer the bottleneck). `it` is the running stage
 // counter of the step.
-DEVI void produce(const Cta& c, const Mat& m, const Slice& s, int& it, int lane) {
+DEVI void produce(const Cta& c, const Mat& m, const Slice& s, RingPos& rp, int lane) {
   const size_t rowall = (size_t)s.rowbytes + s.szrow;
-  for (int st = 0; st < s.nstages; ++st, ++it) {
-    const int slot = it % c.ns;
-    const uint32_t parity = ((it / c.ns) & 1) ^ 1;   // a fresh barrier passes the first round
-    if (!wait_bar(c, &c.empty[slot], parity, ERR_EMPTY)) return;
+  for (int st = 0; st < s.nstages; ++st, advance(rp, c.ns)) {
+    const int slot = rp.slot;
+    if (!wait_bar(c, &c.empty[slot], rp.parity, ERR_EMPTY, 200)) return;
     if (lane == 0) {
       const int u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups);
       const int r0 = 2 * u0, r1 = m.gu ? 2 * u1 : min(m.N, 2 * u1);   // gate|up: two rows per unit, always
@@ -328,14 +357,13 @@ DEVI int kv_tokens_per_stage(const StepParams& p) {
 
 // Producer: the cached K/V rows [0, pos) of one kv head, page by page. Whole pages are copied; rows at or beyond
 // pos in the last page are ignored by the consumer.
-DEVI void produce_kv(const Cta& c, const StepParams& p, const StepLayer& ly, int kvh, int pos, int& it, int lane) {
+DEVI void produce_kv(const Cta& c, const StepParams& p, const StepLayer& ly, int kvh, int pos, RingPos& rp, int lane) {
   const int tps = kv_tokens_per_stage(p), pps = tps >> p.log2P;
   const uint32_t page_bytes = (uint32_t)(p.D * 2) << p.log2P;
   const int nst = (pos + tps - 1) / tps;
-  for (int st = 0; st < nst; ++st, ++it) {
-    const int slot = it % c.ns;
-    const uint32_t parity = ((it / c.ns) & 1) ^ 1;
-    if (!wait_bar(c, &c.empty[slot], parity, ERR_EMPTY)) return;
+  for (int st = 0; st < nst; ++st, advance(rp, c.ns)) {
+    const int slot = rp.slot;
+    if (!wait_bar(c, &c.empty[slot], rp.parity, ERR_EMPTY, 200)) return;
     const int pg0 = st * pps, npg = min(pps, ((pos + (1 << p.log2P) - 1) >> p.log2P) - pg0);
     uint8_t* dst = c.ring + (size_t)slot * c.stage_bytes;
     if (lane == 0) mbar_expect_tx(&c.full[slot], 2 * npg * page_bytes);
@@ -364,26 +392,34 @@ DEVI void fma_word2(uint32_t wa, uint32_t wb, uint4 x, half2* a, half2* b) {
   b[3] = __hfma2(as_h2(wb8 & 0x00F000F0u), as_h2(x.w), b[3]);
 }
 
-// One 32-weight chunk (u) of two rows against the staged x: this lane's share of both dot products.
-DEVI void chunk_two_rows(const Cta& c, const uint4* w0, const uint4* w1, const half2* z0, const half2* z1, int u,
-                         int log2G, float resc, float& p0, float& p1) {
-  const half2 zero2 = __float2half2_rn(0.f);
-  const uint4 wa = w0[u], wb = w1[u];
+// The 32 staged activations of one weight chunk, held in registers, plus their unscaled sum.
+struct XChunk { uint4 x0, x1, x2, x3; float xs; };
+
+DEVI XChunk load_xchunk(const Cta& c, int u) {
   const int sw = (u >> 1) & 3;
-  const uint4 x0 = c.xin[4 * u + (0 ^ sw)], x1 = c.xin[4 * u + (1 ^ sw)], x2 = c.xin[4 * u + (2 ^ sw)],
-              x3 = c.xin[4 * u + (3 ^ sw)];
-  const float xs = c.xsum[u];
-  const int g = (u << 5) >> log2G;
-  const float2 sa = __half22float2(z0[g]), sb = __half22float2(z1[g]);   // (scale, zero)
+  XChunk r;
+  r.x0 = c.xin[4 * u + (0 ^ sw)];
+  r.x1 = c.xin[4 * u + (1 ^ sw)];
+  r.x2 = c.xin[4 * u + (2 ^ sw)];
+  r.x3 = c.xin[4 * u + (3 ^ sw)];
+  r.xs = c.xsum[u];
+  return r;
+}
+
+// One 32-weight chunk of two rows (packed words wa, wb; (scale, zero) sa, sb) against x: this lane's share of both
+// dot products.
+DEVI void chunk_two_rows(uint4 wa, uint4 wb, half2 sza, half2 szb, const XChunk& x, float resc, float& p0, float& p1) {
+  const half2 zero2 = __float2half2_rn(0.f);
+  const float2 sa = __half22float2(sza), sb = __half22float2(szb);
   half2 a[4] = {zero2, zero2, zero2, zero2}, b[4] = {zero2, zero2, zero2, zero2};
-  fma_word2(wa.x, wb.x, x0, a, b);
-  fma_word2(wa.y, wb.y, x1, a, b);
-  fma_word2(wa.z, wb.z, x2, a, b);
-  fma_word2(wa.w, wb.w, x3, a, b);
+  fma_word2(wa.x, wb.x, x.x0, a, b);
+  fma_word2(wa.y, wb.y, x.x1, a, b);
+  fma_word2(wa.z, wb.z, x.x2, a, b);
+  fma_word2(wa.w, wb.w, x.x3, a, b);
   const float2 fa0 = __half22float2(__hadd2(a[0], a[2])), fa1 = __half22float2(__hadd2(a[1], a[3]));
   const float2 fb0 = __half22float2(__hadd2(b[0], b[2])), fb1 = __half22float2(__hadd2(b[1], b[3]));
-  p0 = sa.x * fmaf((fa0.x + fa0.y) + (fa1.x + fa1.y), resc, -sa.y * xs);
-  p1 = sb.x * fmaf((fb0.x + fb0.y) + (fb1.x + fb1.y), resc, -sb.y * xs);
+  p0 = fmaf(sa.x, fmaf((fa0.x + fa0.y) + (fa1.x + fa1.y), resc, -sa.y * x.xs), p0);
+  p1 = fmaf(sb.x, fmaf((fb0.x + fb0.y) + (fb1.x + fb1.y), resc, -sb.y * x.xs), p1);
 }
 
 // Sum p0 over the warp and p1 over the warp with 6 shuffles instead of 10: the first exchange leaves the lower
@@ -399,43 +435,102 @@ DEVI float reduce_pair(float p0, float p1, int lane) {
 
 enum : int { OUT_TAGGED = 0, OUT_SWIGLU = 1, OUT_LOGITS = 2 };
 
-// Consumer side of one matrix slice. The work of the slice is cut into tasks (unit = pair of rows, segment = 32
-// consecutive 32-weight chunks, i.e. 1024 weights of each row); tasks go round robin to the 16 warps, so even a
-// slice of a dozen rows keeps every warp busy and no warp walks a whole row alone. Per task the warp leaves two
-// partial sums in shared memory (c.part); after one barrier per slice, thread i finishes unit i: it adds the
-// segments in a fixed order (deterministic) and emits the output.
+// Consumer side of one matrix slice. A row is cut into segments of 32 chunks (1024 weights); every warp is bound to
+// ONE segment for the whole slice (warp w -> segment w mod segs) and lane l to chunk l of it, so the lane's 32
+// activations sit in registers and are loaded once per slice; the warps that share a segment split the units
+// (pairs of rows) round robin. Per unit a lane reads two 16-byte weight chunks and two (scale, zero) words, runs the
+// 72-instruction core, and the warp leaves two partial sums in shared memory (c.part). After one barrier per slice
+// thread i finishes unit i: it adds the segments in a fixed order (deterministic) and emits the output.
+// When a row has more than 16 segments (K > 16384) a warp owns several segments and reloads x between them.
 //   OUT_TAGGED: E[row] <- tagged y.  OUT_SWIGLU: E[i] <- tagged half(silu(gate_i)) * up_i.
 //   OUT_LOGITS: logits[row] <- y, and `best` tracks this thread's maximum.
-DEVI void consume(const Cta& c, const Mat& m, const Slice& s, int log2G, float resc, int& it, const int OUT,
-                  uint32_t* E, half* logits, unsigned long long& best, int tid) {
-  const int warp = tid >> 5, lane = tid & 31;
-  const int U = m.K >> 5, segs = (U + 31) >> 5;
-  for (int st = 0; st < s.nstages; ++st, ++it) {
-    const int slot = it % c.ns;
-    const bool ok = wait_bar(c, &c.full[slot], (it / c.ns) & 1, ERR_FULL);
+DEVI void consume(const Cta& c, const Mat& m, const Slice& s, const WarpMap& wm_, int log2G, float resc, RingPos& rp,
+                  const int OUT, uint32_t* E, half* logits, unsigned long long& best, int tid) {
+  const int lane = tid & 31;
+  const int U = m.K >> 5, segs = wm_.segs;
+  const int sper = wm_.sper;     // segments per warp (1 unless K > 16384)
+  const int seg0 = wm_.seg0;     // first (usually only) segment of this warp
+  const int group = wm_.group;   // warps sharing seg0
+  const int rank = wm_.rank;     // this warp's place among them
+  XChunk x;
+  int u = 32 * seg0 + lane;
+  if (u < U) x = load_xchunk(c, u);
+  const int g = (u << 5) >> log2G;
+  int joff = 0;   // (index of the stage's first unit within the slice) mod group
+  for (int st = 0; st < s.nstages; ++st, advance(rp, c.ns)) {
+    const int slot = rp.slot;
+    const bool ok = wait_bar(c, &c.full[slot], rp.parity, ERR_FULL);
     const int u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups), nu = u1 - u0;
     const uint8_t* base = c.ring + (size_t)slot * c.stage_bytes;
     const uint8_t* szbase = base + (size_t)((m.gu ? 2 * u1 : min(m.N, 2 * u1)) - 2 * u0) * s.rowbytes;
     if (ok) {
-      const int gt0 = (u0 - s.ub) * segs;   // index of this stage's first task within the slice
-      for (int t = ((warp - gt0) % kNCW + kNCW) % kNCW; t < nu * segs; t += kNCW) {
-        const int j = t / segs, k = t - j * segs, u = 32 * k + lane;
-        int slot0, slot1;
-        if (m.gu) { slot0 = j; slot1 = nu + j; }
-        else { slot0 = 2 * j; slot1 = 2 * (u0 + j) + 1 < m.N ? slot0 + 1 : slot0; }
-        float p0 = 0.f, p1 = 0.f;
-        if (u < U)
-          chunk_two_rows(c, reinterpret_cast<const uint4*>(base + (size_t)slot0 * s.rowbytes),
-                         reinterpret_cast<const uint4*>(base + (size_t)slot1 * s.rowbytes),
-                         reinterpret_cast<const half2*>(szbase + (size_t)slot0 * s.szrow),
-                         reinterpret_cast<const half2*>(szbase + (size_t)slot1 * s.szrow), u, log2G, resc, p0,
-                         p1);
-        const float v = reduce_pair(p0, p1, lane);
-        if ((lane & 15) == 0) c.part[((u0 - s.ub + j) * 2 + (lane >> 4)) * segs + k] = v;
+      const int ui0 = u0 - s.ub;   // index of the stage's first unit within the slice
+      if (sper == 1) {
+        // two units per trip: twice the independent work between dependent shuffles, one combined reduction
+        for (int j = rank - joff + (rank < joff ? group : 0); j < nu; j += 2 * group) {
+          const int j2 = j + group < nu ? j + group : j;   // second unit of the trip (repeats the first at the tail)
+          int sa0, sa1, sb0, sb1;
+          if (m.gu) { sa0 = j; sa1 = nu + j; sb0 = j2; sb1 = nu + j2; }
+          else {
+            sa0 = 2 * j; sa1 = 2 * (u0 + j) + 1 < m.N ? sa0 + 1 : sa0;
+            sb0 = 2 * j2; sb1 = 2 * (u0 + j2) + 1 < m.N ? sb0 + 1 : sb0;
+          }
+          float p0 = 0.f, p1 = 0.f, q0 = 0.f, q1 = 0.f;
+          if (u < U) {
+            const uint4 wa0 = reinterpret_cast<const uint4*>(base + (size_t)sa0 * s.rowbytes)[u];
+            const uint4 wa1 = reinterpret_cast<const uint4*>(base + (size_t)sa1 * s.rowbytes)[u];
+            const uint4 wb0 = reinterpret_cast<const uint4*>(base + (size_t)sb0 * s.rowbytes)[u];
+            const uint4 wb1 = reinterpret_cast<const uint4*>(base + (size_t)sb1 * s.rowbytes)[u];
+            const half2 za0 = reinterpret_cast<const half2*>(szbase + (size_t)sa0 * s.szrow)[g];
+            const half2 za1 = reinterpret_cast<const half2*>(szbase + (size_t)sa1 * s.szrow)[g];
+            const half2 zb0 = reinterpret_cast<const half2*>(szbase + (size_t)sb0 * s.szrow)[g];
+            const half2 zb1 = reinterpret_cast<const half2*>(szbase + (size_t)sb1 * s.szrow)[g];
+            chunk_two_rows(wa0, wa1, za0, za1, x, resc, p0, p1);
+            chunk_two_rows(wb0, wb1, zb0, zb1, x, resc, q0, q1);
+          }
+          // 4 sums with 7 shuffles: quarter q of the warp ends up holding value q
+          const int qd = lane >> 3;
+          float v0 = (qd & 2) ? q0 : p0, v1 = (qd & 2) ? q1 : p1;          // this half-warp's pair
+          const float o0 = (qd & 2) ? p0 : q0, o1 = (qd & 2) ? p1 : q1;    // the other half-warp's pair
+          v0 += __shfl_xor_sync(0xffffffffu, o0, 16);
+          v1 += __shfl_xor_sync(0xffffffffu, o1, 16);
+          float v = (qd & 1) ? v1 : v0;
+          v += __shfl_xor_sync(0xffffffffu, (qd & 1) ? v0 : v1, 8);
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          if ((lane & 7) == 0) {
+            const int jj = (qd & 2) ? j2 : j;
+            if (!(qd & 2) || j2 != j) c.part[((ui0 + jj) * 2 + (qd & 1)) * segs + seg0] = v;
+          }
+        }
+      } else {
+        for (int j = 0; j < nu; ++j) {
+          int slot0, slot1;
+          if (m.gu) { slot0 = j; slot1 = nu + j; }
+          else { slot0 = 2 * j; slot1 = 2 * (u0 + j) + 1 < m.N ? slot0 + 1 : slot0; }
+          const uint4* w0 = reinterpret_cast<const uint4*>(base + (size_t)slot0 * s.rowbytes);
+          const uint4* w1 = reinterpret_cast<const uint4*>(base + (size_t)slot1 * s.rowbytes);
+          const half2* z0 = reinterpret_cast<const half2*>(szbase + (size_t)slot0 * s.szrow);
+          const half2* z1 = reinterpret_cast<const half2*>(szbase + (size_t)slot1 * s.szrow);
+          for (int seg = seg0; seg < segs; seg += kNCW) {
+            const int uu = 32 * seg + lane;
+            float p0 = 0.f, p1 = 0.f;
+            if (uu < U) {
+              const XChunk xx = load_xchunk(c, uu);
+              const int gg = (uu << 5) >> log2G;
+              chunk_two_rows(w0[uu], w1[uu], z0[gg], z1[gg], xx, resc, p0, p1);
+            }
+            const float v = reduce_pair(p0, p1, lane);
+            if ((lane & 15) == 0) c.part[((ui0 + j) * 2 + (lane >> 4)) * segs + seg] = v;
+          }
+        }
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&c.empty[slot]);
+    joff += wm_.upsmod;
+    if (joff >= group) joff -= group;
   }
   consumer_sync();
   for (int i = tid; i < s.ue - s.ub; i += kNT) {
@@ -445,7 +540,7 @@ DEVI void consume(const Cta& c, const Mat& m, const Slice& s, int log2G, float r
     const int unit = s.ub + i;
     if (OUT == OUT_SWIGLU) {
       const float gf = __half2float(h0);
-      const half sl = __float2half(gf / (1.f + expf(-gf)));
+      const half sl = __float2half(__fdividef(gf, 1.f + __expf(-gf)));
       st_tagged(E + unit, c.tagw | (uint32_t)__half_as_ushort(__hmul(sl, h1)));
     } else {
       const int row0 = 2 * unit, row1 = row0 + 1;
@@ -471,7 +566,7 @@ DEVI void consume(const Cta& c, const Mat& m, const Slice& s, int log2G, float r
 // dims [c D/8, (c+1) D/8) of it; each warp keeps a private online-softmax state, merged once at the end.
 template <int D>
 DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly, const uint32_t* Eqkv, uint32_t* Eattn,
-                         int h, int pos, float cs, float sn, int page_new, int& it, int tid) {
+                         int h, int pos, float cs, float sn, int page_new, RingPos& rp, int tid) {
   constexpr int D2 = D / 2, G4 = D / 4, DPL = D / 8;
   const int warp = tid >> 5, lane = tid & 31, ts = lane >> 3, ch = lane & 7;
   const int hpg = p.n_q / p.n_kv, kvh = h / hpg;
@@ -550,9 +645,9 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
 
   const int tps = kv_tokens_per_stage(p);
   const int nst = (pos + tps - 1) / tps;
-  for (int st = 0; st < nst; ++st, ++it) {
-    const int slot = it % c.ns;
-    const bool ok = wait_bar(c, &c.full[slot], (it / c.ns) & 1, ERR_FULL);
+  for (int st = 0; st < nst; ++st, advance(rp, c.ns)) {
+    const int slot = rp.slot;
+    const bool ok = wait_bar(c, &c.full[slot], rp.parity, ERR_FULL);
     const half* kbase = reinterpret_cast<const half*>(c.ring + (size_t)slot * c.stage_bytes);
     const half* vbase = kbase + (size_t)tps * D;
     const int nt = min(tps, pos - st * tps);
@@ -622,6 +717,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   c.ring = smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes + p.att_bytes + p.part_bytes + p.table_bytes;
   c.ctrl = p.ctrl;
   c.ns = p.ns;
+  c.nopoll = p.debug & 1;
   c.stage_bytes = p.stage_bytes;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x, ncta = gridDim.x;
@@ -630,6 +726,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     for (int i = 0; i < p.ns; ++i) { mbar_init(&c.full[i], 1); mbar_init(&c.empty[i], kNCW); }
     *c.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // The five matrix shapes of a step (qkv, o, gate|up, down, head) and this CTA's slice of each: computed once
+  // (they involve integer divisions) and kept in shared memory for producer and consumers.
+  Slice* sl = reinterpret_cast<Slice*>(smem + 512);
+  if (tid < 5) {
+    const int n_qkv_ = (p.n_q + 2 * p.n_kv) * p.D, n_att_ = p.n_q * p.D;
+    const Mat shapes[5] = {{nullptr, n_qkv_, p.H, 0}, {nullptr, p.H, n_att_, 0}, {nullptr, p.I, p.H, 1},
+                           {nullptr, p.H, p.I, 0}, {nullptr, p.V, p.H, 0}};
+    sl[tid] = slice_of(shapes[tid], p.log2G, p.stage_w, blockIdx.x, gridDim.x);
   }
   {
     const uint4* src = reinterpret_cast<const uint4*>(p.layers);
@@ -647,26 +752,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
 
   if (warp == kNCW) {
     // ================= producer =================
-    int it = 0;
+    RingPos rp = {0, 1u, 0};   // parity 1: the first pass over a fresh `empty` barrier does not wait
     for (int l = 0; l < p.L && !*c.abort; ++l) {
       const StepLayer& ly = lys[l];
       const Mat mats[4] = {{(const uint8_t*)ly.w[0], n_qkv, p.H, 0},
                            {(const uint8_t*)ly.w[1], p.H, n_att, 0},
                            {(const uint8_t*)ly.w[2], p.I, p.H, 1},
                            {(const uint8_t*)ly.w[3], p.H, p.I, 0}};
-      produce(c, mats[0], slice_of(mats[0], p.log2G, p.stage_w, cta, ncta), it, lane);
-      for (int h = cta; h < p.n_q && !*c.abort; h += ncta) produce_kv(c, p, ly, h / hpg, pos, it, lane);
+      produce(c, mats[0], sl[0], rp, lane);
+      for (int h = cta; h < p.n_q && !*c.abort; h += ncta) produce_kv(c, p, ly, h / hpg, pos, rp, lane);
 #pragma unroll
       for (int k = 1; k < 4; ++k)
-        if (!*c.abort) produce(c, mats[k], slice_of(mats[k], p.log2G, p.stage_w, cta, ncta), it, lane);
+        if (!*c.abort) produce(c, mats[k], sl[k], rp, lane);
     }
     if (!*c.abort) {
       const Mat head = {(const uint8_t*)p.w_head, p.V, p.H, 0};
-      produce(c, head, slice_of(head, p.log2G, p.stage_w, cta, ncta), it, lane);
+      produce(c, head, sl[4], rp, lane);
     }
     // Leave only when every copy issued has landed. On the normal path the consumers have waited on every full
     // barrier already; on abort, wait (bounded) for the full barriers of the stages still in the ring.
     if (*c.abort) {
+      const int it = rp.count;
       for (int k = max(0, it - c.ns); k < it; ++k) {
         const int slot = k % c.ns;
         for (int i = 0; i < kSpinLimit; ++i)
@@ -688,7 +794,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     }                                                        \
   } while (0)
   TRACE();
-  int it = 0;
+  RingPos rp = {0, 0u, 0};
+  // per-warp work split for the three row lengths (hidden, heads x head_dim, intermediate), in shared memory so
+  // that picking one by phase does not cost registers
+  WarpMap* wmaps = reinterpret_cast<WarpMap*>(smem + 640) + 3 * warp;
+  if (lane < 3) wmaps[lane] = warp_map(lane == 0 ? p.H : (lane == 1 ? n_att : p.I), sl[lane == 0 ? 0 : (lane == 1 ? 1 : 3)].ups, warp);
+  __syncwarp();
   unsigned long long best = 0ull;
   const half* emb_row = p.emb + (size_t)p.tok[0] * p.H;
   // RoPE factors and the page of this step's token depend only on pos: fetch them now, off the critical path
@@ -737,13 +848,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     }
     const float resc = stage_x(c, Ein, emb_row, nw, n_in, p.eps, tid);
     TRACE();
-    consume(c, m, slice_of(m, p.log2G, p.stage_w, cta, ncta), p.log2G, resc, it, out, Eout, p.logits, best, tid);
+    consume(c, m, sl[is_head ? 4 : ph], wmaps[ph == 1 ? 1 : (ph == 3 ? 2 : 0)], p.log2G, resc, rp, out, Eout, p.logits,
+            best, tid);
     if (is_head) break;
     if (consumer_sync_or(*c.abort)) return;
     TRACE();
     if (ph == 0) {
       for (int h = cta; h < p.n_q; h += ncta) {
-        attention_head<D>(c, p, ly, Eqkv, Eatt, h, pos, rope_c, rope_s, page_new, it, tid);
+        attention_head<D>(c, p, ly, Eqkv, Eatt, h, pos, rope_c, rope_s, page_new, rp, tid);
         if (consumer_sync_or(*c.abort)) return;
       }
       TRACE();

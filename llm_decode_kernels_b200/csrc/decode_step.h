@@ -43,6 +43,7 @@ struct StepParams {
   uint32_t* xchg;
   StepCtrl* ctrl;
   long long* trace;   // optional [grid][16 + 16 L] phase timestamps (ns)
+  int debug;          // bit 0: do not wait for exchange tags (results are garbage; for timing experiments)
   // shared-memory plan, computed on the host
   int resid_bytes, xin_bytes, xsum_bytes, att_bytes, part_bytes, table_bytes, stage_w, stage_bytes, ns;
 };
