@@ -486,7 +486,7 @@ DEVI void consume(const Cta& c, const Mat& m, const Slice& s, const WarpMap& wm_
             const half2 zb0 = reinterpret_cast<const half2*>(szbase + (size_t)sb0 * s.szrow)[g];
             const half2 zb1 = reinterpret_cast<const half2*>(szbase + (size_t)sb1 * s.szrow)[g];
             chunk_two_rows(wa0, wa1, za0, za1, x, resc, p0, p1);
-            chunk_two_rows(wb0, wb1, zb0, zb1, x, resc, q0, q1);
+            if (j2 != j) chunk_two_rows(wb0, wb1, zb0, zb1, x, resc, q0, q1);   // warp-uniform: no second unit at the tail
           }
           // 4 sums with 7 shuffles: quarter q of the warp ends up holding value q
           const int qd = lane >> 3;

@@ -23,7 +23,7 @@ from pathlib import Path
 
 import torch
 
-from . import ext
+from . import ext, tp as TP
 from .quant import QuantLinear
 
 ROOT = Path(__file__).resolve().parent
@@ -49,6 +49,9 @@ class DecodeConfig:
     device: str = "cuda"
     # ---- additions (defaults keep the reference behaviour) ----
     seed: int = None             # seed of the page-table shuffle (None: torch's global generator)
+    tp_rank: int = 0             # tensor parallelism: this process's rank ...
+    tp_world: int = 1            # ... of this many (one process per GPU, torch.distributed initialised by the caller)
+    tp_group: object = field(default=None, repr=False)   # process group of the TP ranks (None: the default group)
     step_kernel: str = "auto"    # "persistent": the whole step is one kernel (b200_decode_step); "multi": one launch
                                  # per operator, as the reference does; "auto": persistent when fused and the
                                  # prepared context cap is within PERSISTENT_MAX_CTX
@@ -60,11 +63,10 @@ PERSISTENT_MAX_CTX = 2048   # beyond this the in-kernel attention (one CTA per q
 class Linear:
     """One W4A16 projection in kernel format (reference runtime/model.py:56-72)."""
 
-    def __init__(self, w, cfg: DecodeConfig, key: str = None, keep_ref: bool = False):
+    def __init__(self, w, cfg: DecodeConfig, key: str = None, keep_ref: bool = False, pre=None):
         self.N, self.K = w.shape
         self.quant = True
-        pre = None
-        if cfg.quant == "pre":
+        if cfg.quant == "pre" and pre is None:
             pre = (cfg.qparams or {}).get(key)
             assert pre is not None, f"no precomputed weights for {key}"
         ql = QuantLinear(w.to(cfg.device), cfg.group, keep_ref=keep_ref, clip=cfg.quant == "clip", qsz=pre)
@@ -99,6 +101,16 @@ class Model:
         self.eps = c.rms_norm_eps
         if self.D not in (64, 128):
             raise ValueError(f"head_dim {self.D}: kernels exist for 64 and 128")
+        # tensor parallelism: from here on n_q, n_kv, I and V are THIS RANK's share; the *_full values are the model's
+        self.tp, self.tp_rank = cfg.tp_world, cfg.tp_rank
+        full = (self.n_q, self.n_kv, self.D, self.I, self.V)
+        self.V_full = self.V
+        if self.tp > 1:
+            TP.check(self.n_q, self.n_kv, self.D, self.I, self.V, cfg.group, self.tp)
+            self.n_q, self.n_kv, self.I, self.V = (v // self.tp for v in (self.n_q, self.n_kv, self.I, self.V))
+        shard = lambda kind, w: TP.shard_weight(kind, w, full, self.tp_rank, self.tp)
+        pre = lambda kind, key: (TP.shard_qsz(kind, (cfg.qparams or {}).get(key), full, cfg.group, self.tp_rank, self.tp)
+                                 if cfg.quant == "pre" else None)
         dev = cfg.device
         self.K = ext.load()
         sd = hf_state
@@ -113,14 +125,16 @@ class Model:
             self.layers.append({
                 "ln1": g(p + "input_layernorm.weight").contiguous(),
                 "ln2": g(p + "post_attention_layernorm.weight").contiguous(),
-                "qkv": Linear(wqkv, cfg, f"layers.{i}.qkv"),
-                "o": Linear(g(p + "self_attn.o_proj.weight"), cfg, f"layers.{i}.o"),
-                "gu": Linear(wgu, cfg, f"layers.{i}.gu"),
-                "down": Linear(g(p + "mlp.down_proj.weight"), cfg, f"layers.{i}.down")})
+                "qkv": Linear(shard("qkv", wqkv), cfg, f"layers.{i}.qkv", pre=pre("qkv", f"layers.{i}.qkv")),
+                "o": Linear(shard("o", g(p + "self_attn.o_proj.weight")), cfg, f"layers.{i}.o",
+                            pre=pre("o", f"layers.{i}.o")),
+                "gu": Linear(shard("gu", wgu), cfg, f"layers.{i}.gu", pre=pre("gu", f"layers.{i}.gu")),
+                "down": Linear(shard("down", g(p + "mlp.down_proj.weight")), cfg, f"layers.{i}.down",
+                               pre=pre("down", f"layers.{i}.down"))})
             del wqkv, wgu
         self.norm_f = g("model.norm.weight").contiguous()
         lm = sd["lm_head.weight"] if "lm_head.weight" in sd else sd["model.embed_tokens.weight"]
-        self.lm_head = Linear(lm.to(dev).half(), cfg, "lm_head")
+        self.lm_head = Linear(shard("lm_head", lm.to(dev).half()), cfg, "lm_head", pre=pre("lm_head", "lm_head"))
 
         # paged KV cache [L, 2, pages, n_kv, P, D]; one block table shared by all layers (one sequence)
         self.n_pages = (cfg.max_ctx + cfg.page - 1) // cfg.page + 1
@@ -145,7 +159,8 @@ class Model:
         self.gu = torch.empty(2 * self.I, **h16)
         self.act = torch.empty(self.I, **h16)
         self.down = torch.empty(self.H, **h16)
-        self.logits = torch.empty(self.V, **h16)
+        self.logits = torch.empty(self.V_full, **h16)   # full vocabulary on every rank
+        self.logits_local = self.logits if self.tp == 1 else torch.empty(self.V, **h16)
         self.graph = None
         self.host_pos = 0
         self.set_attention_partition(cfg.max_ctx)
@@ -187,7 +202,9 @@ class Model:
         mode = self.cfg.step_kernel
         G = self.cfg.group
         fits = all(k % 128 == 0 and k % G == 0 and (k // G) % 4 == 0 for k in (self.H, self.n_q * self.D, self.I))
-        self.persistent = mode == "persistent" or (mode == "auto" and self.cfg.fused and fits
+        if mode == "persistent" and self.tp > 1:
+            raise ValueError("step_kernel='persistent' is single-GPU; tensor-parallel steps use one launch per operator")
+        self.persistent = mode == "persistent" or (mode == "auto" and self.cfg.fused and fits and self.tp == 1
                                                    and self.ctx_cap <= PERSISTENT_MAX_CTX)
         if mode == "persistent" and not fits:
             raise ValueError("step_kernel='persistent' needs every K (hidden, heads*head_dim, intermediate) to hold a "
@@ -252,6 +269,11 @@ class Model:
         s, r, w, pf = self.gemv_cfg(lin)
         self.K.gemv_w4a16(s, r, w, pf, lin.packed, lin.sz, x, y, self.cfg.group)
 
+    def all_reduce(self, t):
+        """Sum the partial outputs of a column-split projection over the TP ranks (NCCL, in stream, capturable)."""
+        if self.tp > 1:
+            torch.distributed.all_reduce(t, group=self.cfg.tp_group)
+
     def add_norm(self, delta, w):
         if self.cfg.fused:
             self.K.add_rmsnorm(self.x, delta, w, self.normed, self.eps)
@@ -295,13 +317,17 @@ class Model:
             self.linear(lw["qkv"], self.normed, self.qkv)
             self.attention(li)
             self.linear(lw["o"], self.attn.view(-1), self.o)
+            self.all_reduce(self.o)
             self.add_norm(self.o, lw["ln2"])
             self.linear(lw["gu"], self.normed, self.gu)
             self.swiglu()
             self.linear(lw["down"], self.act, self.down)
+            self.all_reduce(self.down)
             delta = self.down
         self.add_norm(delta, self.norm_f)
-        self.linear(self.lm_head, self.normed, self.logits)
+        self.linear(self.lm_head, self.normed, self.logits_local)
+        if self.tp > 1:   # every rank gathers the whole vocabulary and takes the same argmax: no broadcast needed
+            torch.distributed.all_gather_into_tensor(self.logits, self.logits_local, group=self.cfg.tp_group)
         self.K.argmax(self.logits, self.tok, self.pos, self.history)
 
     def capture(self):
@@ -348,7 +374,7 @@ class Model:
         tokens = torch.as_tensor(tokens).long()
         if tokens.device.type != "cuda":
             tokens = (tokens.pin_memory() if tokens.numel() else tokens).to(self.tok.device, non_blocking=True)
-        out = torch.empty(len(tokens), self.V, dtype=torch.half, device=self.tok.device) if collect_logits else None
+        out = torch.empty(len(tokens), self.V_full, dtype=torch.half, device=self.tok.device) if collect_logits else None
         for i in range(len(tokens)):
             self.tok.copy_(tokens[i:i + 1])
             self.run_step(use_graph)
