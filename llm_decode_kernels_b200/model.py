@@ -334,6 +334,11 @@ class Model:
         """Capture step() into a CUDA graph (two warm-up steps on a side stream first, as torch requires).
         Warm-up runs at positions 0 and 1 (reference runtime/model.py:235-251); the token, position, history
         entries and the KV page it touches are saved and put back, so capturing in mid-sequence loses nothing."""
+        if self.tp > 1:
+            # Capturing a step that contains NCCL collectives did not complete on the B200 pool this was developed on
+            # (both ranks stalled inside the capture); tensor-parallel steps are therefore launched eagerly.
+            self.graph = None
+            return
         saved_tok, saved_pos, saved_hist = self.tok.clone(), self.pos.clone(), self.history[:2].clone()
         page0 = int(self.bt[0])
         saved_kv = self.kv[:, :, page0].clone()
