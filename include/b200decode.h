@@ -87,6 +87,16 @@ int b200_paged_attention_batched(const void* q, const void* kc, const void* vc, 
                                  const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
                                  float* o_part, float* m_part, float* l_part, void* out, void* stream);
 
+/* b200_paged_attention for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * callers always allocate the partial buffers with torch, runtime/model.py:148-150). The split-K partials go to a
+ * fixed array inside the library (about 1 MB per GPU, held until the process exits) instead of caller scratch:
+ * n_q <= 64, max_splits <= 32, D in {64, 128}, one sequence; anything larger returns B200_ERR_LIMIT. The first call
+ * on a device looks up the array's address (cudaGetSymbolAddress), so make that first call outside any stream
+ * capture. All calls on a device share the array: do not let two of them overlap on the GPU. No cudaMalloc, cudaFree
+ * or other allocating call is made. q [n_q, D]; kc, vc [pages, n_kv, 2^log2P, D]; out [n_q, D]. */
+int b200_paged_attention_noalloc(const void* q, const void* kc, const void* vc, const int* bt, const int* pos, int n_q,
+                                 int n_kv, int D, int log2P, int PS, int max_splits, void* out, void* stream);
+
 /* Batched, head_dim-generic form of b200_rope_append. qkv [B, (n_q + 2 n_kv) D]; bt [B, bt_stride]; pos [B];
  * cos_t, sin_t fp32 [max_pos, D/2]. D even, D <= 256. */
 int b200_rope_append_batched(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt,

@@ -252,3 +252,54 @@ cudaError_t paged_attention_dispatch(const void* q, const void* kc, const void* 
 }
 
 }  // namespace b200
+
+// ---- attention without any allocation by the caller --------------------------------------------------------------------
+// b200_paged_attention needs three scratch arrays for the split-K partials, and its callers get them from
+// cudaMalloc (or torch). Some callers cannot allocate device memory at all: a plugin running inside a host
+// application that owns the allocator and hands out nothing, code on a latency-critical path where an allocation may
+// synchronise the device, a process whose memory budget was fixed at start-up. For them the partials live in this
+// file-scope device array instead. Every GPU that loads the library holds it until the process exits.
+//   capacity: 64 query heads x 32 splits x head_dim 128 (about 1 MB), one sequence per call.
+// The array is shared by every call on the device and keeps whatever the previous call left; nothing in it has to
+// start at zero (the combine step reads only the slots the partial kernel of the same call has just written), so it
+// is never cleared. Two calls that overlap on the GPU (different streams) would overwrite each other's partials.
+#include "../../include/b200decode.h"
+
+namespace {
+constexpr int kNoAllocMaxHeads = 64, kNoAllocMaxSplits = 32, kNoAllocMaxD = 128;
+constexpr size_t kNoAllocO = (size_t)kNoAllocMaxHeads * kNoAllocMaxSplits * kNoAllocMaxD;
+constexpr size_t kNoAllocML = (size_t)kNoAllocMaxHeads * kNoAllocMaxSplits;
+static __device__ __align__(256) float g_attn_scratch[kNoAllocO + 2 * kNoAllocML];
+
+constexpr int kMaxDevices = 64;
+float* g_attn_scratch_ptr[kMaxDevices] = {};   // device address of the array, per device, filled on first use
+}  // namespace
+
+extern "C" int b200_paged_attention_noalloc(const void* q, const void* kc, const void* vc, const int* bt, const int* pos,
+                                            int n_q, int n_kv, int D, int log2P, int PS, int max_splits, void* out,
+                                            void* stream) {
+  if (!q || !kc || !vc || !bt || !pos || !out || n_q <= 0 || n_kv <= 0 || PS <= 0 || max_splits <= 0 || log2P < 0 ||
+      log2P >= 16)
+    return B200_ERR_ARG;
+  if ((D != 64 && D != 128) || n_q % n_kv) return B200_ERR_SHAPE;
+  const int hpg = n_q / n_kv;
+  if (hpg != 1 && hpg != 2 && hpg != 4 && hpg != 8) return B200_ERR_SHAPE;
+  if (n_q > kNoAllocMaxHeads || max_splits > kNoAllocMaxSplits || D > kNoAllocMaxD) return B200_ERR_LIMIT;
+  if ((reinterpret_cast<uintptr_t>(kc) & 15u) || (reinterpret_cast<uintptr_t>(vc) & 15u)) return B200_ERR_ALIGN;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_ERR_LAUNCH;
+  if (!g_attn_scratch_ptr[dev]) {
+    // In host code `g_attn_scratch` is only a handle for the symbol, not a device address: ask the runtime for the
+    // address on the current device, once per device.
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_scratch) != cudaSuccess || !p) return B200_ERR_LAUNCH;
+    g_attn_scratch_ptr[dev] = p;
+  }
+  float* o_part = g_attn_scratch_ptr[dev];
+  float* m_part = o_part + (size_t)n_q * max_splits * D;
+  float* l_part = m_part + (size_t)n_q * max_splits;
+  const cudaError_t e = b200::paged_attention_dispatch(q, kc, vc, bt, 1 << 30, pos, 1, n_q, n_kv, D, log2P, PS,
+                                                       max_splits, o_part, m_part, l_part, out,
+                                                       reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}

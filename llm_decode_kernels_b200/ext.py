@@ -36,6 +36,8 @@ SIGNATURES = {
                          c_void_p],
     "b200_paged_attention_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "b200_paged_attention_noalloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_void_p, c_void_p],
     "b200_rope_append_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_void_p],
     "b200_dequant_w4a16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -231,6 +233,19 @@ class Ops:
             q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bt.shape[1], pos.data_ptr(), B, n_q,
             kc.shape[1], D, _ilog2_exact(kc.shape[2], "page size"), int(part_size), S, o_part.data_ptr(),
             m_part.data_ptr(), l_part.data_ptr(), out.data_ptr(), _stream()), "paged_attention_batched")
+
+    def paged_attention_noalloc(self, q, kc, vc, bt, pos, part_size, max_splits, out):
+        """paged_attention without caller scratch, for callers that cannot allocate: the split-K partials live in a
+        fixed ~1 MB array inside the library (n_q <= 64, max_splits <= 32, one sequence, head_dim 64 or 128). Calls on
+        one device share that array and must not overlap; make the first call before any stream capture."""
+        for t, n in ((q, "q"), (kc, "kc"), (vc, "vc"), (out, "out")):
+            _cuda(t, n, torch.float16)
+        _cuda(bt, "bt", torch.int32), _cuda(pos, "pos", torch.int32)
+        D = kc.shape[3]
+        self._check(self.lib.b200_paged_attention_noalloc(
+            q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), pos.data_ptr(), q.numel() // D, kc.shape[1], D,
+            _ilog2_exact(kc.shape[2], "page size"), int(part_size), int(max_splits), out.data_ptr(), _stream()),
+            "paged_attention_noalloc")
 
     def rope_append_batched(self, qkv, cos_t, sin_t, pos, bt, kc, vc, n_q, n_kv):
         """qkv [B, (n_q + 2 n_kv) * D]; bt int32 [B, max_pages]; pos int32 [B]; D = 2 * cos_t.shape[1]."""
