@@ -93,6 +93,63 @@ DEVI void unpack8(uint4 v, float* f) {
   }
 }
 
+// ---- inner product on masked nibbles (used by the persistent step kernel and the segmented GEMV) ------------------
+// A nibble masked in place is an fp16 SUBNORMAL: bits 0..3 of a half are q * 2^-24, bits 4..7 are q * 2^-20. So
+// (word & 0x000F000F) and (word & 0x00F000F0) are ready-made half2 operands and one shift by 8 exposes the other four
+// nibbles. x is staged multiplied by 2^s (pairs under the low mask) or 2^(s-4) (pairs under the high mask), s chosen
+// from max|x| so nothing overflows; every product is then q * x * 2^(s-24). With xs = sum of x over a 32-weight chunk,
+//     sum (q - z) * scale * x = scale * (2^(24-s) * sum q x'  -  z * xs),
+// so the zero point costs one FMA per chunk instead of one subtraction per weight.
+// 16-byte chunk ci of x lives at swz(ci): a lane of the GEMV reads the four consecutive chunks 4u..4u+3 for its
+// weight chunk u = lane, and without the swizzle those reads would be 64 bytes apart across lanes (4-way conflicts).
+DEVI int swz(int ci) { return (ci & ~3) | ((ci & 3) ^ ((ci >> 3) & 3)); }
+
+struct XScale { half2 lo, hi; float resc; };
+// Power-of-two staging scale from max|x|: x * 2^s stays below 2^15.
+DEVI XScale scale_for(float xmax) {
+  int s = 14 - ilogbf(fmaxf(xmax, 1e-30f));
+  s = max(-10, min(15, s));
+  XScale r;
+  r.lo = __float2half2_rn(exp2f((float)s));
+  r.hi = __float2half2_rn(exp2f((float)(s - 4)));
+  r.resc = exp2f((float)(24 - s));
+  return r;
+}
+
+// One packed word (8 weights) of each of two rows against the 8 staged activations x = (x01, x23, x45, x67).
+// Four independent half2 accumulators per row (one per nibble position): short chains, so fp16 rounding stays small
+// and the FMAs of one word do not wait on each other.
+DEVI void fma_word2(uint32_t wa, uint32_t wb, uint4 x, half2* a, half2* b) {
+  const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+  a[0] = __hfma2(as_h2(wa & 0x000F000Fu), as_h2(x.x), a[0]);
+  b[0] = __hfma2(as_h2(wb & 0x000F000Fu), as_h2(x.x), b[0]);
+  a[1] = __hfma2(as_h2(wa & 0x00F000F0u), as_h2(x.y), a[1]);
+  b[1] = __hfma2(as_h2(wb & 0x00F000F0u), as_h2(x.y), b[1]);
+  a[2] = __hfma2(as_h2(wa8 & 0x000F000Fu), as_h2(x.z), a[2]);
+  b[2] = __hfma2(as_h2(wb8 & 0x000F000Fu), as_h2(x.z), b[2]);
+  a[3] = __hfma2(as_h2(wa8 & 0x00F000F0u), as_h2(x.w), a[3]);
+  b[3] = __hfma2(as_h2(wb8 & 0x00F000F0u), as_h2(x.w), b[3]);
+}
+
+// The 32 staged activations of one weight chunk, held in registers, plus their unscaled sum.
+struct XChunk { uint4 x0, x1, x2, x3; float xs; };
+
+// One 32-weight chunk of two rows (packed words wa, wb; (scale, zero) sa, sb) against x: this lane's share of both
+// dot products.
+DEVI void chunk_two_rows(uint4 wa, uint4 wb, half2 sza, half2 szb, const XChunk& x, float resc, float& p0, float& p1) {
+  const half2 zero2 = __float2half2_rn(0.f);
+  const float2 sa = __half22float2(sza), sb = __half22float2(szb);
+  half2 a[4] = {zero2, zero2, zero2, zero2}, b[4] = {zero2, zero2, zero2, zero2};
+  fma_word2(wa.x, wb.x, x.x0, a, b);
+  fma_word2(wa.y, wb.y, x.x1, a, b);
+  fma_word2(wa.z, wb.z, x.x2, a, b);
+  fma_word2(wa.w, wb.w, x.x3, a, b);
+  const float2 fa0 = __half22float2(__hadd2(a[0], a[2])), fa1 = __half22float2(__hadd2(a[1], a[3]));
+  const float2 fb0 = __half22float2(__hadd2(b[0], b[2])), fb1 = __half22float2(__hadd2(b[1], b[3]));
+  p0 = fmaf(sa.x, fmaf((fa0.x + fa0.y) + (fa1.x + fa1.y), resc, -sa.y * x.xs), p0);
+  p1 = fmaf(sb.x, fmaf((fb0.x + fb0.y) + (fb1.x + fb1.y), resc, -sb.y * x.xs), p1);
+}
+
 // Order key for greedy argmax over fp16 logits: larger value wins, then the lower index. One max-reduction
 // over these keys settles value and tie-break together.
 DEVI unsigned long long argmax_key(half v, int idx) {

@@ -127,6 +127,191 @@ __global__ void dequant_w4a16_kernel(const uint32_t* __restrict__ Wp, const half
   out[i] = o;
 }
 
+// ---- segmented GEMV: the library's default ------------------------------------------------------------------------------
+// Same arithmetic as the GEMV phases of the persistent step kernel (masked nibbles as fp16 subnormals, zero point
+// folded into one FMA per chunk; see common.cuh), laid out for one launch per matrix:
+//   * a CTA of 8 warps owns a tile of consecutive units (unit = two consecutive rows);
+//   * a row is cut into segments of 32 chunks (1024 weights); warp w works on segment w mod segs for the whole tile,
+//     lane l on chunk l of it, so the lane's 32 activations are read from shared memory once per tile and stay in
+//     registers; the warps sharing a segment take the tile's units round robin, two units (four rows) per trip;
+//   * weights come straight from global memory with 128-bit streaming loads, the next trip's four loads issued before
+//     the current trip's arithmetic; (scale, zero) words through the read-only cache;
+//   * four partial sums per trip are reduced with 7 shuffles into shared memory; after one barrier per tile a thread
+//     per unit adds the segments in order and stores two fp16 results.
+// x is staged by every CTA itself: max|x| -> power-of-two scale -> scaled copy + per-chunk sums (4-16 KB from L2).
+constexpr int kSegWarps = 8, kSegThreads = kSegWarps * 32;
+
+struct SegRows { uint4 a0, a1, b0, b1; half2 za0, za1, zb0, zb1; };
+
+__global__ void __launch_bounds__(kSegThreads)
+gemv_w4a16_seg_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ, const uint2* __restrict__ X,
+                      half* __restrict__ y, int N, int K, int log2G, int tile_units) {
+  extern __shared__ __align__(16) uint8_t seg_smem[];
+  const int U = K >> 5, ng = K >> log2G, segs = (U + 31) >> 5;
+  uint4* xin = reinterpret_cast<uint4*>(seg_smem);                       // [K/8] scaled, swizzled
+  float* xsum = reinterpret_cast<float*>(seg_smem + (size_t)K * 2);      // [U]
+  float* part = xsum + U;                                                 // [tile_units * 2][segs]
+  __shared__ float red[kSegWarps];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- this CTA's tile and this warp's share of it
+  const int units = (N + 1) >> 1;
+  const int ub = blockIdx.x * tile_units, ue = min(units, ub + tile_units);
+  if (ub >= ue) return;   // (CTA-uniform: taken by all threads or none, before any barrier)
+  const int seg_first = warp % segs;                     // segs <= 8: one segment per warp; else several, strided
+  const bool resident = segs <= kSegWarps;
+  const int group = resident ? (kSegWarps - seg_first + segs - 1) / segs : 1;
+  const int rank = resident ? warp / segs : 0;
+  const size_t rowU = (size_t)U;
+
+  auto x_of = [&](int u) {
+    const int sw = (u >> 1) & 3;
+    XChunk r;
+    r.x0 = xin[4 * u + (0 ^ sw)]; r.x1 = xin[4 * u + (1 ^ sw)]; r.x2 = xin[4 * u + (2 ^ sw)]; r.x3 = xin[4 * u + (3 ^ sw)];
+    r.xs = xsum[u];
+    return r;
+  };
+  // ---- staging of x (run by the whole CTA, once, after the first weight loads have been issued)
+  XScale sc;
+  auto stage_x_all = [&]() {
+    uint2* raw = reinterpret_cast<uint2*>(xin);
+    float mx = 0.f;
+    for (int g = tid; g < (K >> 2); g += kSegThreads) {
+      const uint2 v = __ldg(X + g);
+      raw[2 * swz(g >> 1) + (g & 1)] = v;
+      const float2 a = __half22float2(__habs2(as_h2(v.x))), b = __half22float2(__habs2(as_h2(v.y)));
+      mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)));
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    float xmax = 0.f;
+  #pragma unroll
+    for (int k = 0; k < kSegWarps; ++k) xmax = fmaxf(xmax, red[k]);
+    sc = scale_for(xmax);
+    const int ngran = K >> 2;
+    for (int g0 = 0; g0 < ngran; g0 += kSegThreads) {   // whole warps take part in the shuffles below
+      const int g = g0 + tid;
+      const bool live = g < ngran;
+      const uint2 v = live ? raw[2 * swz(g >> 1) + (g & 1)] : make_uint2(0u, 0u);
+      const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
+      float sm = (a.x + a.y) + (b.x + b.y);
+      sm += __shfl_xor_sync(0xffffffffu, sm, 1);
+      sm += __shfl_xor_sync(0xffffffffu, sm, 2);
+      sm += __shfl_xor_sync(0xffffffffu, sm, 4);
+      if (live && (tid & 7) == 0) xsum[g >> 3] = sm;
+      uint2 o;
+      o.x = as_u32(__hmul2(as_h2(v.x), sc.lo));
+      o.y = as_u32(__hmul2(as_h2(v.y), sc.hi));
+      if (live) raw[2 * swz(g >> 1) + (g & 1)] = o;
+    }
+    __syncthreads();
+
+  };
+
+  const int nu = ue - ub;
+  bool staged = false;
+  for (int seg = seg_first; seg < segs; seg += kSegWarps) {
+    const int u = 32 * seg + lane;
+    const bool act = u < U;
+    const int uc = act ? u : U - 1, g = (uc << 5) >> log2G;
+    // Running pointers to row 0 of the trip's two units; a trip advances them by 2 * group units = 4 * group rows.
+    // Loads are predicated on the unit being inside the tile (and the odd row inside the matrix), so no clamping.
+    const size_t wstep = (size_t)4 * group * rowU, zstep = (size_t)4 * group * ng;
+    const uint4* wa = Wp + (size_t)(2 * (ub + rank)) * rowU + uc;
+    const half2* za = SZ + (size_t)(2 * (ub + rank)) * ng + g;
+    const uint4* wb = wa + (size_t)2 * group * rowU;
+    const half2* zb = za + (size_t)2 * group * ng;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    const half2 zeroh = __float2half2_rn(0.f);
+    const int last_row = N - 1;
+
+#define SEG_LOAD(R, j)                                                                           \
+  {                                                                                              \
+    const bool ua_ = (j) < nu, ub_ = (j) + group < nu;                                           \
+    const bool ua1_ = ua_ && 2 * (ub + (j)) + 1 <= last_row;                                     \
+    const bool ub1_ = ub_ && 2 * (ub + (j) + group) + 1 <= last_row;                             \
+    R.a0 = ua_ ? ld_stream(wa) : zero4;                                                          \
+    R.a1 = ua1_ ? ld_stream(wa + rowU) : zero4;                                                  \
+    R.b0 = ub_ ? ld_stream(wb) : zero4;                                                          \
+    R.b1 = ub1_ ? ld_stream(wb + rowU) : zero4;                                                  \
+    R.za0 = ua_ ? __ldg(za) : zeroh;                                                             \
+    R.za1 = ua1_ ? __ldg(za + ng) : zeroh;                                                       \
+    R.zb0 = ub_ ? __ldg(zb) : zeroh;                                                             \
+    R.zb1 = ub1_ ? __ldg(zb + ng) : zeroh;                                                       \
+    wa += wstep; wb += wstep; za += zstep; zb += zstep;                                          \
+  }
+#define SEG_TRIP(R, j)                                                                           \
+  {                                                                                              \
+    float p0 = 0.f, p1 = 0.f, q0 = 0.f, q1 = 0.f;                                                \
+    if (act) {                                                                                   \
+      chunk_two_rows(R.a0, R.a1, R.za0, R.za1, x, sc.resc, p0, p1);                              \
+      if ((j) + group < nu) chunk_two_rows(R.b0, R.b1, R.zb0, R.zb1, x, sc.resc, q0, q1);        \
+    }                                                                                            \
+    const int qd = lane >> 3; /* 4 sums with 7 shuffles: quarter qd of the warp ends up holding value qd */ \
+    float v0 = (qd & 2) ? q0 : p0, v1 = (qd & 2) ? q1 : p1;                                      \
+    const float o0 = (qd & 2) ? p0 : q0, o1 = (qd & 2) ? p1 : q1;                                \
+    v0 += __shfl_xor_sync(0xffffffffu, o0, 16);                                                  \
+    v1 += __shfl_xor_sync(0xffffffffu, o1, 16);                                                  \
+    float v = (qd & 1) ? v1 : v0;                                                                \
+    v += __shfl_xor_sync(0xffffffffu, (qd & 1) ? v0 : v1, 8);                                    \
+    v += __shfl_xor_sync(0xffffffffu, v, 4);                                                     \
+    v += __shfl_xor_sync(0xffffffffu, v, 2);                                                     \
+    v += __shfl_xor_sync(0xffffffffu, v, 1);                                                     \
+    const int jj = (j) + ((qd & 2) ? group : 0);                                                 \
+    if ((lane & 7) == 0 && jj < nu) part[(jj * 2 + (qd & 1)) * segs + seg] = v;                  \
+  }
+
+    // two register buffers used alternately: the loads of the next trip are in flight during the arithmetic of this
+    // one, and no buffer is ever copied
+    SegRows r0, r1;
+    int j = rank;
+    if (j < nu) SEG_LOAD(r0, j);
+    if (!staged) {   // the weights just requested travel while x is staged (two barriers, one L2 round trip)
+      stage_x_all();
+      staged = true;
+    }
+    const XChunk x = x_of(uc);
+    for (; j < nu; j += 4 * group) {
+      const int j1 = j + 2 * group;
+      if (j1 < nu) SEG_LOAD(r1, j1);
+      SEG_TRIP(r0, j);
+      if (j1 < nu) {
+        if (j1 + 2 * group < nu) SEG_LOAD(r0, j1 + 2 * group);
+        SEG_TRIP(r1, j1);
+      }
+    }
+#undef SEG_LOAD
+#undef SEG_TRIP
+  }
+  __syncthreads();
+  for (int i = tid; i < nu; i += kSegThreads) {
+    float y0 = 0.f, y1 = 0.f;
+    for (int k = 0; k < segs; ++k) { y0 += part[(2 * i) * segs + k]; y1 += part[(2 * i + 1) * segs + k]; }
+    const int row0 = 2 * (ub + i);
+    if (row0 + 1 < N) *reinterpret_cast<half2*>(y + row0) = __floats2half2_rn(y0, y1);
+    else y[row0] = __float2half(y0);
+  }
+}
+
+static cudaError_t launch_seg(const void* Wp, const void* SZ, const void* x, void* y, int N, int K, int log2G,
+                              cudaStream_t st) {
+  const int units = (N + 1) / 2, U = K >> 5, segs = (U + 31) / 32;
+  int tile = (units + 2 * kNumSMs - 1) / (2 * kNumSMs);   // one wave of two CTAs per SM ...
+  tile = tile < 8 ? 8 : (tile > 512 ? 512 : tile);          // ... but at least 16 rows
+  const int blocks = (units + tile - 1) / tile;
+  const size_t smem = (size_t)K * 2 + (size_t)U * 4 + (size_t)tile * 2 * segs * 4;
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_seg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  gemv_w4a16_seg_kernel<<<blocks, kSegThreads, smem, st>>>((const uint4*)Wp, (const half2*)SZ, (const uint2*)x, (half*)y,
+                                                           N, K, log2G, tile);
+  return cudaPeekAtLastError();
+}
+
 template <int R, int UNR>
 static cudaError_t launch_rows(const void* Wp, const void* SZ, const void* x, void* y, int N, int K, int log2G,
                                int warps, cudaStream_t st) {
@@ -143,9 +328,8 @@ static cudaError_t launch_rows(const void* Wp, const void* SZ, const void* x, vo
   return cudaPeekAtLastError();
 }
 
-// stage 0: plain kernel. stage >= 1 with R in {1,2,4,8} and warps in 1..8: that configuration.
-// Anything else (R == 0): a shape-based choice - enough warps to cover 148 SMs several times over for
-// small N, more rows per warp (fewer reads of x from shared memory per weight byte) for large N.
+// stage 0: plain kernel. stage >= 1 with R in {1,2,4,8} and warps in 1..8: the row-per-warp kernel in that
+// configuration. Anything else (R == 0): the segmented kernel.
 cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, const void* SZ, const void* x, void* y,
                                 int N, int K, int log2G, cudaStream_t st) {
   if (stage == 0) {
@@ -155,9 +339,10 @@ cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, con
     return cudaPeekAtLastError();
   }
   if (!(R == 1 || R == 2 || R == 4 || R == 8) || warps < 1 || warps > 8) {
-    if (N >= 16384) { R = 4; warps = 8; }
-    else if (N >= 4096) { R = 2; warps = 8; }
-    else { R = 2; warps = 4; }
+    if ((reinterpret_cast<uintptr_t>(y) & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0)
+      return launch_seg(Wp, SZ, x, y, N, K, log2G, st);   // the library's own choice: the segmented kernel
+    R = 2;   // y not 4-byte aligned (the segmented kernel stores row pairs): row-per-warp kernel
+    warps = 4;
   }
   switch (R) {
     case 1: return launch_rows<1, 4>(Wp, SZ, x, y, N, K, log2G, warps, st);
