@@ -53,7 +53,11 @@ int b200_bw_read(const void* p, size_t bytes, void* sink, int blocks, int thread
  * q [n_q, 64]; kc, vc [pages, n_kv, 2^log2P, 64] (16B); bt int32 [pages]; pos int32 [1] on the device, context
  * = pos + 1; PS = tokens per split; scratch o_part fp32 [n_q, max_splits, 64], m_part, l_part fp32
  * [n_q, max_splits]; out [n_q, 64]. n_q / n_kv in {1,2,4,8}. Tokens beyond max_splits * PS are ignored.
- * `version` (1..3 in the reference) is accepted and ignored: there is one implementation. */
+ * `version` (1..3, as in the reference, whose three versions are three generations of its kernel) selects the kernel:
+ * 1 = K/V by register loads (any page and split size); 2 = K/V pages pulled into a shared-memory ring by bulk async
+ * copies, arithmetic on the fp32 pipes; 3 = the same ring with both contractions as warp-level tensor-core MMAs
+ * (the fastest; with 8 query heads per KV head the fp32 pipes cannot keep up with HBM). 2 and 3 need pages of 8..64
+ * tokens and PS a multiple of the page size and otherwise run as 1. All three meet the same tolerance. */
 int b200_paged_attention(int version, const void* q, const void* kc, const void* vc, const int* bt, const int* pos,
                          int n_q, int n_kv, int log2P, int PS, int max_splits, float* o_part, float* m_part,
                          float* l_part, void* out, void* stream);
@@ -86,6 +90,19 @@ int b200_bw_read_bulk(const void* p, size_t bytes, void* sink, int blocks, int s
 int b200_paged_attention_batched(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
                                  const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
                                  float* o_part, float* m_part, float* l_part, void* out, void* stream);
+
+/* b200_paged_attention_batched with the kernel chosen by `version` (0 = the library's choice, which is what
+ * b200_paged_attention_batched runs; 1..3 as for b200_paged_attention). */
+int b200_paged_attention_batched_v(int version, const void* q, const void* kc, const void* vc, const int* bt,
+                                   int bt_stride, const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS,
+                                   int max_splits, float* o_part, float* m_part, float* l_part, void* out,
+                                   void* stream);
+
+/* Health word of the attention kernels on the current device (no counterpart in the reference): *code = 0, or 1 once
+ * a thread block gave up a bounded wait for its own asynchronous copies, in which case the outputs of that call are
+ * invalid. Every wait inside the library is bounded; this is how a caller learns that one ran out. Synchronises the
+ * device. */
+int b200_paged_attention_status(int* code);
 
 /* b200_paged_attention for callers that cannot allocate device memory (no counterpart in the reference, whose
  * callers always allocate the partial buffers with torch, runtime/model.py:148-150). The split-K partials go to a

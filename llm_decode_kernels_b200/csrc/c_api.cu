@@ -27,7 +27,8 @@ cudaError_t bw_read_bulk_dispatch(const void* p, size_t bytes, void* sink, int b
                                   cudaStream_t st);
 cudaError_t repack_stream_dispatch(const void* W, const void* SZ, void* out, int N, int K, int log2G, int gu, int ncta,
                                    int stage_w, cudaStream_t st);
-cudaError_t paged_attention_dispatch(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
+cudaError_t paged_attention_status(int* code);
+cudaError_t paged_attention_dispatch(int version, const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
                                      const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS,
                                      int max_splits, float* o_part, float* m_part, float* l_part, void* out,
                                      cudaStream_t st);
@@ -94,12 +95,12 @@ int b200_bw_read_bulk(const void* p, size_t bytes, void* sink, int blocks, int s
   return finish(b200::bw_read_bulk_dispatch(p, bytes, sink, blocks, stage_bytes, stages, S(stream)));
 }
 
-int b200_paged_attention_batched(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
-                                 const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
-                                 float* o_part, float* m_part, float* l_part, void* out, void* stream) {
+static int attention_entry(int version, const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
+                           const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
+                           float* o_part, float* m_part, float* l_part, void* out, void* stream) {
   REQUIRE(q && kc && vc && bt && pos && out, B200_ERR_ARG);
   REQUIRE(B > 0 && B <= 65535 && n_q > 0 && n_kv > 0 && PS > 0 && max_splits > 0 && max_splits <= 65535 &&
-              bt_stride > 0 && log2P >= 0 && log2P < 16,
+              bt_stride > 0 && log2P >= 0 && log2P < 16 && version >= 0 && version <= 3,
           B200_ERR_ARG);
   REQUIRE(max_splits == 1 || (o_part && m_part && l_part), B200_ERR_ARG);
   REQUIRE(D == 64 || D == 128, B200_ERR_SHAPE);
@@ -107,16 +108,36 @@ int b200_paged_attention_batched(const void* q, const void* kc, const void* vc, 
   const int hpg = n_q / n_kv;
   REQUIRE(hpg == 1 || hpg == 2 || hpg == 4 || hpg == 8, B200_ERR_SHAPE);
   REQUIRE(aligned16(kc) && aligned16(vc), B200_ERR_ALIGN);
-  return finish(b200::paged_attention_dispatch(q, kc, vc, bt, bt_stride, pos, B, n_q, n_kv, D, log2P, PS, max_splits,
-                                               o_part, m_part, l_part, out, S(stream)));
+  return finish(b200::paged_attention_dispatch(version, q, kc, vc, bt, bt_stride, pos, B, n_q, n_kv, D, log2P, PS,
+                                               max_splits, o_part, m_part, l_part, out, S(stream)));
+}
+
+int b200_paged_attention_batched(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
+                                 const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
+                                 float* o_part, float* m_part, float* l_part, void* out, void* stream) {
+  return attention_entry(0, q, kc, vc, bt, bt_stride, pos, B, n_q, n_kv, D, log2P, PS, max_splits, o_part, m_part,
+                         l_part, out, stream);
+}
+
+int b200_paged_attention_batched_v(int version, const void* q, const void* kc, const void* vc, const int* bt,
+                                   int bt_stride, const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS,
+                                   int max_splits, float* o_part, float* m_part, float* l_part, void* out,
+                                   void* stream) {
+  return attention_entry(version, q, kc, vc, bt, bt_stride, pos, B, n_q, n_kv, D, log2P, PS, max_splits, o_part,
+                         m_part, l_part, out, stream);
 }
 
 int b200_paged_attention(int version, const void* q, const void* kc, const void* vc, const int* bt, const int* pos,
                          int n_q, int n_kv, int log2P, int PS, int max_splits, float* o_part, float* m_part,
                          float* l_part, void* out, void* stream) {
   REQUIRE(version >= 1 && version <= 3, B200_ERR_ARG);
-  return b200_paged_attention_batched(q, kc, vc, bt, 1 << 30, pos, 1, n_q, n_kv, 64, log2P, PS, max_splits, o_part,
-                                      m_part, l_part, out, stream);
+  return attention_entry(version, q, kc, vc, bt, 1 << 30, pos, 1, n_q, n_kv, 64, log2P, PS, max_splits, o_part, m_part,
+                         l_part, out, stream);
+}
+
+int b200_paged_attention_status(int* code) {
+  REQUIRE(code, B200_ERR_ARG);
+  return finish(b200::paged_attention_status(code));
 }
 
 int b200_add_rmsnorm(void* x, const void* delta, const void* w, void* out, int H, float eps, void* stream) {

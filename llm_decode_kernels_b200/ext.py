@@ -36,6 +36,10 @@ SIGNATURES = {
                          c_void_p],
     "b200_paged_attention_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "b200_paged_attention_batched_v": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                       c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p],
+    "b200_paged_attention_status": [c_void_p],
     "b200_paged_attention_noalloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_void_p, c_void_p],
     "b200_rope_append_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
@@ -212,9 +216,9 @@ class Ops:
                                               _ilog2_exact(kc.shape[2], "page size"), _stream()), "rope_append")
 
     # ---- additions ----------------------------------------------------------------------------------------
-    def paged_attention_batched(self, q, kc, vc, bt, pos, part_size, o_part, m_part, l_part, out):
+    def paged_attention_batched(self, q, kc, vc, bt, pos, part_size, o_part, m_part, l_part, out, version=0):
         """q [B, n_q, D]; bt int32 [B, max_pages]; pos int32 [B]; o_part [B, n_q, S, D]; m/l_part [B, n_q, S];
-        out [B, n_q, D]; D = 64 or 128."""
+        out [B, n_q, D]; D = 64 or 128. version: 0 the library's choice, 1..3 as for paged_attention."""
         for t, n in ((q, "q"), (kc, "kc"), (vc, "vc"), (out, "out")):
             _cuda(t, n, torch.float16)
         _cuda(bt, "bt", torch.int32), _cuda(pos, "pos", torch.int32)
@@ -229,10 +233,17 @@ class Ops:
         if tuple(o_part.shape) != (B, n_q, S, D) or tuple(m_part.shape) != (B, n_q, S) or m_part.shape != l_part.shape:
             raise RuntimeError("split buffers have inconsistent shapes")
         _aligned16(kc, "kc"), _aligned16(vc, "vc")
-        self._check(self.lib.b200_paged_attention_batched(
-            q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bt.shape[1], pos.data_ptr(), B, n_q,
+        self._check(self.lib.b200_paged_attention_batched_v(
+            int(version), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bt.shape[1], pos.data_ptr(), B, n_q,
             kc.shape[1], D, _ilog2_exact(kc.shape[2], "page size"), int(part_size), S, o_part.data_ptr(),
             m_part.data_ptr(), l_part.data_ptr(), out.data_ptr(), _stream()), "paged_attention_batched")
+
+    def paged_attention_status(self):
+        """0, or 1 once an attention block gave up a bounded wait for its own copies (outputs invalid). Synchronises."""
+        import ctypes
+        code = ctypes.c_int(-1)
+        self._check(self.lib.b200_paged_attention_status(ctypes.byref(code)), "paged_attention_status")
+        return code.value
 
     def paged_attention_noalloc(self, q, kc, vc, bt, pos, part_size, max_splits, out):
         """paged_attention without caller scratch, for callers that cannot allocate: the split-K partials live in a

@@ -52,6 +52,10 @@ class DecodeConfig:
     tp_rank: int = 0             # tensor parallelism: this process's rank ...
     tp_world: int = 1            # ... of this many (one process per GPU, torch.distributed initialised by the caller)
     tp_group: object = field(default=None, repr=False)   # process group of the TP ranks (None: the default group)
+    ablate: tuple = ()           # fusions switched off for ablation runs, any of "dequant" (dequantize the matrix to
+                                 # an fp16 buffer, then an fp16 matrix-vector product), "norm", "swiglu" (the two
+                                 # that fused=False switches off together) and "rope" (rotation and cache append as
+                                 # separate device ops); any entry implies one launch per operator
     step_kernel: str = "auto"    # "persistent": the whole step is one kernel (b200_decode_step); "multi": one launch
                                  # per operator, as the reference does; "auto": persistent when fused and the
                                  # prepared context cap is within PERSISTENT_MAX_CTX
@@ -163,6 +167,15 @@ class Model:
         self.logits_local = self.logits if self.tp == 1 else torch.empty(self.V, **h16)
         self.graph = None
         self.host_pos = 0
+        bad = set(cfg.ablate) - {"dequant", "norm", "swiglu", "rope"}
+        if bad:
+            raise ValueError(f"unknown ablation switch {sorted(bad)}")
+        self.off = set(cfg.ablate) | (set() if cfg.fused else {"norm", "swiglu"})
+        if "dequant" in self.off:   # one fp16 buffer large enough for the biggest matrix
+            mats = [lw[n] for lw in self.layers for n in ("qkv", "o", "gu", "down")] + [self.lm_head]
+            self.w_fp16 = torch.empty(max(m.N * m.K for m in mats), **h16)
+        if "rope" in self.off:
+            self.kv_heads = torch.arange(self.n_kv, device=dev)
         self.set_attention_partition(cfg.max_ctx)
 
     # ------------------------------------------------------------------ attention partitioning
@@ -204,13 +217,14 @@ class Model:
         fits = all(k % 128 == 0 and k % G == 0 and (k // G) % 4 == 0 for k in (self.H, self.n_q * self.D, self.I))
         if mode == "persistent" and self.tp > 1:
             raise ValueError("step_kernel='persistent' is single-GPU; tensor-parallel steps use one launch per operator")
-        self.persistent = mode == "persistent" or (mode == "auto" and self.cfg.fused and fits and self.tp == 1
+        self.persistent = mode == "persistent" or (mode == "auto" and not self.off and fits and self.tp == 1
                                                    and self.ctx_cap <= PERSISTENT_MAX_CTX)
         if mode == "persistent" and not fits:
             raise ValueError("step_kernel='persistent' needs every K (hidden, heads*head_dim, intermediate) to hold a "
                              "multiple of 4 quantization groups; use step_kernel='multi' for this shape")
-        if mode == "persistent" and not self.cfg.fused:
-            raise ValueError("step_kernel='persistent' computes the fused operators; it cannot run with fused=False")
+        if mode == "persistent" and self.off:
+            raise ValueError("step_kernel='persistent' computes the fused operators; it cannot run with fused=False or "
+                             "an ablation switch")
         if not self.persistent:
             return
         dev = self.cfg.device
@@ -266,6 +280,11 @@ class Model:
         return self.cfg.gemv_stage if self.cfg.gemv_stage is not None else (2, 0, 0, 0)
 
     def linear(self, lin: Linear, x, y):
+        if "dequant" in self.off:   # ablation: weights go through an fp16 copy in HBM (4.5x the bytes)
+            w16 = self.w_fp16[: lin.N * lin.K].view(lin.N, lin.K)
+            self.K.dequant_w4a16(lin.packed, lin.sz, w16, self.cfg.group)
+            torch.mv(w16, x, out=y)
+            return
         s, r, w, pf = self.gemv_cfg(lin)
         self.K.gemv_w4a16(s, r, w, pf, lin.packed, lin.sz, x, y, self.cfg.group)
 
@@ -275,7 +294,7 @@ class Model:
             torch.distributed.all_reduce(t, group=self.cfg.tp_group)
 
     def add_norm(self, delta, w):
-        if self.cfg.fused:
+        if "norm" not in self.off:
             self.K.add_rmsnorm(self.x, delta, w, self.normed, self.eps)
         else:  # the unfused op sequence, on the device (ablation)
             if delta is not None:
@@ -284,15 +303,34 @@ class Model:
             self.normed.copy_(w * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).half())
 
     def swiglu(self):
-        if self.cfg.fused:
+        if "swiglu" not in self.off:
             self.K.swiglu(self.gu, self.act)
         else:
             s = torch.nn.functional.silu(self.gu[: self.I].float()).half()
             torch.mul(s, self.gu[self.I:], out=self.act)
 
+    def rope_append_unfused(self, kc, vc):
+        """Ablation: rotate q and k and append k, v to the cache as separate device ops (same arithmetic as the fused
+        kernel: fp32 rotation of pairs (i, i + D/2), fp16 result; everything indexed by the device-resident pos)."""
+        nq, nkv, D = self.n_q, self.n_kv, self.D
+        c, s = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)       # [1, D/2]
+        qk = self.qkv[: (nq + nkv) * D].view(nq + nkv, D)
+        a, b = qk[:, : D // 2].float(), qk[:, D // 2:].float()
+        qk.copy_(torch.cat([a * c - b * s, b * c + a * s], dim=-1).half())
+        page = self.bt.index_select(0, self.pos // self.cfg.page).long().expand(nkv)
+        slot = (self.pos % self.cfg.page).long().expand(nkv)
+        kc.index_put_((page, self.kv_heads, slot), qk[nq:])
+        vc.index_put_((page, self.kv_heads, slot), self.qkv[(nq + nkv) * D:].view(nkv, D))
+
     def attention(self, li):
         kc, vc = self.kv[li, 0], self.kv[li, 1]
-        if self.D == 64:
+        if "rope" in self.off:
+            self.rope_append_unfused(kc, vc)
+            self.K.paged_attention_batched(self.qkv[: self.n_q * self.D].view(1, self.n_q, self.D), kc, vc,
+                                           self.bt.view(1, -1), self.pos, self.part_size, self.o_part.unsqueeze(0),
+                                           self.m_part.unsqueeze(0), self.l_part.unsqueeze(0),
+                                           self.attn.view(1, self.n_q, self.D))
+        elif self.D == 64:
             self.K.rope_append(self.qkv, self.cos, self.sin, self.pos, self.bt, kc, vc, self.n_q, self.n_kv)
             self.K.paged_attention(self.qkv[: self.n_q * self.D], kc, vc, self.bt, self.pos, self.part_size,
                                    self.o_part, self.m_part, self.l_part, self.attn, 3)

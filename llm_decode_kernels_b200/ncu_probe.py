@@ -1,7 +1,7 @@
 """Small, self-ending workloads to run under `ncu` (the reference has bench/ncu_probe.py for the same purpose).
 
     python -m llm_decode_kernels_b200.ncu_probe gemv  [--n 32000 --k 2048 --copies 8 --iters 3]
-    python -m llm_decode_kernels_b200.ncu_probe attn  [--ctx 8192 --batch 8 --iters 3]
+    python -m llm_decode_kernels_b200.ncu_probe attn  [--ctx 8192 --batch 8 --part 256 --version 0 --iters 3]
     python -m llm_decode_kernels_b200.ncu_probe step  [--layers 4 --tokens 4]
 
 gemv: `copies` distinct quantized matrices (together larger than the 126 MB L2) are multiplied in turn, so every
@@ -47,7 +47,7 @@ def probe_attn(a):
     m_part, l_part = torch.empty(a.batch, n_q, S, device="cuda"), torch.empty(a.batch, n_q, S, device="cuda")
     out = torch.empty(a.batch, n_q, D, dtype=torch.half, device="cuda")
     for _ in range(a.iters):
-        K.paged_attention_batched(q, kc, vc, bt, pos, PS, o_part, m_part, l_part, out)
+        K.paged_attention_batched(q, kc, vc, bt, pos, PS, o_part, m_part, l_part, out, version=a.version)
     torch.cuda.synchronize()
     print("attention bytes per launch:", 2 * a.ctx * n_kv * D * 2 * a.batch)
 
@@ -74,6 +74,7 @@ if __name__ == "__main__":
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--part", type=int, default=256)
+    ap.add_argument("--version", type=int, default=0, help="attention kernel: 0 library's choice, 1..3")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--tokens", type=int, default=4)
     ap.add_argument("--step-kernel", default="multi", choices=["multi", "persistent"])

@@ -168,7 +168,8 @@ def test_attention_odd_contexts(K, ctx):
     q = torch.randn(32, 64, device=dev).half()
     ref = R.paged_attention_ref(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), ctx, 16)
     for PS in (8192, 64, 256):
-        assert rel_err(run_attn(K, q, kc, vc, bt, ctx, PS), ref) <= ATTN_TOL, (ctx, PS)
+        for ver in (1, 2, 3):
+            assert rel_err(run_attn(K, q, kc, vc, bt, ctx, PS, ver), ref) <= ATTN_TOL, (ctx, PS, ver)
 
 
 @pytest.mark.parametrize("ctx", [512, 1024, 2048, 4096, 8192, 16384])
@@ -179,7 +180,8 @@ def test_attention_real_contexts(K, ctx, peaky):
     q = torch.randn(32, 64, device=dev).half()
     ref = R.paged_attention_ref(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), ctx, 16)
     for PS in (ctx, 1024, 256, 128, 64):
-        assert rel_err(run_attn(K, q, kc, vc, bt, ctx, PS), ref) <= ATTN_TOL, (ctx, peaky, PS)
+        for ver in (1, 2, 3):
+            assert rel_err(run_attn(K, q, kc, vc, bt, ctx, PS, ver), ref) <= ATTN_TOL, (ctx, peaky, PS, ver)
 
 
 @pytest.mark.parametrize("ctx", [1, 40, 64, 100, 700, 2048, 5000])
@@ -191,14 +193,36 @@ def test_attention_spare_split_buffers(K, ctx):
     q = torch.randn(32, 64, device=dev).half()
     ref = R.paged_attention_ref(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), ctx, 16)
     for PS in (64, 128, 256):
-        assert rel_err(run_attn(K, q, kc, vc, bt, ctx, PS, spare=8), ref) <= ATTN_TOL, (ctx, PS)
+        for ver in (1, 2, 3):
+            assert rel_err(run_attn(K, q, kc, vc, bt, ctx, PS, ver, spare=8), ref) <= ATTN_TOL, (ctx, PS, ver)
+
+
+@pytest.mark.parametrize("page", [4, 8, 64, 128])
+def test_attention_page_sizes_and_poisoned_tail(K, page):
+    """Pages of 8..64 tokens take the ring-staged kernel, others the register-load kernel. Cache slots past the
+    context (rest of the last page, spare pages) hold NaN: whole pages are copied, none of it may leak."""
+    torch.manual_seed(page)
+    for ctx in (1, page - 1, page + 3, 333, 1500):
+        kc, vc, bt = make_cache(ctx, 4, page)
+        q = torch.randn(32, 64, device=dev).half()
+        ref = R.paged_attention_ref(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), ctx, page)
+        last, used = bt[(ctx - 1) // page].item(), (ctx - 1) % page + 1
+        kc[last, :, used:], vc[last, :, used:] = float("nan"), float("nan")
+        for spare_page in bt[(ctx + page - 1) // page:].tolist():
+            kc[spare_page], vc[spare_page] = float("nan"), float("nan")
+        for PS in (128, 256, 2048):
+            for ver in (1, 2, 3):
+                out = run_attn(K, q, kc, vc, bt, ctx, PS, ver)
+                assert torch.isfinite(out).all() and rel_err(out, ref) <= ATTN_TOL, (page, ctx, PS, ver)
+    assert K.paged_attention_status() == 0
 
 
 def test_attention_golden(K, golden):
     g = golden("ops")
     T = lambda k: torch.from_numpy(g[k]).to(dev)
-    out = run_attn(K, T("attn_q_d64"), T("ra_kc_d64"), T("ra_vc_d64"), T("ra_bt_d64"), 70, 32)
-    assert rel_err(out, torch.from_numpy(g["attn_out_d64"])) <= ATTN_TOL
+    for ver in (1, 2, 3):
+        out = run_attn(K, T("attn_q_d64"), T("ra_kc_d64"), T("ra_vc_d64"), T("ra_bt_d64"), 70, 32, ver)
+        assert rel_err(out, torch.from_numpy(g["attn_out_d64"])) <= ATTN_TOL, ver
 
 
 @pytest.mark.parametrize("D,n_q,n_kv", [(64, 32, 4), (128, 64, 8), (128, 8, 1), (128, 16, 8)])
@@ -224,14 +248,14 @@ def test_attention_batched(K, D, n_q, n_kv, B):
         q = torch.randn(B, n_q, D, device=dev).half()
         pos = torch.tensor([c - 1 for c in ctxs], dtype=torch.int32, device=dev)
         ref = R.paged_attention_batched_ref(q.cpu(), kc.cpu(), vc.cpu(), bt, ctxs, page)
-        for PS in (256, 512):
+        for PS, ver in ((256, 0), (512, 1), (256, 2), (512, 3)):
             S = (max(ctxs) + PS - 1) // PS
             o_part = torch.full((B, n_q, S, D), float("nan"), device=dev)
             m_part = torch.full((B, n_q, S), float("nan"), device=dev)
             l_part = torch.full_like(m_part, float("nan"))
             out = torch.empty(B, n_q, D, dtype=torch.half, device=dev)
-            K.paged_attention_batched(q, kc, vc, bt.to(dev), pos, PS, o_part, m_part, l_part, out)
-            assert rel_err(out, ref) <= ATTN_TOL, (D, n_q, n_kv, ctxs, PS)
+            K.paged_attention_batched(q, kc, vc, bt.to(dev), pos, PS, o_part, m_part, l_part, out, version=ver)
+            assert rel_err(out, ref) <= ATTN_TOL, (D, n_q, n_kv, ctxs, PS, ver)
 
 
 # ---- 6. fused operators ---------------------------------------------------------------------------------

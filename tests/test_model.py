@@ -103,16 +103,18 @@ def test_golden_model(golden, quant, step_kernel):
 
 
 @pytest.mark.parametrize("step_kernel", STEP_KERNELS)
-@pytest.mark.parametrize("shape", ["gqa8_d64", "gqa8_d128", "gqa4_d64_big_group"])
+@pytest.mark.parametrize("shape", ["gqa8_d64", "gqa8_d128", "gqa4_d64_big_group", "rows_over_16k"])
 def test_against_oracle_model(shape, step_kernel):
     """Mid-sized random models: oracle on the very same packed weights and block table."""
     if shape == "gqa8_d64":
         c, D, group = hf_cfg(512, 3, 8, 1, 1536, 4001), None, 128
     elif shape == "gqa8_d128":
         c, D, group = hf_cfg(1024, 2, 8, 1, 2048, 3000, D=128), 128, 128
-    else:
+    elif shape == "gqa4_d64_big_group":
         c, D, group = hf_cfg(1024, 2, 16, 4, 1024, 1000), None, 256
-    sd = random_state(c, 11, D)
+    else:   # down-projection rows of 18432 weights: a consumer warp of the step kernel owns more than one segment
+        c, D, group = hf_cfg(256, 1, 4, 1, 18432, 600), None, 64
+    sd = random_state(c, 11, D, scale=0.02 if shape == "rows_over_16k" else 0.05)
     cfg = DecodeConfig(group=group, max_ctx=160, page=16, seed=5, step_kernel=step_kernel)
     m = Model(sd, c, cfg)
     ocfg = types.SimpleNamespace(group=group, quant="rtn", qparams=None, max_ctx=160, page=16, shuffle_pages=True)
@@ -137,6 +139,28 @@ def test_against_oracle_model(shape, step_kernel):
             row = ref_logits[len(prompt) - 1 + t].float()
             assert row[b] - row[a] <= 2 * LOGIT_TOL * scale, f"free-run diverged at {t} outside the noise floor"
             break
+
+
+@pytest.mark.parametrize("off", ["dequant", "norm", "swiglu", "rope", "unfused"])
+def test_ablation_switches_keep_the_numbers(off):
+    """Each fusion switched off in turn: the step still matches the oracle model, through the CUDA graph."""
+    c = hf_cfg(512, 2, 8, 2, 1024, 1500)
+    sd = random_state(c, 21)
+    kw = dict(fused=False) if off == "unfused" else dict(ablate=(off,))
+    m = Model(sd, c, DecodeConfig(max_ctx=96, seed=2, **kw))
+    assert not m.persistent and m.off == ({"norm", "swiglu"} if off == "unfused" else {off})
+    ocfg = types.SimpleNamespace(group=128, quant="rtn", qparams=None, max_ctx=96, page=16, shuffle_pages=True)
+    o = MO.OracleModel(sd, c, ocfg, packed=packed_of(m), block_table=m.bt.cpu())
+    torch.manual_seed(1)
+    stream = torch.randint(0, c.vocab_size, (40,)).tolist()
+    ref_logits = o.teacher_force(stream, collect_logits=True)
+    m.prepare(96, use_graph=True, part_size=32)
+    m.reset(0)
+    check_logits_and_tokens(m.teacher_force(stream, collect_logits=True).cpu(), ref_logits)
+    with pytest.raises(ValueError):
+        Model(sd, c, DecodeConfig(max_ctx=96, step_kernel="persistent", **kw))
+    with pytest.raises(ValueError):
+        Model(sd, c, DecodeConfig(max_ctx=96, ablate=("everything",)))
 
 
 def test_capture_in_mid_sequence_keeps_the_cache():
