@@ -744,14 +744,17 @@ __global__ void paged_attn_combine_kernel(const float* __restrict__ o_part, cons
   const float* m = m_part + hq * max_splits;
   const float* l = l_part + hq * max_splits;
   const float* o = o_part + hq * max_splits * D + d;
-  float M = -CUDART_INF_F;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldg(m + s));
-  float L = 0.f, acc = 0.f;
-#pragma unroll 4
+  // one pass with a running max: every load of the loop is independent of the arithmetic, so the unrolled body has
+  // eight splits' worth of loads in flight instead of one round trip per split
+  float M = -CUDART_INF_F, L = 0.f, acc = 0.f;
+#pragma unroll 8
   for (int s = 0; s < nsplit; ++s) {
-    const float a = __expf(__ldg(m + s) - M);
-    L = fmaf(a, __ldg(l + s), L);
-    acc = fmaf(a, o[(size_t)s * D], acc);
+    const float ms = __ldg(m + s), ls = __ldg(l + s), os = __ldg(o + (size_t)s * D);
+    const float Mn = fmaxf(M, ms);
+    const float a = __expf(M - Mn), c = __expf(ms - Mn);   // first split: e^(-inf) = 0
+    L = fmaf(L, a, c * ls);
+    acc = fmaf(acc, a, c * os);
+    M = Mn;
   }
   out[hq * D + d] = __float2half(acc / L);
 }
