@@ -192,6 +192,39 @@ size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D
  * 3 ring empty) and the step's outputs are invalid; the caller checks it after synchronising. */
 int b200_decode_step(const b200_step_desc* d, void* stream);
 
+/* ---- tensor-parallel exchange over NVLink peer memory (one process per GPU, all GPUs in one node) ----
+ * No counterpart in the reference, which is single-GPU; the 70B-shape configuration splits o_proj / down_proj by
+ * rows and the LM head by vocabulary, and these entry points are the collectives of that split, fused with the
+ * operator that follows them. They are the only entry points that own device memory.
+ *
+ * An exchange block is b200_comm_header_bytes() of flags followed by data slots at caller-chosen offsets (multiples
+ * of 16). Every rank allocates one block of the same size (b200_comm_alloc, zero-filled), exports it as a 64-byte
+ * CUDA IPC handle (b200_comm_export), sends the handle to its peers by any host channel, and maps theirs
+ * (b200_comm_import). `peers` below is a HOST array of W device pointers, peers[r] = rank r's block as this process
+ * sees it (peers[rank] = the local block). All ranks must issue the same sequence of exchange calls. */
+int b200_comm_header_bytes(void);
+int b200_comm_alloc(size_t bytes, void** ptr);
+int b200_comm_free(void* ptr);
+int b200_comm_export(void* ptr, void* handle64);
+int b200_comm_import(const void* handle64, void** ptr);
+int b200_comm_unimport(void* ptr);
+/* Zero the block's header (flags, step counter, error word). Call on every rank, between two host-side barriers. */
+int b200_comm_reset(void* base);
+/* *code = 0, or 1 once a bounded wait for a peer ran out (that call's outputs are invalid). Synchronises. */
+int b200_comm_error(const void* base, int* code);
+
+/* Replaces "NCCL all-reduce, then add_rmsnorm" after a row-split projection. Every rank's GEMV has written its
+ * partial fp16 [H] at slot_off of its own block; this sums the W partials (fp32, rank order, rounded to fp16 - the
+ * same bits on every rank), then x <- x + sum and out <- RMSNorm(x) * w exactly as b200_add_rmsnorm. One kernel:
+ * flag round with the peers (bounded waits), peer loads, norm. H % 8 == 0, H <= 32768. A slot may be reused once
+ * another exchange call has completed in between. */
+int b200_tp_allreduce_add_rmsnorm(const void* const* peers, int rank, int W, size_t slot_off, void* x, const void* w,
+                                  void* out, int H, float eps, void* stream);
+
+/* Replaces the all-gather of the vocabulary-split LM head: dst[r * n + i] = rank r's fp16 shard[i] found at slot_off
+ * of its block. Same flag round. dst 16-byte aligned when n % 8 == 0. */
+int b200_tp_allgather(const void* const* peers, int rank, int W, size_t slot_off, void* dst, int n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "decode_step.h"
 #include <stdlib.h>
+#include <string.h>
 
 namespace b200 {
 cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, const void* SZ, const void* x, void* y,
@@ -28,6 +29,13 @@ cudaError_t bw_read_bulk_dispatch(const void* p, size_t bytes, void* sink, int b
 cudaError_t repack_stream_dispatch(const void* W, const void* SZ, void* out, int N, int K, int log2G, int gu, int ncta,
                                    int stage_w, cudaStream_t st);
 cudaError_t paged_attention_status(int* code);
+cudaError_t tp_allreduce_add_rmsnorm_dispatch(const void* const* peers, int rank, int W, size_t off, void* x,
+                                              const void* w, void* out, int H, float eps, cudaStream_t st);
+cudaError_t tp_allgather_dispatch(const void* const* peers, int rank, int W, size_t off, void* dst, int n,
+                                  cudaStream_t st);
+int comm_header_bytes();
+int comm_max_ranks();
+int comm_error_offset();
 cudaError_t paged_attention_dispatch(int version, const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
                                      const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS,
                                      int max_splits, float* o_part, float* m_part, float* l_part, void* out,
@@ -282,6 +290,84 @@ int b200_argmax(const void* logits, int V, long long* tok, int* pos, long long* 
   REQUIRE(logits && tok && V > 0, B200_ERR_ARG);
   REQUIRE(history == nullptr || pos != nullptr, B200_ERR_ARG);
   return finish(b200::argmax_dispatch(logits, V, tok, pos, history, S(stream)));
+}
+
+// ---- tensor-parallel exchange blocks (the only entry points of the library that own device memory) -----------------
+int b200_comm_header_bytes(void) { return b200::comm_header_bytes(); }
+
+int b200_comm_alloc(size_t bytes, void** ptr) {
+  REQUIRE(ptr && bytes >= (size_t)b200::comm_header_bytes(), B200_ERR_ARG);
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (p) cudaFree(p);
+    return finish(e);
+  }
+  *ptr = p;
+  return B200_OK;
+}
+
+int b200_comm_free(void* ptr) {
+  REQUIRE(ptr, B200_ERR_ARG);
+  return finish(cudaFree(ptr));
+}
+
+int b200_comm_export(void* ptr, void* handle64) {
+  REQUIRE(ptr && handle64, B200_ERR_ARG);
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is passed around as 64 bytes");
+  return finish(cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle64), ptr));
+}
+
+int b200_comm_import(const void* handle64, void** ptr) {
+  REQUIRE(handle64 && ptr, B200_ERR_ARG);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return finish(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int b200_comm_unimport(void* ptr) {
+  REQUIRE(ptr, B200_ERR_ARG);
+  return finish(cudaIpcCloseMemHandle(ptr));
+}
+
+int b200_comm_reset(void* base) {
+  REQUIRE(base, B200_ERR_ARG);
+  cudaError_t e = cudaMemset(base, 0, b200::comm_header_bytes());
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  return finish(e);
+}
+
+int b200_comm_error(const void* base, int* code) {
+  REQUIRE(base && code, B200_ERR_ARG);
+  return finish(cudaMemcpy(code, (const char*)base + b200::comm_error_offset(), sizeof(int), cudaMemcpyDeviceToHost));
+}
+
+static int check_peers(const void* const* peers, int rank, int W, size_t off) {
+  REQUIRE(peers && W >= 1 && W <= b200::comm_max_ranks() && rank >= 0 && rank < W, B200_ERR_ARG);
+  REQUIRE(off >= (size_t)b200::comm_header_bytes() && off % 16 == 0, B200_ERR_ALIGN);
+  for (int r = 0; r < W; ++r) REQUIRE(peers[r] && aligned16(peers[r]), B200_ERR_ARG);
+  return B200_OK;
+}
+
+int b200_tp_allreduce_add_rmsnorm(const void* const* peers, int rank, int W, size_t slot_off, void* x, const void* w,
+                                  void* out, int H, float eps, void* stream) {
+  const int rc = check_peers(peers, rank, W, slot_off);
+  if (rc) return rc;
+  REQUIRE(x && w && out && H > 0, B200_ERR_ARG);
+  REQUIRE(H % 8 == 0, B200_ERR_SHAPE);
+  REQUIRE(H <= 32768, B200_ERR_LIMIT);
+  REQUIRE(aligned16(x) && aligned16(w) && aligned16(out), B200_ERR_ALIGN);
+  return finish(b200::tp_allreduce_add_rmsnorm_dispatch(peers, rank, W, slot_off, x, w, out, H, eps, S(stream)));
+}
+
+int b200_tp_allgather(const void* const* peers, int rank, int W, size_t slot_off, void* dst, int n, void* stream) {
+  const int rc = check_peers(peers, rank, W, slot_off);
+  if (rc) return rc;
+  REQUIRE(dst && n > 0, B200_ERR_ARG);
+  REQUIRE(n % 8 != 0 || aligned16(dst), B200_ERR_ALIGN);
+  return finish(b200::tp_allgather_dispatch(peers, rank, W, slot_off, dst, n, S(stream)));
 }
 
 }  // extern "C"

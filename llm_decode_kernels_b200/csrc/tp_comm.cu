@@ -1,0 +1,198 @@
+// Tensor-parallel exchange over NVLink peer memory, fused with the operator that follows it.
+//
+// A row-split projection (o_proj, down_proj) leaves every rank with a partial [H] vector; the reference design for
+// the 70B shape sums them with an NCCL all-reduce and then runs residual add + RMSNorm. Here each rank's GEMV writes
+// its partial straight into a buffer that the other GPUs of the node can read (CUDA IPC mapping, one process per
+// GPU), and ONE kernel per rank does the rest:
+//   1. tell every peer "my partial number `step` is ready" (a release store of `step` into the peer's flag word),
+//   2. wait until every peer has said the same (acquire loads of the local flag words, bounded),
+//   3. read all W partials (peer loads over NVLink), add them in rank order with fp32 accumulation - the same order
+//      on every rank, so all ranks compute bit-identical sums -, round to fp16,
+//   4. residual add and RMSNorm exactly as add_rmsnorm_kernel does.
+// That is a one-shot all-reduce: for 16 KB vectors latency is everything, and one round of flag + data over NVSwitch
+// is the least it can cost. No library kernel touches peer memory, nothing here uses multicast loads.
+//
+// The vocabulary-split LM head ends with the same flag round followed by a gather of the logit shards.
+//
+// Buffer reuse needs no second flag round: a rank signals step s+1 only after it has finished reading step s, and
+// two buffers alternate (o_proj partials use one slot, down_proj partials another), so when a rank overwrites a slot
+// every peer has signalled a later step and is therefore done with the slot's previous contents.
+//
+// Every wait is bounded (about four seconds, enough for ranks that drift apart between host-driven steps). A wait
+// that runs out stores a code in the block's error word, and the kernel returns without touching the outputs.
+#include "common.cuh"
+
+namespace b200 {
+
+// Layout of one rank's exchange block (allocated by comm_alloc, zeroed): a 256-byte header, then the data slots at
+// offsets the caller chooses (multiples of 16 bytes).
+constexpr int kCommHeaderBytes = 256;
+constexpr int kCommMaxRanks = 16;
+constexpr int kCommFlagsOff = 0;      // uint32 flags[16]: flags[j] = latest step rank j has announced to this rank
+constexpr int kCommCounterOff = 64;   // uint32: steps this rank has taken
+constexpr int kCommErrorOff = 68;     // uint32: 0, or the code of a wait that ran out
+constexpr int kCommThreads = 1024;
+constexpr int kCommSpinLimit = 1 << 22;
+
+enum : uint32_t { COMM_ERR_PEER_WAIT = 1 };
+
+struct CommPeers {
+  uint8_t* p[kCommMaxRanks];   // base of every rank's exchange block as mapped into this process; p[rank] is local
+};
+
+namespace {
+
+DEVI void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+DEVI uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+DEVI uint4 ld_peer16(const void* p) {
+  uint4 r;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p)
+               : "memory");
+  return r;
+}
+
+// Steps 1 and 2 of the header comment, by all threads of the (single) block. Returns false if a wait ran out.
+DEVI bool exchange_flags(const CommPeers& P, int rank, int W) {
+  __shared__ uint32_t step_s;
+  uint8_t* base = P.p[rank];
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    uint32_t* counter = reinterpret_cast<uint32_t*>(base + kCommCounterOff);
+    step_s = *counter + 1u;
+    *counter = step_s;
+  }
+  __syncthreads();
+  const uint32_t step = step_s;
+  int failed = 0;
+  if (tid < W && tid != rank) {
+    __threadfence_system();   // the partial was written by the previous kernel of this stream; order it before the flag
+    st_release_sys(reinterpret_cast<uint32_t*>(P.p[tid] + kCommFlagsOff) + rank, step);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(base + kCommFlagsOff) + tid;
+    int i = 0;
+    while ((int32_t)(ld_acquire_sys(mine) - step) < 0) {
+      if (++i > kCommSpinLimit) { failed = 1; break; }
+      __nanosleep(500);
+    }
+    if (failed) atomicExch(reinterpret_cast<uint32_t*>(base + kCommErrorOff), COMM_ERR_PEER_WAIT);
+  }
+  return __syncthreads_or(failed) == 0;
+}
+
+}  // namespace
+
+// delta = sum over ranks of the partial at `off` (fp32 accumulation in rank order, rounded to fp16), then
+// x <- x +_fp16 delta, out <- w *_fp16 half(float(x) * rsqrt(mean(x^2) + eps)): the rounding of add_rmsnorm_kernel.
+// One block of 1024 threads; H % 8 == 0, H <= 1024 * 8 * 4.
+__global__ void __launch_bounds__(kCommThreads)
+tp_allreduce_add_rmsnorm_kernel(const CommPeers P, int rank, int W, size_t off, half* __restrict__ x,
+                                const half* __restrict__ w, half* __restrict__ out, int H, float eps) {
+  constexpr int MAXC = 4;
+  __shared__ float part[kCommThreads / 32];
+  if (!exchange_flags(P, rank, W)) return;
+  const int tid = threadIdx.x, nchunk = H >> 3;
+  uint4 xv[MAXC];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int i = tid + c * kCommThreads;
+    if (i < nchunk) {
+      float acc[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+      for (int r = 0; r < W; ++r) {
+        float f[8];
+        unpack8(ld_peer16(P.p[r] + off + 16 * (size_t)i), f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += f[k];
+      }
+      uint4 v = reinterpret_cast<const uint4*>(x)[i];
+      v.x = as_u32(__hadd2(as_h2(v.x), __floats2half2_rn(acc[0], acc[1])));
+      v.y = as_u32(__hadd2(as_h2(v.y), __floats2half2_rn(acc[2], acc[3])));
+      v.z = as_u32(__hadd2(as_h2(v.z), __floats2half2_rn(acc[4], acc[5])));
+      v.w = as_u32(__hadd2(as_h2(v.w), __floats2half2_rn(acc[6], acc[7])));
+      reinterpret_cast<uint4*>(x)[i] = v;
+      float f[8];
+      unpack8(v, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss = fmaf(f[k], f[k], ss);
+      xv[c] = v;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) part[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < kCommThreads / 32; ++k) tot += part[k];
+  const float rinv = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int i = tid + c * kCommThreads;
+    if (i < nchunk) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + i);
+      const uint32_t xu[4] = {xv[c].x, xv[c].y, xv[c].z, xv[c].w}, wu[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __half22float2(as_h2(xu[k]));
+        o[k] = as_u32(__hmul2(as_h2(wu[k]), __floats2half2_rn(f.x * rinv, f.y * rinv)));
+      }
+      reinterpret_cast<uint4*>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// dst[r * n + i] = rank r's shard[i] (shards of n fp16 values at `off` of every block). One block of 1024 threads.
+__global__ void __launch_bounds__(kCommThreads)
+tp_allgather_kernel(const CommPeers P, int rank, int W, size_t off, half* __restrict__ dst, int n) {
+  if (!exchange_flags(P, rank, W)) return;
+  const int tid = threadIdx.x;
+  if ((n & 7) == 0) {
+    const int nchunk = n >> 3;
+    for (int r = 0; r < W; ++r) {
+      uint4* d = reinterpret_cast<uint4*>(dst + (size_t)r * n);
+      const uint8_t* s = P.p[r] + off;
+#pragma unroll 4
+      for (int i = tid; i < nchunk; i += kCommThreads) d[i] = ld_peer16(s + 16 * (size_t)i);
+    }
+  } else {
+    for (int r = 0; r < W; ++r) {
+      const volatile half* s = reinterpret_cast<const volatile half*>(P.p[r] + off);
+      for (int i = tid; i < n; i += kCommThreads) {
+        const unsigned short u = reinterpret_cast<const volatile unsigned short*>(s)[i];
+        dst[(size_t)r * n + i] = __ushort_as_half(u);
+      }
+    }
+  }
+}
+
+cudaError_t tp_allreduce_add_rmsnorm_dispatch(const void* const* peers, int rank, int W, size_t off, void* x,
+                                              const void* w, void* out, int H, float eps, cudaStream_t st) {
+  CommPeers P = {};
+  for (int r = 0; r < W; ++r) P.p[r] = (uint8_t*)peers[r];
+  tp_allreduce_add_rmsnorm_kernel<<<1, kCommThreads, 0, st>>>(P, rank, W, off, (half*)x, (const half*)w, (half*)out, H,
+                                                              eps);
+  return cudaPeekAtLastError();
+}
+
+cudaError_t tp_allgather_dispatch(const void* const* peers, int rank, int W, size_t off, void* dst, int n,
+                                  cudaStream_t st) {
+  CommPeers P = {};
+  for (int r = 0; r < W; ++r) P.p[r] = (uint8_t*)peers[r];
+  tp_allgather_kernel<<<1, kCommThreads, 0, st>>>(P, rank, W, off, (half*)dst, n);
+  return cudaPeekAtLastError();
+}
+
+int comm_header_bytes() { return kCommHeaderBytes; }
+int comm_max_ranks() { return kCommMaxRanks; }
+int comm_error_offset() { return kCommErrorOff; }
+
+}  // namespace b200

@@ -1,0 +1,181 @@
+"""End-to-end decode benchmarks beside the headline one (the reference's bench/e2e.py, for the two configurations
+that bench.py does not time).
+
+    python -m llm_decode_kernels_b200.e2e_bench ctx [--quant gptq|rtn] [--tokens 64] [--out FILE.json]
+        TinyLlama shape, tokens/s at KV contexts 512 .. 8192 (cache pre-filled with N(0,1), as the reference does), and
+        at context 2048 with each fusion switched off in turn (DecodeConfig.ablate). --quant gptq calibrates on 128
+        synthetic sequences of 512 uniform random ids with clipping (the stand-in for the WikiText-2 calibration set).
+
+    torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m llm_decode_kernels_b200.e2e_bench tp
+             [--layers 80] [--ctx 4096] [--tokens 128] [--tp-comm p2p|nccl]
+        Llama-3-70B shape, random N(0, 0.02) weights, W4A16 g128, batch-1 greedy decode of `tokens` tokens from a
+        pre-filled context, tensor-parallel over the N ranks (N = 1 without torchrun). Prints one JSON line on rank 0:
+        tokens/s, microseconds per token, bytes each GPU streams per token and the fraction of the measured HBM
+        bandwidth that is.
+
+Timing: CUDA events around the decode steps on the launching stream, after 8 warm-up steps, max over ranks.
+"""
+import argparse
+import json
+import os
+import time
+from pathlib import Path
+
+import torch
+
+from .model import DecodeConfig, Model
+from .shapes import LLAMA3_70B, TINYLLAMA, LazyRandomState, config, random_llama_state
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def peak_hbm_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def time_decode(m, ctx, tokens, warm=8, dist=None):
+    """Decode `tokens` tokens starting at context `ctx` (cache contents as they are); returns microseconds per token."""
+    m.reset(ctx - warm)
+    for _ in range(warm):
+        m.run_step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(tokens):
+        m.run_step()
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device=m.tok.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t)
+    return ms * 1e3 / tokens
+
+
+def run_ctx(a):
+    c = config(TINYLLAMA)
+    qparams, quant = None, "rtn"
+    if a.quant == "gptq":
+        # calibration works on a HF module (as the reference's driver does): a random-init LlamaForCausalLM of the shape
+        from transformers import LlamaConfig, LlamaForCausalLM
+        from . import gptq
+        torch.manual_seed(0)
+        hf = LlamaForCausalLM(LlamaConfig(**TINYLLAMA, max_position_embeddings=2048, initializer_range=0.02))
+        hf = hf.half().cuda().eval()
+        tok = type("Tok", (), {"bos_token_id": 1, "vocab_size": c.vocab_size})()
+        t0 = time.time()
+        qparams = gptq.calibrate(hf, tok, 128, clip=True, n=128, L=512, lm_head=True, log=lambda *x: None)
+        quant = "pre"
+        sd = {k: v.detach() for k, v in hf.state_dict().items()}
+        print(f"calibrated in {time.time() - t0:.1f} s", flush=True)
+    else:
+        sd = random_llama_state(c, "cuda", 0)
+    peak, kind = peak_hbm_gbs()
+    res = {"gpu": torch.cuda.get_device_name(0), "quant": a.quant, "tokens_timed": a.tokens, "contexts": {},
+           "ablations_at_2048": {}}
+    max_ctx = 8192 + a.tokens + 16
+
+    def build(**kw):
+        return Model(sd, c, DecodeConfig(group=128, quant=quant, qparams=qparams, max_ctx=max_ctx, seed=0, **kw))
+
+    m = build()
+    m.kv.normal_()
+    for ctx in (512, 1024, 2048, 4096, 8192):
+        m.prepare(ctx + a.tokens + 8)
+        us = time_decode(m, ctx, a.tokens)
+        nbytes = m.bytes_per_token(ctx + a.tokens // 2)
+        res["contexts"][ctx] = {"us_per_token": round(us, 1), "tok_s": round(1e6 / us, 1), "bytes_per_token": nbytes,
+                                "frac_of_hbm": round(nbytes / us / 1e3 / peak, 4),
+                                "step_kernel": "persistent" if m.persistent else "multi", "part_size": m.part_size}
+        print(ctx, res["contexts"][ctx], flush=True)
+    del m
+    for name, kw in (("all fused, one launch per operator", dict(step_kernel="multi")),
+                     ("dequant-in-GEMV off", dict(ablate=("dequant",))),
+                     ("residual+RMSNorm off", dict(ablate=("norm",))),
+                     ("SwiGLU off", dict(ablate=("swiglu",))),
+                     ("RoPE+KV-append off", dict(ablate=("rope",)))):
+        m = build(**kw)
+        m.kv.normal_()
+        m.prepare(2048 + a.tokens + 8)
+        us = time_decode(m, 2048, a.tokens)
+        res["ablations_at_2048"][name] = {"us_per_token": round(us, 1), "tok_s": round(1e6 / us, 1)}
+        print(name, res["ablations_at_2048"][name], flush=True)
+        del m
+        torch.cuda.empty_cache()
+    res["peak_hbm_gbs"], res["peak_source"] = peak, kind
+    txt = json.dumps(res, indent=1)
+    print(txt)
+    if a.out:
+        Path(a.out).write_text(txt)
+
+
+def run_tp(a):
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    dist = None
+    if world > 1:
+        import datetime
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(dev), timeout=datetime.timedelta(seconds=600))
+    c = config(LLAMA3_70B, num_hidden_layers=a.layers)
+    t0 = time.time()
+    cfg = DecodeConfig(group=128, max_ctx=a.ctx + a.tokens + 16, page=16, device=dev, seed=0, tp_rank=rank,
+                       tp_world=world, tp_comm=a.tp_comm, step_kernel="multi")
+    m = Model(LazyRandomState(c, dev, 0), c, cfg)
+    torch.cuda.empty_cache()
+    build_s = time.time() - t0
+    m.kv.normal_()
+    m.prepare(a.ctx + a.tokens + 8)
+    if dist is not None:
+        dist.barrier()
+    us = time_decode(m, a.ctx, a.tokens, dist=dist)
+    err = m.step_error()
+    nbytes = m.bytes_per_token(a.ctx + a.tokens // 2)      # what THIS rank streams per token
+    peak, kind = peak_hbm_gbs()
+    if rank == 0:
+        line = {"metric": "batch-1 decode tok/s (W4A16), tensor-parallel", "value": round(1e6 / us, 2), "unit": "tok/s",
+                "n_gpus": world, "us_per_token": round(us, 1),
+                "config": {"workload": f"llama-3-70b-shape W4A16 g128 RTN, {a.layers} layers, batch 1, context "
+                                       f"{a.ctx}, {a.tokens} greedy tokens", "tp": world, "tp_comm": a.tp_comm,
+                           "graph": m.graph is not None},
+                "bytes_per_token_per_gpu": nbytes, "floor_us_at_peak": round(nbytes / peak / 1e3, 1),
+                "frac_of_hbm_per_gpu": round(nbytes / us / 1e3 / peak, 4), "peak_hbm_gbs": peak, "peak_source": kind,
+                "exchanges_per_token": 2 * a.layers + 1 if world > 1 else 0, "build_s": round(build_s, 1),
+                "step_error": err, "data": "synthetic"}
+        print(json.dumps(line), flush=True)
+        if a.out:
+            Path(a.out).write_text(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        if m.comm is not None:
+            m.comm.close()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["ctx", "tp"])
+    ap.add_argument("--quant", default="rtn", choices=["rtn", "gptq"])
+    ap.add_argument("--tokens", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=80)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--tp-comm", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args()
+    if a.tokens is None:
+        a.tokens = 128 if a.what == "tp" else 64
+    {"ctx": run_ctx, "tp": run_tp}[a.what](a)
+
+
+if __name__ == "__main__":
+    main()

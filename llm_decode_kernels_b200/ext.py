@@ -40,6 +40,17 @@ SIGNATURES = {
                                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p],
     "b200_paged_attention_status": [c_void_p],
+    "b200_comm_header_bytes": [],
+    "b200_comm_alloc": [c_size_t, c_void_p],
+    "b200_comm_free": [c_void_p],
+    "b200_comm_export": [c_void_p, c_void_p],
+    "b200_comm_import": [c_void_p, c_void_p],
+    "b200_comm_unimport": [c_void_p],
+    "b200_comm_reset": [c_void_p],
+    "b200_comm_error": [c_void_p, c_void_p],
+    "b200_tp_allreduce_add_rmsnorm": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_float,
+                                      c_void_p],
+    "b200_tp_allgather": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_int, c_void_p],
     "b200_paged_attention_noalloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_void_p, c_void_p],
     "b200_rope_append_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
@@ -244,6 +255,53 @@ class Ops:
         code = ctypes.c_int(-1)
         self._check(self.lib.b200_paged_attention_status(ctypes.byref(code)), "paged_attention_status")
         return code.value
+
+    # ---- tensor-parallel exchange blocks (see tp.PeerComm for the object that owns them)
+    def comm_header_bytes(self):
+        return int(self.lib.b200_comm_header_bytes())
+
+    def comm_alloc(self, nbytes):
+        p = ctypes.c_void_p()
+        self._check(self.lib.b200_comm_alloc(int(nbytes), ctypes.byref(p)), "comm_alloc")
+        return p.value
+
+    def comm_free(self, ptr):
+        self._check(self.lib.b200_comm_free(ptr), "comm_free")
+
+    def comm_export(self, ptr):
+        h = ctypes.create_string_buffer(64)
+        self._check(self.lib.b200_comm_export(ptr, h), "comm_export")
+        return h.raw
+
+    def comm_import(self, handle):
+        p = ctypes.c_void_p()
+        self._check(self.lib.b200_comm_import(ctypes.c_char_p(handle), ctypes.byref(p)), "comm_import")
+        return p.value
+
+    def comm_unimport(self, ptr):
+        self._check(self.lib.b200_comm_unimport(ptr), "comm_unimport")
+
+    def comm_reset(self, base):
+        self._check(self.lib.b200_comm_reset(base), "comm_reset")
+
+    def comm_error(self, base):
+        code = ctypes.c_int(-1)
+        self._check(self.lib.b200_comm_error(base, ctypes.byref(code)), "comm_error")
+        return code.value
+
+    def tp_allreduce_add_rmsnorm(self, peers, rank, slot_off, x, w, out, eps):
+        """peers: ctypes array of the W block pointers (tp.PeerComm.peers). x, w, out fp16 [H] as add_rmsnorm."""
+        _cuda(x, "x", torch.float16), _cuda(w, "w", torch.float16), _cuda(out, "out", torch.float16)
+        self._check(self.lib.b200_tp_allreduce_add_rmsnorm(peers, int(rank), len(peers), int(slot_off), x.data_ptr(),
+                                                           w.data_ptr(), out.data_ptr(), x.numel(), float(eps),
+                                                           _stream()), "tp_allreduce_add_rmsnorm")
+
+    def tp_allgather(self, peers, rank, slot_off, dst, n):
+        _cuda(dst, "dst", torch.float16)
+        if dst.numel() != n * len(peers):
+            raise RuntimeError("tp_allgather: dst must hold W shards of n values")
+        self._check(self.lib.b200_tp_allgather(peers, int(rank), len(peers), int(slot_off), dst.data_ptr(), int(n),
+                                               _stream()), "tp_allgather")
 
     def paged_attention_noalloc(self, q, kc, vc, bt, pos, part_size, max_splits, out):
         """paged_attention without caller scratch, for callers that cannot allocate: the split-K partials live in a

@@ -52,6 +52,10 @@ class DecodeConfig:
     tp_rank: int = 0             # tensor parallelism: this process's rank ...
     tp_world: int = 1            # ... of this many (one process per GPU, torch.distributed initialised by the caller)
     tp_group: object = field(default=None, repr=False)   # process group of the TP ranks (None: the default group)
+    tp_comm: str = "p2p"         # collectives of a tensor-parallel step: "p2p" = the library's one-shot exchange over
+                                 # NVLink peer memory, fused with the residual add + RMSNorm that follows (all GPUs in
+                                 # one node; the step is captured in a CUDA graph); "nccl" = torch.distributed
+                                 # all_reduce / all_gather, launched eagerly
     ablate: tuple = ()           # fusions switched off for ablation runs, any of "dequant" (dequantize the matrix to
                                  # an fp16 buffer, then an fp16 matrix-vector product), "norm", "swiglu" (the two
                                  # that fused=False switches off together) and "rope" (rotation and cache append as
@@ -176,6 +180,18 @@ class Model:
             self.w_fp16 = torch.empty(max(m.N * m.K for m in mats), **h16)
         if "rope" in self.off:
             self.kv_heads = torch.arange(self.n_kv, device=dev)
+        self.comm = None
+        if self.tp > 1:
+            if cfg.tp_comm not in ("p2p", "nccl"):
+                raise ValueError(f"tp_comm must be 'p2p' or 'nccl', got {cfg.tp_comm!r}")
+            if cfg.tp_comm == "p2p":
+                if self.off & {"norm"}:
+                    raise ValueError("tp_comm='p2p' fuses the all-reduce with residual add + RMSNorm; it cannot run "
+                                     "with that fusion switched off (use tp_comm='nccl')")
+                # the row-split projections and the LM head write straight into slots of the exchange block
+                self.comm = TP.PeerComm(self.K, self.tp_rank, self.tp, [2 * self.H, 2 * self.H, 2 * self.V], dev,
+                                        cfg.tp_group)
+                self.o, self.down, self.logits_local = self.comm.slot(0), self.comm.slot(1), self.comm.slot(2)
         self.set_attention_partition(cfg.max_ctx)
 
     # ------------------------------------------------------------------ attention partitioning
@@ -264,6 +280,8 @@ class Model:
 
     def step_error(self):
         """Code left by the persistent step kernel if one of its bounded waits gave up (0 = none). Synchronises."""
+        if getattr(self, "comm", None) is not None:
+            return self.comm.error()
         if not getattr(self, "persistent", False):
             return 0
         return int(self._step_static["ctrl"][1])
@@ -293,7 +311,16 @@ class Model:
         if self.tp > 1:
             torch.distributed.all_reduce(t, group=self.cfg.tp_group)
 
-    def add_norm(self, delta, w):
+    def add_norm(self, delta, w, slot=None):
+        """x <- x + delta, normed <- RMSNorm(x) * w. With tensor parallelism `delta` is this rank's partial of a
+        row-split projection, held in exchange slot `slot`: the sum over the ranks happens here, inside the same
+        kernel (tp_comm='p2p') or by an NCCL all-reduce in front of it."""
+        if self.tp > 1 and delta is not None:
+            if self.comm is not None:
+                self.K.tp_allreduce_add_rmsnorm(self.comm.peers, self.tp_rank, self.comm.offsets[slot], self.x, w,
+                                                self.normed, self.eps)
+                return
+            self.all_reduce(delta)
         if "norm" not in self.off:
             self.K.add_rmsnorm(self.x, delta, w, self.normed, self.eps)
         else:  # the unfused op sequence, on the device (ablation)
@@ -351,20 +378,20 @@ class Model:
         self.K.embed_row(self.emb, self.tok, self.x)
         delta = None
         for li, lw in enumerate(self.layers):
-            self.add_norm(delta, lw["ln1"])
+            self.add_norm(delta, lw["ln1"], 1)
             self.linear(lw["qkv"], self.normed, self.qkv)
             self.attention(li)
             self.linear(lw["o"], self.attn.view(-1), self.o)
-            self.all_reduce(self.o)
-            self.add_norm(self.o, lw["ln2"])
+            self.add_norm(self.o, lw["ln2"], 0)
             self.linear(lw["gu"], self.normed, self.gu)
             self.swiglu()
             self.linear(lw["down"], self.act, self.down)
-            self.all_reduce(self.down)
             delta = self.down
-        self.add_norm(delta, self.norm_f)
+        self.add_norm(delta, self.norm_f, 1)
         self.linear(self.lm_head, self.normed, self.logits_local)
-        if self.tp > 1:   # every rank gathers the whole vocabulary and takes the same argmax: no broadcast needed
+        if self.comm is not None:   # every rank gathers the whole vocabulary and takes the same argmax: no broadcast
+            self.K.tp_allgather(self.comm.peers, self.tp_rank, self.comm.offsets[2], self.logits, self.V)
+        elif self.tp > 1:
             torch.distributed.all_gather_into_tensor(self.logits, self.logits_local, group=self.cfg.tp_group)
         self.K.argmax(self.logits, self.tok, self.pos, self.history)
 
@@ -372,9 +399,10 @@ class Model:
         """Capture step() into a CUDA graph (two warm-up steps on a side stream first, as torch requires).
         Warm-up runs at positions 0 and 1 (reference runtime/model.py:235-251); the token, position, history
         entries and the KV page it touches are saved and put back, so capturing in mid-sequence loses nothing."""
-        if self.tp > 1:
+        if self.tp > 1 and self.comm is None:
             # Capturing a step that contains NCCL collectives did not complete on the B200 pool this was developed on
-            # (both ranks stalled inside the capture); tensor-parallel steps are therefore launched eagerly.
+            # (both ranks stalled inside the capture); with tp_comm="nccl" the steps are therefore launched eagerly.
+            # The peer-memory exchange is made of this library's own kernels and is captured like everything else.
             self.graph = None
             return
         saved_tok, saved_pos, saved_hist = self.tok.clone(), self.pos.clone(), self.history[:2].clone()

@@ -100,3 +100,72 @@ def shard_qsz(kind, qsz, dims, group, rank, world):
     if a % group or b % group:
         raise ValueError("a column slice would cut a quantization group")
     return q[:, a:b].contiguous(), s[:, a // group:b // group].contiguous(), z[:, a // group:b // group].contiguous()
+
+
+# ---- exchange over NVLink peer memory ------------------------------------------------------------------------------
+class _RawCuda:
+    """Minimal __cuda_array_interface__ carrier, so torch can wrap memory the exchange block owns."""
+
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class PeerComm:
+    """One rank's exchange block plus its mapping of every peer's block (b200_comm_* of the C library).
+
+    `slots` are byte sizes of the data slots (e.g. [2 H, 2 H, 2 V/TP]: o_proj partial, down_proj partial, logit
+    shard). The block is allocated by the library (cudaMalloc, so that a CUDA IPC handle names exactly it), the
+    handles travel through torch.distributed (all_gather_object on `group`), and every peer block is opened with
+    peer access enabled. slot(i) is a torch fp16 tensor over slot i of the LOCAL block: a GEMV that writes its
+    output there has published its partial. `peers` is the ctypes array the exchange entry points take."""
+
+    def __init__(self, K, rank, world, slots, device, group=None):
+        import ctypes
+        import torch.distributed as dist
+        self.K, self.rank, self.world, self.group, self.device = K, rank, world, group, device
+        align = lambda n: (n + 255) // 256 * 256
+        self.offsets, off = [], K.comm_header_bytes()
+        for nbytes in slots:
+            self.offsets.append(off)
+            off += align(nbytes)
+        self.slot_bytes, self.nbytes = list(slots), off
+        with torch.cuda.device(device):
+            self.base = K.comm_alloc(self.nbytes)
+            handle = K.comm_export(self.base)
+            handles = [None] * world
+            dist.all_gather_object(handles, handle, group=group)
+            self.mapped = [self.base if r == rank else K.comm_import(handles[r]) for r in range(world)]
+        self.peers = (ctypes.c_void_p * world)(*self.mapped)
+        self._views = [torch.as_tensor(_RawCuda(self.base + o, n // 2, "<f2"), device=device)
+                       for o, n in zip(self.offsets, self.slot_bytes)]
+        dist.barrier(group=group)   # nobody signals before everybody has mapped everybody
+
+    def slot(self, i):
+        return self._views[i]
+
+    def error(self):
+        """0, or the code of a peer wait that ran out on this rank. Synchronises."""
+        return self.K.comm_error(self.base)
+
+    def reset(self):
+        """Zero flags, step counter and error word on every rank (collective: every rank must call it)."""
+        import torch.distributed as dist
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self.K.comm_reset(self.base)
+        dist.barrier(group=self.group)
+
+    def close(self):
+        """Unmap the peers and free the local block (collective: peers must not be inside an exchange)."""
+        import torch.distributed as dist
+        if self.base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self._views = []
+        for r, p in enumerate(self.mapped):
+            if r != self.rank:
+                self.K.comm_unimport(p)
+        dist.barrier(group=self.group)
+        self.K.comm_free(self.base)
+        self.base = None

@@ -38,7 +38,7 @@ def test_python_signatures_cover_the_header():
     for name, argtypes in ext.SIGNATURES.items():
         m = re.search(name + r"\s*\((.*?)\)\s*;", text, flags=re.S)
         assert m, name
-        assert len([a for a in m.group(1).split(",") if a.strip()]) == len(argtypes), name
+        assert len([a for a in m.group(1).split(",") if a.strip() not in ("", "void")]) == len(argtypes), name
 
 
 def test_bad_arguments_are_refused_on_the_host():
@@ -52,6 +52,13 @@ def test_bad_arguments_are_refused_on_the_host():
     assert lib.b200_gemv_w4a16(2, 0, 0, 0, p16, p16, p16, p16, 4, 128, 4, None) == -3           # group 16 < 32
     assert lib.b200_gemv_w4a16(2, 0, 0, 0, p16 + 4, p16, p16, p16, 4, 128, 7, None) == -2       # misaligned weights
     assert lib.b200_add_rmsnorm(p16, None, p16, p16, 12, 1e-5, None) == -3                      # H % 8 != 0
+    peers = (ctypes.c_void_p * 2)(p16, p16)
+    assert lib.b200_tp_allreduce_add_rmsnorm(peers, 2, 2, 256, p16, p16, p16, 64, 1e-5, None) == -1   # rank >= W
+    assert lib.b200_tp_allreduce_add_rmsnorm(peers, 0, 2, 64, p16, p16, p16, 64, 1e-5, None) == -2    # inside header
+    assert lib.b200_tp_allreduce_add_rmsnorm(peers, 0, 2, 256, p16, p16, p16, 60, 1e-5, None) == -3   # H % 8 != 0
+    assert lib.b200_tp_allgather(peers, 0, 17, 256, p16, 64, None) == -1                              # too many ranks
+    assert lib.b200_comm_alloc(16, ctypes.byref(ctypes.c_void_p())) == -1                             # below the header
+    assert lib.b200_comm_header_bytes() == 256
     assert lib.b200_add_rmsnorm(p16, None, p16, p16, 65536, 1e-5, None) == -5                   # H over capacity
     assert lib.b200_swiglu(p16, p16, 0, None) == -1
     assert lib.b200_paged_attention(7, p16, p16, p16, p16, p16, 32, 4, 4, 64, 1, p16, p16, p16, p16, None) == -1

@@ -349,6 +349,39 @@ def test_rope_golden(K, golden):
         assert np.array_equal(vc.cpu().numpy().view(np.uint16), g[f"ra_vc_out_d{D}"].view(np.uint16))
 
 
+def test_exchange_kernels_with_one_rank(K):
+    """W = 1: no peer to wait for, so the fused kernels reduce to add_rmsnorm / a copy and run on a single GPU.
+    (Two ranks need two GPUs: see tests/test_tp_gpu.py.)"""
+    import ctypes
+    torch.manual_seed(5)
+    H, n = 4096, 1000
+    hdr = K.comm_header_bytes()
+    off2 = hdr + 2 * H + 256
+    base = K.comm_alloc(off2 + 2 * n + 256)
+    try:
+        peers = (ctypes.c_void_p * 1)(base)
+        assert K.comm_error(base) == 0 and len(K.comm_export(base)) == 64
+        part = torch.randn(H, device=dev).half()
+        shard = torch.randn(n, device=dev).half()
+        import llm_decode_kernels_b200.tp as TP
+        torch.as_tensor(TP._RawCuda(base + hdr, H, "<f2"), device=dev).copy_(part)
+        torch.as_tensor(TP._RawCuda(base + off2, n, "<f2"), device=dev).copy_(shard)
+        x0, w = torch.randn(H, device=dev).half(), (1 + 0.1 * torch.randn(H, device=dev)).half()
+        for _ in range(3):   # the step counter advances; the result does not change
+            x, out = x0.clone(), torch.empty(H, dtype=torch.half, device=dev)
+            K.tp_allreduce_add_rmsnorm(peers, 0, hdr, x, w, out, 1e-5)
+            xr, ref = x0.clone(), torch.empty(H, dtype=torch.half, device=dev)
+            K.add_rmsnorm(xr, part, w, ref, 1e-5)
+            assert torch.equal(x, xr) and torch.equal(out, ref)
+            dst = torch.zeros(n, dtype=torch.half, device=dev)
+            K.tp_allgather(peers, 0, off2, dst, n)
+            assert torch.equal(dst, shard)
+        assert K.comm_error(base) == 0
+        K.comm_reset(base)
+    finally:
+        K.comm_free(base)
+
+
 def test_embed_and_argmax(K):
     torch.manual_seed(0)
     emb = torch.randn(1000, 2048, device=dev).half()

@@ -15,7 +15,7 @@ def _cfg():
                                  head_dim=128)
 
 
-def _rank_main(rank, world, port, out, modes):
+def _rank_main(rank, world, port, out, modes, tp_comm):
     import datetime
     import torch.distributed as dist
     from llm_decode_kernels_b200.model import DecodeConfig, Model
@@ -27,8 +27,10 @@ def _rank_main(rank, world, port, out, modes):
     try:
         c = _cfg()
         sd = {k: (v * 3 if v.dim() == 2 else v) for k, v in random_llama_state(c, "cpu", 3).items()}
-        m = Model(sd, c, DecodeConfig(max_ctx=96, seed=4, device=f"cuda:{rank}", tp_rank=rank, tp_world=world))
+        m = Model(sd, c, DecodeConfig(max_ctx=96, seed=4, device=f"cuda:{rank}", tp_rank=rank, tp_world=world,
+                                      tp_comm=tp_comm))
         assert not m.persistent and m.n_q == 8 // world and m.V == 3000 // world
+        assert (m.comm is not None) == (tp_comm == "p2p")
         g = torch.Generator().manual_seed(1)
         prompt = torch.randint(0, 3000, (20,), generator=g).tolist()
         res = {}
@@ -36,20 +38,26 @@ def _rank_main(rank, world, port, out, modes):
             m.kv.zero_()
             m.prepare(96, use_graph=use_graph, part_size=32)
             m.reset(0)
+            assert (m.graph is not None) == (use_graph and tp_comm == "p2p")
             res[use_graph] = m.teacher_force(prompt, use_graph=use_graph, collect_logits=True).float().cpu()
         toks = m.generate(prompt, 12, use_graph=modes[-1])
+        assert m.step_error() == 0
+        if len(modes) == 2:   # the captured graph replays exactly what the eager launches compute
+            assert torch.equal(res[modes[0]], res[modes[1]])
         if rank == 0:
             torch.save({"logits": res[modes[-1]], "tokens": toks, "prompt": prompt}, out)
         dist.barrier()
+        if m.comm is not None:
+            m.comm.close()
     finally:
         dist.destroy_process_group()
 
 
-def _spawn(world, out, modes, limit_s=150):
+def _spawn(world, out, modes, tp_comm, limit_s=150):
     """Child processes with a deadline: a rank that never returns is killed and the test fails, it does not hang."""
     ctx = mp.get_context("spawn")
-    port = 29900 + (os.getpid() + len(modes)) % 1000
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, out, modes)) for r in range(world)]
+    port = 29900 + (os.getpid() + len(modes) + len(tp_comm)) % 1000
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, out, modes, tp_comm)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -61,14 +69,15 @@ def _spawn(world, out, modes, limit_s=150):
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
 
 
-@pytest.mark.parametrize("use_graph", [False])   # tensor-parallel steps are launched eagerly (see Model.capture)
-def test_tp2_matches_single_gpu(tmp_path, use_graph):
+@pytest.mark.parametrize("tp_comm,modes", [("nccl", (False,)),          # NCCL collectives: launched eagerly
+                                           ("p2p", (False, True))])     # peer-memory exchange: eager, then one graph
+def test_tp2_matches_single_gpu(tmp_path, tp_comm, modes):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from llm_decode_kernels_b200.model import DecodeConfig, Model
     from llm_decode_kernels_b200.shapes import random_llama_state
     out = str(tmp_path / "tp2.pt")
-    _spawn(2, out, (use_graph,))
+    _spawn(2, out, modes, tp_comm)
     got = torch.load(out)
     c = _cfg()
     sd = {k: (v * 3 if v.dim() == 2 else v) for k, v in random_llama_state(c, "cpu", 3).items()}
