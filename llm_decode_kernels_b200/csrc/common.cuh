@@ -30,6 +30,41 @@ DEVI float warp_max(float v) {
   return v;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------------------
+// The decode step is a chain of small kernels, each waiting for the one before it; between two ordinary launches the
+// GPU drains, flushes and only then schedules the next grid. Launched with launch_pdl(), a kernel may be scheduled
+// while its predecessor still runs: every kernel says "my dependents may be scheduled" at its top
+// (pdl_launch_dependents) and then blocks in pdl_wait() until the predecessor has completed and its writes are
+// visible. Nothing that another kernel produced may be read before pdl_wait(); what does not depend on the
+// predecessor (weights) may be fetched before it. Both are no-ops in a kernel launched the ordinary way.
+DEVI void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+DEVI void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool pdl_enabled();   // false when the environment variable B200_PDL is set to 0 (for A/B timing)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// launch_pdl(...) inside a function that returns cudaError_t: a refused launch is returned at once
+#define B200_LAUNCH(...)                               \
+  do {                                                 \
+    const cudaError_t pe_ = launch_pdl(__VA_ARGS__);   \
+    if (pe_ != cudaSuccess) return pe_;                \
+  } while (0)
+
 DEVI half2 as_h2(uint32_t u) { return *reinterpret_cast<half2*>(&u); }
 DEVI uint32_t as_u32(half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 

@@ -4,8 +4,17 @@
 // data held in registers between its phases.
 #include "common.cuh"
 #include <math_constants.h>
+#include <stdlib.h>
 
 namespace b200 {
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 // ---- residual add + RMSNorm -----------------------------------------------------------------------------
 // Replaces add_rmsnorm_launch (reference kernels/fused_norm.cu:56-58). Rounding as in HF LlamaRMSNorm
@@ -18,6 +27,8 @@ constexpr int kNormMaxChunks = 8;  // H <= 512 * 8 * 8 = 32768
 __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(half* __restrict__ x, const half* __restrict__ delta, const half* __restrict__ w,
                    half* __restrict__ out, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float part[kNormThreads / 32];
   const int tid = threadIdx.x, nchunk = H >> 3;
   uint4 xv[kNormMaxChunks];
@@ -68,7 +79,8 @@ add_rmsnorm_kernel(half* __restrict__ x, const half* __restrict__ delta, const h
 
 cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int H, float eps,
                                  cudaStream_t st) {
-  add_rmsnorm_kernel<<<1, kNormThreads, 0, st>>>((half*)x, (const half*)delta, (const half*)w, (half*)out, H, eps);
+  B200_LAUNCH(add_rmsnorm_kernel, dim3(1), dim3(kNormThreads), 0, st, (half*)x, (const half*)delta, (const half*)w,
+              (half*)out, H, eps);
   return cudaPeekAtLastError();
 }
 
@@ -77,6 +89,8 @@ cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void
 // out[i] = half(silu_fp32(gate_i)) *_fp16 up_i (reference reference/ref_ops.py:23-27).
 __global__ void swiglu_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out,
                               int nchunk) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= nchunk) return;
   const uint4 gv = gate[i], uv = up[i];
@@ -93,8 +107,8 @@ __global__ void swiglu_kernel(const uint4* __restrict__ gate, const uint4* __res
 
 cudaError_t swiglu_dispatch(const void* gu, void* out, int I, cudaStream_t st) {
   const int nchunk = I >> 3, threads = 128;
-  swiglu_kernel<<<(nchunk + threads - 1) / threads, threads, 0, st>>>(
-      (const uint4*)gu, (const uint4*)((const half*)gu + I), (uint4*)out, nchunk);
+  B200_LAUNCH(swiglu_kernel, dim3((nchunk + threads - 1) / threads), dim3(threads), 0, st, (const uint4*)gu, (const
+              uint4*)((const half*)gu + I), (uint4*)out, nchunk);
   return cudaPeekAtLastError();
 }
 
@@ -108,6 +122,8 @@ __global__ void rope_append_kernel(half* __restrict__ qkv, const float* __restri
                                    const float* __restrict__ sin_t, const int* __restrict__ pos_ptr,
                                    const int* __restrict__ bt, int bt_stride, half* __restrict__ kc,
                                    half* __restrict__ vc, int n_q, int n_kv, int D, int log2P) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, d2 = D >> 1;
   const int pos = pos_ptr[b];
   half* v = qkv + ((size_t)b * (n_q + 2 * n_kv) + head) * D;
@@ -129,8 +145,8 @@ __global__ void rope_append_kernel(half* __restrict__ qkv, const float* __restri
 cudaError_t rope_append_dispatch(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt,
                                  int bt_stride, void* kc, void* vc, int B, int n_q, int n_kv, int D, int log2P,
                                  cudaStream_t st) {
-  rope_append_kernel<<<dim3(n_q + 2 * n_kv, B), D / 2, 0, st>>>((half*)qkv, cos_t, sin_t, pos, bt, bt_stride,
-                                                                (half*)kc, (half*)vc, n_q, n_kv, D, log2P);
+  B200_LAUNCH(rope_append_kernel, dim3(n_q + 2 * n_kv, B), dim3(D / 2), 0, st, (half*)qkv, cos_t, sin_t, pos, bt,
+              bt_stride, (half*)kc, (half*)vc, n_q, n_kv, D, log2P);
   return cudaPeekAtLastError();
 }
 
@@ -138,13 +154,16 @@ cudaError_t rope_append_dispatch(void* qkv, const float* cos_t, const float* sin
 // Stands in for the torch.index_select of the reference's step (runtime/model.py:218).
 __global__ void embed_row_kernel(const uint4* __restrict__ emb, const long long* __restrict__ tok,
                                  uint4* __restrict__ x, int nchunk) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < nchunk) x[i] = emb[(size_t)tok[0] * nchunk + i];
 }
 
 cudaError_t embed_row_dispatch(const void* emb, const long long* tok, void* x, int H, cudaStream_t st) {
   const int nchunk = H >> 3;
-  embed_row_kernel<<<(nchunk + 255) / 256, 256, 0, st>>>((const uint4*)emb, tok, (uint4*)x, nchunk);
+  B200_LAUNCH(embed_row_kernel, dim3((nchunk + 255) / 256), dim3(256), 0, st, (const uint4*)emb, tok, (uint4*)x,
+              nchunk);
   return cudaPeekAtLastError();
 }
 
@@ -156,6 +175,8 @@ cudaError_t embed_row_dispatch(const void* emb, const long long* tok, void* x, i
 __global__ void __launch_bounds__(1024)
 argmax_kernel(const half* __restrict__ logits, int V, long long* __restrict__ tok, int* __restrict__ pos,
               long long* __restrict__ history) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ unsigned long long part[32];
   unsigned long long best = 0ull;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -193,7 +214,7 @@ argmax_kernel(const half* __restrict__ logits, int V, long long* __restrict__ to
 
 cudaError_t argmax_dispatch(const void* logits, int V, long long* tok, int* pos, long long* history,
                             cudaStream_t st) {
-  argmax_kernel<<<1, 1024, 0, st>>>((const half*)logits, V, tok, pos, history);
+  B200_LAUNCH(argmax_kernel, dim3(1), dim3(1024), 0, st, (const half*)logits, V, tok, pos, history);
   return cudaPeekAtLastError();
 }
 

@@ -24,6 +24,8 @@ template <int R, int UNR>
 __global__ void __launch_bounds__(256)
 gemv_w4a16_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ, const uint4* __restrict__ X,
                   half* __restrict__ y, int N, int K, int log2G) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ uint4 xs[];  // K/8 chunks of 8 pre-scaled activations
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int U = K >> 5;          // 16-byte weight chunks per row
@@ -88,6 +90,8 @@ gemv_w4a16_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ, co
 __global__ void gemv_w4a16_plain_kernel(const uint32_t* __restrict__ Wp, const half2* __restrict__ SZ,
                                         const half* __restrict__ x, half* __restrict__ y, int N, int K,
                                         int log2G) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= N) return;
   const int words = K >> 3, ng = K >> log2G;
@@ -153,6 +157,7 @@ gemv_w4a16_seg_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
   float* part = xsum + U;                                                 // [tile_units * 2][segs]
   __shared__ float red[kSegWarps];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
 
   // ---- this CTA's tile and this warp's share of it
   const int units = (N + 1) >> 1;
@@ -268,6 +273,7 @@ gemv_w4a16_seg_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
     int j = rank;
     if (j < nu) SEG_LOAD(r0, j);
     if (!staged) {   // the weights just requested travel while x is staged (two barriers, one L2 round trip)
+      pdl_wait();    // weights do not depend on the previous kernel, x does: from here on it may be read
       stage_x_all();
       staged = true;
     }
@@ -307,9 +313,8 @@ static cudaError_t launch_seg(const void* Wp, const void* SZ, const void* x, voi
     if (e != cudaSuccess) return e;
     configured = smem;
   }
-  gemv_w4a16_seg_kernel<<<blocks, kSegThreads, smem, st>>>((const uint4*)Wp, (const half2*)SZ, (const uint2*)x, (half*)y,
-                                                           N, K, log2G, tile);
-  return cudaPeekAtLastError();
+  return launch_pdl(gemv_w4a16_seg_kernel, dim3(blocks), dim3(kSegThreads), smem, st, (const uint4*)Wp, (const half2*)SZ,
+                    (const uint2*)x, (half*)y, N, K, log2G, tile);
 }
 
 template <int R, int UNR>
@@ -323,9 +328,8 @@ static cudaError_t launch_rows(const void* Wp, const void* SZ, const void* x, vo
                                          (int)smem);
     if (e != cudaSuccess) return e;
   }
-  gemv_w4a16_kernel<R, UNR><<<blocks, 32 * warps, smem, st>>>((const uint4*)Wp, (const half2*)SZ, (const uint4*)x,
-                                                              (half*)y, N, K, log2G);
-  return cudaPeekAtLastError();
+  return launch_pdl(gemv_w4a16_kernel<R, UNR>, dim3(blocks), dim3(32 * warps), smem, st, (const uint4*)Wp,
+                    (const half2*)SZ, (const uint4*)x, (half*)y, N, K, log2G);
 }
 
 // stage 0: plain kernel. stage >= 1 with R in {1,2,4,8} and warps in 1..8: the row-per-warp kernel in that
@@ -334,9 +338,8 @@ cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, con
                                 int N, int K, int log2G, cudaStream_t st) {
   if (stage == 0) {
     const int w = (warps >= 1 && warps <= 8) ? warps : 4;
-    gemv_w4a16_plain_kernel<<<(N + w - 1) / w, 32 * w, 0, st>>>((const uint32_t*)Wp, (const half2*)SZ,
-                                                                 (const half*)x, (half*)y, N, K, log2G);
-    return cudaPeekAtLastError();
+    return launch_pdl(gemv_w4a16_plain_kernel, dim3((N + w - 1) / w), dim3(32 * w), 0, st, (const uint32_t*)Wp,
+                      (const half2*)SZ, (const half*)x, (half*)y, N, K, log2G);
   }
   if (!(R == 1 || R == 2 || R == 4 || R == 8) || warps < 1 || warps > 8) {
     if ((reinterpret_cast<uintptr_t>(y) & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0)

@@ -49,6 +49,8 @@ paged_attn_partial_kernel(const half* __restrict__ q, const half* __restrict__ k
                           const int* __restrict__ bt, int bt_stride, const int* __restrict__ pos_ptr, int n_kv,
                           int log2P, int PS, float scale, float* __restrict__ o_part, float* __restrict__ m_part,
                           float* __restrict__ l_part, half* __restrict__ out, int max_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int DPL = D / 32;      // output dims owned by one lane
   constexpr int CHUNKS = D / 8;    // 16-byte chunks per K/V row
   __shared__ __align__(16) float q_s[HPG][D];
@@ -268,6 +270,8 @@ paged_attn_staged_kernel(const half* __restrict__ q, const half* __restrict__ kc
                          const int* __restrict__ bt, int bt_stride, const int* __restrict__ pos_ptr, int n_kv,
                          int log2P, int PS, float scale, float* __restrict__ o_part, float* __restrict__ m_part,
                          float* __restrict__ l_part, half* __restrict__ out, int max_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int T = kStageTokens;
   constexpr int NS = attn_ring_stages<D>();
   constexpr int LPT = D / 8;               // lanes that share one token in the score phase
@@ -502,6 +506,8 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
                       const int* __restrict__ bt, int bt_stride, const int* __restrict__ pos_ptr, int n_kv, int log2P,
                       int PS, float scale, float* __restrict__ o_part, float* __restrict__ m_part,
                       float* __restrict__ l_part, half* __restrict__ out, int max_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int TS = kStageTokens / KH;    // tokens per ring stage (of each of the KH heads)
   constexpr int NS = attn_ring_stages<D>();
   constexpr int WPH = kAttnWarps / KH;     // arithmetic warps per kv head, 16 tokens of a stage each
@@ -736,6 +742,8 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
 __global__ void paged_attn_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ m_part,
                                           const float* __restrict__ l_part, const int* __restrict__ pos_ptr, int PS,
                                           int max_splits, int D, half* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int ctx = pos_ptr[b] + 1;
   const int nsplit = min((ctx + PS - 1) / PS, max_splits);
@@ -786,9 +794,9 @@ static cudaError_t launch_mma(const AttnArgs& a, int dev, cudaStream_t st) {
   static bool configured[64] = {};
   const cudaError_t e = allow_ring(paged_attn_mma_kernel<D, HPG, KH>, attn_ring_bytes<D>(), &configured[dev]);
   if (e != cudaSuccess) return e;
-  paged_attn_mma_kernel<D, HPG, KH><<<dim3(a.n_kv / KH, a.max_splits, a.B), kMmaThreads, attn_ring_bytes<D>(), st>>>(
-      a.q, a.kc, a.vc, a.bt, a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale, a.o_part, a.m_part, a.l_part, a.out,
-      a.max_splits);
+  B200_LAUNCH(paged_attn_mma_kernel<D, HPG, KH>, dim3(a.n_kv / KH, a.max_splits, a.B), dim3(kMmaThreads),
+              attn_ring_bytes<D>(), st, a.q, a.kc, a.vc, a.bt, a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale,
+              a.o_part, a.m_part, a.l_part, a.out, a.max_splits);
   return cudaPeekAtLastError();
 }
 
@@ -807,13 +815,13 @@ static cudaError_t launch_partial_for(int kind, const AttnArgs& a, cudaStream_t 
     static bool configured[64] = {};
     const cudaError_t e = allow_ring(paged_attn_staged_kernel<D, HPG>, attn_ring_bytes<D>(), &configured[dev]);
     if (e != cudaSuccess) return e;
-    paged_attn_staged_kernel<D, HPG><<<grid, kAttnThreads, attn_ring_bytes<D>(), st>>>(
-        a.q, a.kc, a.vc, a.bt, a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale, a.o_part, a.m_part, a.l_part, a.out,
-        a.max_splits);
+    B200_LAUNCH(paged_attn_staged_kernel<D, HPG>, dim3(grid), dim3(kAttnThreads), attn_ring_bytes<D>(), st, a.q, a.kc,
+                a.vc, a.bt, a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale, a.o_part, a.m_part, a.l_part, a.out,
+                a.max_splits);
   } else {
-    paged_attn_partial_kernel<D, HPG><<<grid, kAttnThreads, 0, st>>>(a.q, a.kc, a.vc, a.bt, a.bt_stride, a.pos, a.n_kv,
-                                                                     a.log2P, a.PS, a.scale, a.o_part, a.m_part,
-                                                                     a.l_part, a.out, a.max_splits);
+    B200_LAUNCH(paged_attn_partial_kernel<D, HPG>, dim3(grid), dim3(kAttnThreads), 0, st, a.q, a.kc, a.vc, a.bt,
+                a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale, a.o_part, a.m_part, a.l_part, a.out,
+                a.max_splits);
   }
   return cudaPeekAtLastError();
 }
@@ -850,8 +858,8 @@ cudaError_t paged_attention_dispatch(int version, const void* q, const void* kc,
   cudaError_t e = D == 64 ? launch_partial<64>(hpg, kind, a, st) : launch_partial<128>(hpg, kind, a, st);
   if (e != cudaSuccess) return e;
   if (max_splits > 1) {
-    paged_attn_combine_kernel<<<dim3(n_q, B), D, 0, st>>>(o_part, m_part, l_part, pos, PS, max_splits, D,
-                                                          (half*)out);
+    B200_LAUNCH(paged_attn_combine_kernel, dim3(n_q, B), dim3(D), 0, st, o_part, m_part, l_part, pos, PS, max_splits,
+                D, (half*)out);
     e = cudaPeekAtLastError();
   }
   return e;

@@ -94,6 +94,8 @@ DEVI bool exchange_flags(const CommPeers& P, int rank, int W) {
 __global__ void __launch_bounds__(kCommThreads)
 tp_allreduce_add_rmsnorm_kernel(const CommPeers P, int rank, int W, size_t off, half* __restrict__ x,
                                 const half* __restrict__ w, half* __restrict__ out, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int MAXC = 4;
   __shared__ float part[kCommThreads / 32];
   if (!exchange_flags(P, rank, W)) return;
@@ -153,6 +155,8 @@ tp_allreduce_add_rmsnorm_kernel(const CommPeers P, int rank, int W, size_t off, 
 // dst[r * n + i] = rank r's shard[i] (shards of n fp16 values at `off` of every block). One block of 1024 threads.
 __global__ void __launch_bounds__(kCommThreads)
 tp_allgather_kernel(const CommPeers P, int rank, int W, size_t off, half* __restrict__ dst, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (!exchange_flags(P, rank, W)) return;
   const int tid = threadIdx.x;
   if ((n & 7) == 0) {
@@ -178,8 +182,8 @@ cudaError_t tp_allreduce_add_rmsnorm_dispatch(const void* const* peers, int rank
                                               const void* w, void* out, int H, float eps, cudaStream_t st) {
   CommPeers P = {};
   for (int r = 0; r < W; ++r) P.p[r] = (uint8_t*)peers[r];
-  tp_allreduce_add_rmsnorm_kernel<<<1, kCommThreads, 0, st>>>(P, rank, W, off, (half*)x, (const half*)w, (half*)out, H,
-                                                              eps);
+  B200_LAUNCH(tp_allreduce_add_rmsnorm_kernel, dim3(1), dim3(kCommThreads), 0, st, P, rank, W, off, (half*)x, (const
+              half*)w, (half*)out, H, eps);
   return cudaPeekAtLastError();
 }
 
@@ -187,7 +191,7 @@ cudaError_t tp_allgather_dispatch(const void* const* peers, int rank, int W, siz
                                   cudaStream_t st) {
   CommPeers P = {};
   for (int r = 0; r < W; ++r) P.p[r] = (uint8_t*)peers[r];
-  tp_allgather_kernel<<<1, kCommThreads, 0, st>>>(P, rank, W, off, (half*)dst, n);
+  B200_LAUNCH(tp_allgather_kernel, dim3(1), dim3(kCommThreads), 0, st, P, rank, W, off, (half*)dst, n);
   return cudaPeekAtLastError();
 }
 
