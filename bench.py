@@ -279,7 +279,7 @@ def run_b200_arm(args, rank, world, local_rank):
     ctx_mid = PROMPT_LEN + NEW_TOKENS // 2
     step_bytes = m.bytes_per_token(ctx_mid)
     us_per_token = dev_ms * 1e3 / (args.steps * NEW_TOKENS)
-    gemv_roofline = {"kernel": "gemv_w4a16_seg_kernel", "achieved": round(achieved, 1), "unit": "GB/s",
+    gemv_roofline = {"kernel": "gemv_w4a16_mma_kernel", "achieved": round(achieved, 1), "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "launches": len(lins), "bytes_per_launch_mix": gemv_bytes,
                      "how": "the 89 GEMVs of one token replayed as one graph, CUDA events, 50 replays"}
     if m.persistent:

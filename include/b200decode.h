@@ -38,7 +38,9 @@ const char* b200_last_cuda_error(void);
  * Wp: packed int32 [N, K/8] (16B), SZ: half2 (scale, zero) [N, K >> log2G], x: [K] (16B), y: [N].
  * K % 32 == 0, group = 2^log2G >= 32 and divides K.
  * stage 0 = plain one-thread-per-weight kernel. stage >= 1 with R in {1,2,4,8} and warps in 1..8 runs
- * that rows-per-warp / warps-per-block configuration; any other R (use 0) lets the library choose by shape.
+ * that rows-per-warp / warps-per-block configuration on the CUDA cores; R = 16 runs the segmented CUDA-core kernel;
+ * any other R (use 0) lets the library choose: the tensor-core kernel (masked nibbles fed to mma.m16n8k16 as fp16
+ * subnormals, fp32 accumulation) when K % 128 == 0 and the group size is a multiple of 128, else the segmented one.
  * pf is accepted for signature compatibility and ignored. */
 int b200_gemv_w4a16(int stage, int R, int warps, int pf, const void* Wp, const void* SZ, const void* x, void* y,
                     int N, int K, int log2G, void* stream);
@@ -78,6 +80,16 @@ int b200_rope_append(void* qkv, const float* cos_t, const float* sin_t, const in
                      void* vc, int n_q, int n_kv, int log2P, void* stream);
 
 /* ---- additions: no counterpart among the reference's launchers ---- */
+
+/* The same GEMV from a copy of the matrix in "tile layout": per 16-row tile and per 128 columns, the bytes in the
+ * order the tensor-core kernel's warps read them (512 B for rows 0-7 of the tile, 512 B for rows 8-15, the 16 rows'
+ * (scale, zero)), tiles and column blocks back to back. Every warp load is then one contiguous 512-byte read; on
+ * matrices with long rows this is worth 1.5x over the row-major tensors (DRAM locality). b200_gemv_w4a16_tiled_bytes
+ * gives the size of the copy (0 if K % 128 != 0), b200_gemv_w4a16_tile_repack fills it once from the quantizer's
+ * tensors (group size a multiple of 128), b200_gemv_w4a16_tiled computes y = W x from it (x 8-byte aligned). */
+size_t b200_gemv_w4a16_tiled_bytes(int N, int K);
+int b200_gemv_w4a16_tile_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, void* stream);
+int b200_gemv_w4a16_tiled(const void* Wt, const void* x, void* y, int N, int K, void* stream);
 
 /* Like b200_bw_read, but through the path the persistent step kernel uses: each of `blocks` CTAs streams its share
  * of the buffer into a shared-memory ring of `stages` x `stage_bytes` with 1-D bulk async copies. stage_bytes a

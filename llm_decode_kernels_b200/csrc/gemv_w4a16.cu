@@ -317,6 +317,287 @@ static cudaError_t launch_seg(const void* Wp, const void* SZ, const void* x, voi
                     (const uint2*)x, (half*)y, N, K, log2G, tile);
 }
 
+// ---- tensor-core GEMV: the library's default where the shape allows -------------------------------------------------------
+// The CUDA-core kernels above spend ~3.6 issued instructions per weight (mask, shift, half2 FMA, conversions, shuffles)
+// and are bound by instruction issue at 45-60 % of the HBM bandwidth of this part. The quantization format happens to
+// be a tensor-core operand already: (word & 0x000F000F) is the fp16 pair (q[8j], q[8j+1]) * 2^-24 and
+// (word & 0x00F000F0) the pair (q[8j+2], q[8j+3]) * 2^-20 - two consecutive-k elements of one row, which is what one
+// register of the A fragment of mma.m16n8k16 holds. So a 16-row x 128-weight block of W is 8 MMAs whose A registers
+// are masked words, with x (scaled by 2^s / 2^(s-4) as in the kernels above) in column 0 of B; the accumulators are
+// fp32, and scale and zero point are applied once per group:
+//     y += scale * (2^(24-s) * acc - zero * sum_group(x)).
+// Seven of the eight B columns are zero: the MMA is not used for its FLOPs but because it replaces 128 half2 FMAs,
+// their conversions and the cross-lane reduction by 8 instructions (about 1 issued instruction per weight instead of
+// 3.6), and because its fp32 accumulation removes the fp16 rounding of the half2 chains.
+//   lane (g = lane / 4, t = lane % 4) loads 16 bytes (32 weights: words 4t .. 4t+3 of the group) of row g and of row
+//   g + 8; word j feeds k-steps 2j (low byte's nibbles) and 2j + 1 (after a shift by 8). B's k-slots are dealt to match:
+//   lane (0, t) holds the 32 staged activations of the same 32 columns, other lanes hold zeros.
+// A block of 8 warps stages x once and walks row tiles of 16 rows; `ksplit` warps share a tile by splitting K (small
+// matrices need the parallelism) and meet in shared memory, with ksplit = 1 a warp owns its tile and there is no
+// barrier in the loop. Needs K % 128 == 0 and a group size that is a multiple of 128.
+constexpr int kMmaGemvWarps = 8, kMmaGemvThreads = kMmaGemvWarps * 32;
+
+DEVI void mma16816_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D = A * B (no accumulator input: the first MMA of a unit starts from zero without clearing registers)
+DEVI void mma16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// A batch = 4 consecutive 128-weight units of two rows and their (scale, zero). A lane's four 16-byte loads per row
+// are 64 bytes apart, so the warp's loads of a batch cover 256 contiguous bytes of each of its 16 rows, issued back to
+// back (row-buffer locality in DRAM), and 8 loads per lane are in flight per batch.
+constexpr int kMmaBatch = 4;
+struct MmaBatchRegs { uint4 wa[kMmaBatch], wb[kMmaBatch]; half2 sa[kMmaBatch], sb[kMmaBatch]; };
+
+//
+// TILED = true reads the weights from the tile layout made by gemv_tile_repack_kernel instead of the quantizer's
+// row-major tensors. Row-major, the 16 rows of a tile are K/2 bytes apart and every load instruction of a warp touches
+// 16 separate 64-byte pieces; measured on 134 MB matrices the kernel then moves 4.6 TB/s with 512-byte rows but only
+// 3.4 TB/s with 8 KB rows (DRAM sees scattered short bursts). In the tile layout the bytes of a tile are stored in
+// the order the warp consumes them: per 128-weight unit 512 bytes for rows g (lane l at 16 l), 512 bytes for rows
+// g + 8, then the 16 rows' (scale, zero) - 1088 bytes, units and tiles back to back - so every warp load is one
+// contiguous 512-byte read and a warp streams through memory in address order.
+constexpr int kTileUnitBytes = 1088;
+
+template <bool TILED>
+__global__ void __launch_bounds__(kMmaGemvThreads, 2)
+gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ, const uint2* __restrict__ X,
+                      half* __restrict__ y, int N, int K, int log2G, int ksplit, int rounds) {
+  extern __shared__ __align__(16) uint8_t mma_smem[];
+  const int nunit = K >> 7;                                                // 128-weight units per row
+  uint4* xin = reinterpret_cast<uint4*>(mma_smem);                         // [K/8] staged x, 16 bytes = one word's 8
+  uint4* zeros = xin + (K >> 3);                                           // 64 zero bytes: B of the lanes with g != 0
+  float* part = reinterpret_cast<float*>(zeros + 4);                       // [kMmaGemvWarps][16]
+  float* xsg = part + kMmaGemvWarps * 16;                                  // [nunit] sum of x over each unit
+  __shared__ float red[kMmaGemvWarps];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  pdl_launch_dependents();
+
+  const int ntiles = (N + 15) >> 4, tiles_per_round = kMmaGemvWarps / ksplit;
+  const int kpart = warp % ksplit, tslot = warp / ksplit;
+  const int ub = (int)(((long long)nunit * kpart) / ksplit), ue = (int)(((long long)nunit * (kpart + 1)) / ksplit);
+  const int ng = K >> log2G, rowU4 = K >> 5;   // (scale, zero) entries and 16-byte pieces per row
+  const int last = N - 1;
+
+  const int tile_step = gridDim.x * tiles_per_round;   // round r: tile groups r * gridDim.x + blockIdx.x
+  int tile = blockIdx.x * tiles_per_round + tslot;
+  // Running pointers of the batch that will be loaded next: rows g and g + 8 of a tile (rows past the end repeat the
+  // last one), this lane's 16-byte piece of unit u. `full` batches need no predicate; the host gives every warp a
+  // K range that is a whole number of batches whenever K allows.
+  const uint4 *pa, *pb;
+  const half2 *za, *zb;
+  auto seek = [&](int tl) {
+    if (TILED) {   // Wp is the tile layout; SZ is unused
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(Wp) + ((size_t)tl * nunit + ub) * kTileUnitBytes;
+      pa = reinterpret_cast<const uint4*>(base) + lane;
+      pb = pa + 32;
+      za = reinterpret_cast<const half2*>(base + 1024) + g;
+      zb = za + 8;
+    } else {
+      const int ra = min(16 * tl + g, last), rb = min(16 * tl + g + 8, last);
+      pa = Wp + (size_t)ra * rowU4 + 4 * ub + t;
+      pb = Wp + (size_t)rb * rowU4 + 4 * ub + t;
+      za = SZ + (size_t)ra * ng;
+      zb = SZ + (size_t)rb * ng;
+    }
+  };
+  auto load = [&](int u0, MmaBatchRegs& d) {
+    constexpr int step = TILED ? kTileUnitBytes / 16 : 4;   // 16-byte pieces from one unit to the next
+#pragma unroll
+    for (int i = 0; i < kMmaBatch; ++i) {
+      if (u0 + i < ue) {
+        d.wa[i] = ld_stream(pa + step * i);
+        d.wb[i] = ld_stream(pb + step * i);
+        if (TILED) {
+          d.sa[i] = __ldg(za + (kTileUnitBytes / 4) * i);
+          d.sb[i] = __ldg(zb + (kTileUnitBytes / 4) * i);
+        } else {
+          const int gi = ((u0 + i) << 7) >> log2G;
+          d.sa[i] = __ldg(za + gi);
+          d.sb[i] = __ldg(zb + gi);
+        }
+      }
+    }
+    pa += step * kMmaBatch;
+    pb += step * kMmaBatch;
+    if (TILED) {
+      za += (kTileUnitBytes / 4) * kMmaBatch;
+      zb += (kTileUnitBytes / 4) * kMmaBatch;
+    }
+  };
+  // the first weights travel while x is staged: they do not depend on the previous kernel, x does
+  MmaBatchRegs cur, nxt;
+  if (tile < ntiles) {
+    seek(tile);
+    load(ub, cur);
+  }
+  pdl_wait();
+
+  // ---- stage x: max|x| -> power-of-two scale -> (x0 x1) 2^s, (x2 x3) 2^(s-4), ... and the unit sums
+  float mx = 0.f;
+  for (int i = tid; i < (K >> 2); i += kMmaGemvThreads) {
+    const uint2 v = __ldg(X + i);
+    reinterpret_cast<uint2*>(xin)[i] = v;
+    const float2 a = __half22float2(__habs2(as_h2(v.x))), b = __half22float2(__habs2(as_h2(v.y)));
+    mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)));
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  if (tid < 4) zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+  float xmax = 0.f;
+#pragma unroll
+  for (int k = 0; k < kMmaGemvWarps; ++k) xmax = fmaxf(xmax, red[k]);
+  const XScale sc = scale_for(xmax);
+  for (int u = warp; u < nunit; u += kMmaGemvWarps) {   // one warp per unit: lane = granule of 4 activations
+    uint2 v = reinterpret_cast<uint2*>(xin)[32 * u + lane];
+    const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
+    const float sm = warp_sum((a.x + a.y) + (b.x + b.y));
+    if (lane == 0) xsg[u] = sm;
+    v.x = as_u32(__hmul2(as_h2(v.x), sc.lo));
+    v.y = as_u32(__hmul2(as_h2(v.y), sc.hi));
+    reinterpret_cast<uint2*>(xin)[32 * u + lane] = v;
+  }
+  __syncthreads();
+
+  // B operand: lanes with g == 0 walk x (16 pieces of 16 bytes per unit), the others keep reading the zero block
+  const uint4* xbase = g == 0 ? xin + 4 * t : zeros;
+  const int xstride = g == 0 ? 16 : 0;
+
+  for (int r = 0; r < rounds; ++r, tile += tile_step) {
+    float ya = 0.f, yb = 0.f;
+    if (tile < ntiles) {
+      for (int u0 = ub; u0 < ue; u0 += kMmaBatch) {
+        // the next batch's loads (this tile's, or the first of the warp's next tile) fly during this batch's arithmetic
+        if (u0 + kMmaBatch < ue) {
+          load(u0 + kMmaBatch, nxt);
+        } else if (r + 1 < rounds && tile + tile_step < ntiles) {
+          seek(tile + tile_step);
+          load(ub, nxt);
+        }
+#pragma unroll
+        for (int i = 0; i < kMmaBatch; ++i) {
+          const int u = u0 + i;
+          if (u < ue) {   // warp-uniform
+            const uint4* xb = xbase + u * xstride;
+            float c[4];
+            const uint32_t wa[4] = {cur.wa[i].x, cur.wa[i].y, cur.wa[i].z, cur.wa[i].w};
+            const uint32_t wb[4] = {cur.wb[i].x, cur.wb[i].y, cur.wb[i].z, cur.wb[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 xv = xb[j];
+              const uint32_t a8 = wa[j] >> 8, b8 = wb[j] >> 8;
+              if (j == 0)
+                mma16816_zero(c, wa[j] & 0x000F000Fu, wb[j] & 0x000F000Fu, wa[j] & 0x00F000F0u, wb[j] & 0x00F000F0u,
+                              xv.x, xv.y);
+              else
+                mma16816_acc(c, wa[j] & 0x000F000Fu, wb[j] & 0x000F000Fu, wa[j] & 0x00F000F0u, wb[j] & 0x00F000F0u,
+                             xv.x, xv.y);
+              mma16816_acc(c, a8 & 0x000F000Fu, b8 & 0x000F000Fu, a8 & 0x00F000F0u, b8 & 0x00F000F0u, xv.z, xv.w);
+            }
+            // column 0 of the product sits in c[0] (row g) and c[2] (row g + 8) of the lanes with t == 0
+            const float2 sa = __half22float2(cur.sa[i]), sb = __half22float2(cur.sb[i]);
+            const float xs = xsg[u];
+            ya = fmaf(sa.x, fmaf(c[0], sc.resc, -sa.y * xs), ya);
+            yb = fmaf(sb.x, fmaf(c[2], sc.resc, -sb.y * xs), yb);
+          }
+        }
+        cur = nxt;
+      }
+    }
+    if (ksplit == 1) {
+      if (t == 0 && tile < ntiles) {
+        const int ra = 16 * tile + g, rb = ra + 8;
+        if (ra < N) y[ra] = __float2half(ya);
+        if (rb < N) y[rb] = __float2half(yb);
+      }
+    } else {
+      if (t == 0) { part[warp * 16 + g] = ya; part[warp * 16 + g + 8] = yb; }
+      __syncthreads();
+      if (tid < tiles_per_round * 16) {
+        const int ts = tid >> 4, row = tid & 15, tl = tile - tslot + ts;   // tile - tslot: first tile of the round
+        float v = 0.f;
+        for (int k = 0; k < ksplit; ++k) v += part[(ts * ksplit + k) * 16 + row];
+        if (tl < ntiles && 16 * tl + row < N) y[16 * tl + row] = __float2half(v);
+      }
+      __syncthreads();
+    }
+  }
+}
+
+static cudaError_t launch_mma(bool tiled, const void* Wp, const void* SZ, const void* x, void* y, int N, int K,
+                              int log2G, cudaStream_t st) {
+  const int ntiles = (N + 15) / 16, nunit = K / 128;
+  // ksplit warps share a row tile: the smallest split that gives the chip enough warps (measured: with enough tiles
+  // a warp per tile, no barrier, is as fast as any split; short of tiles, splitting K wins), as long as a warp keeps
+  // at least two units. Blocks: at most two per SM (register limit); with more tile groups than blocks every block
+  // takes `rounds` of them, interleaved over the grid so the last round is spread over all SMs.
+  const int max_blocks = 2 * kNumSMs, want_warps = (kNumSMs * 16 * 4) / 5;
+  int ksplit = 1;
+  while (ksplit < kMmaGemvWarps && ntiles * ksplit < want_warps && nunit / (2 * ksplit) >= 2) ksplit *= 2;
+  const int tpr = kMmaGemvWarps / ksplit;
+  const int groups = (ntiles + tpr - 1) / tpr;
+  const int blocks = groups < max_blocks ? groups : max_blocks;
+  const int rounds = (groups + blocks - 1) / blocks;
+  const size_t smem = (size_t)K * 2 + (size_t)nunit * 4 + kMmaGemvWarps * 16 * 4 + 64;
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  if (tiled)
+    return launch_pdl(gemv_w4a16_mma_kernel<true>, dim3(blocks), dim3(kMmaGemvThreads), smem, st, (const uint4*)Wp,
+                      (const half2*)SZ, (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds);
+  return launch_pdl(gemv_w4a16_mma_kernel<false>, dim3(blocks), dim3(kMmaGemvThreads), smem, st, (const uint4*)Wp,
+                    (const half2*)SZ, (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds);
+}
+
+// ---- tile layout -------------------------------------------------------------------------------------------------------
+// One thread per 16-byte piece of the output: 68 pieces per (tile, unit), see gemv_w4a16_mma_kernel. Rows past N are
+// stored as zero weights with scale 0, so they add nothing.
+__global__ void gemv_tile_repack_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ,
+                                        uint4* __restrict__ out, int N, int K, int log2G) {
+  const int nunit = K >> 7, u = blockIdx.x, tile = blockIdx.y, idx = threadIdx.x;
+  if (idx >= kTileUnitBytes / 16) return;
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (idx < 64) {
+    const int lane = idx & 31, g = lane >> 2, t = lane & 3, row = 16 * tile + g + 8 * (idx >> 5);
+    if (row < N) v = Wp[(size_t)row * (K >> 5) + 4 * u + t];
+  } else {
+    uint32_t e[4] = {0u, 0u, 0u, 0u};
+    for (int k = 0; k < 4; ++k) {
+      const int row = 16 * tile + 4 * (idx - 64) + k;
+      if (row < N) e[k] = as_u32(SZ[(size_t)row * (K >> log2G) + ((u << 7) >> log2G)]);
+    }
+    v = make_uint4(e[0], e[1], e[2], e[3]);
+  }
+  out[((size_t)tile * nunit + u) * (kTileUnitBytes / 16) + idx] = v;
+}
+
+size_t gemv_tiled_bytes(int N, int K) { return (size_t)((N + 15) / 16) * (K / 128) * kTileUnitBytes; }
+
+cudaError_t gemv_tile_repack_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G,
+                                      cudaStream_t st) {
+  gemv_tile_repack_kernel<<<dim3(K / 128, (N + 15) / 16), 96, 0, st>>>((const uint4*)Wp, (const half2*)SZ, (uint4*)out,
+                                                                        N, K, log2G);
+  return cudaPeekAtLastError();
+}
+
+cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, int N, int K, cudaStream_t st) {
+  return launch_mma(true, Wt, nullptr, x, y, N, K, 7, st);
+}
+
 template <int R, int UNR>
 static cudaError_t launch_rows(const void* Wp, const void* SZ, const void* x, void* y, int N, int K, int log2G,
                                int warps, cudaStream_t st) {
@@ -333,7 +614,8 @@ static cudaError_t launch_rows(const void* Wp, const void* SZ, const void* x, vo
 }
 
 // stage 0: plain kernel. stage >= 1 with R in {1,2,4,8} and warps in 1..8: the row-per-warp kernel in that
-// configuration. Anything else (R == 0): the segmented kernel.
+// configuration. R == 16: the segmented kernel. Anything else (R == 0): the tensor-core kernel, or the segmented one
+// where the shape rules it out.
 cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, const void* SZ, const void* x, void* y,
                                 int N, int K, int log2G, cudaStream_t st) {
   if (stage == 0) {
@@ -342,8 +624,11 @@ cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, con
                       (const half2*)SZ, (const half*)x, (half*)y, N, K, log2G);
   }
   if (!(R == 1 || R == 2 || R == 4 || R == 8) || warps < 1 || warps > 8) {
-    if ((reinterpret_cast<uintptr_t>(y) & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0)
-      return launch_seg(Wp, SZ, x, y, N, K, log2G, st);   // the library's own choice: the segmented kernel
+    const bool x_ok = (reinterpret_cast<uintptr_t>(x) & 7u) == 0;
+    // the library's own choice: the tensor-core kernel where the shape allows (R == 16 asks for the segmented one)
+    if (R != 16 && x_ok && K % 128 == 0 && log2G >= 7) return launch_mma(false, Wp, SZ, x, y, N, K, log2G, st);
+    if ((reinterpret_cast<uintptr_t>(y) & 3u) == 0 && x_ok)
+      return launch_seg(Wp, SZ, x, y, N, K, log2G, st);   // the segmented kernel
     R = 2;   // y not 4-byte aligned (the segmented kernel stores row pairs): row-per-warp kernel
     warps = 4;
   }

@@ -130,7 +130,8 @@ def run_tp(a):
     c = config(LLAMA3_70B, num_hidden_layers=a.layers)
     t0 = time.time()
     cfg = DecodeConfig(group=128, max_ctx=a.ctx + a.tokens + 16, page=16, device=dev, seed=0, tp_rank=rank,
-                       tp_world=world, tp_comm=a.tp_comm, step_kernel="multi")
+                       tp_world=world, tp_comm=a.tp_comm, step_kernel="multi", tile_weights=a.gemv == "tiled",
+                       gemv_stage=(2, 16, 0, 0) if a.gemv == "segmented" else None)
     m = Model(LazyRandomState(c, dev, 0), c, cfg)
     torch.cuda.empty_cache()
     build_s = time.time() - t0
@@ -147,6 +148,7 @@ def run_tp(a):
                 "n_gpus": world, "us_per_token": round(us, 1),
                 "config": {"workload": f"llama-3-70b-shape W4A16 g128 RTN, {a.layers} layers, batch 1, context "
                                        f"{a.ctx}, {a.tokens} greedy tokens", "tp": world, "tp_comm": a.tp_comm,
+                           "gemv": a.gemv,
                            "graph": m.graph is not None},
                 "bytes_per_token_per_gpu": nbytes, "floor_us_at_peak": round(nbytes / peak / 1e3, 1),
                 "frac_of_hbm_per_gpu": round(nbytes / us / 1e3 / peak, 4), "peak_hbm_gbs": peak, "peak_source": kind,
@@ -170,6 +172,9 @@ def main():
     ap.add_argument("--layers", type=int, default=80)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--tp-comm", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--gemv", default="tiled", choices=["tiled", "rowmajor", "segmented"],
+                    help="tp: tensor-core GEMV from the tile layout (default) / from the row-major tensors / the "
+                         "segmented CUDA-core GEMV")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     if a.tokens is None:

@@ -63,8 +63,8 @@ GEMV_SHAPES = {"config1 5632x2048": (5632, 2048), "qkv 2560x2048": (2560, 2048),
                "gate_up 11264x2048": (11264, 2048), "down 2048x5632": (2048, 5632), "lm_head 32000x2048": (32000, 2048),
                "70b qkv 10240x8192": (10240, 8192), "70b gate_up 57344x8192": (57344, 8192),
                "70b down 8192x28672": (8192, 28672), "70b tp8 o 8192x1024": (8192, 1024)}
-GEMV_KERNELS = {"segmented (default)": (2, 0, 0, 0), "rows R=2 warps=8": (2, 2, 8, 0), "rows R=4 warps=8": (2, 4, 8, 0),
-                "plain": (0, 1, 4, 0)}
+GEMV_KERNELS = {"tensor-core (default)": (2, 0, 0, 0), "segmented": (2, 16, 0, 0), "rows R=2 warps=8": (2, 2, 8, 0),
+                "rows R=4 warps=8": (2, 4, 8, 0), "plain": (0, 1, 4, 0)}
 
 
 def bench_gemv(K):
@@ -91,6 +91,18 @@ def bench_gemv(K):
                     K.gemv_w4a16(*cfg, m.packed, m.sz, x, y, 128)
             us = graph_time_us(run, copies)
             row[label] = {"us": round(us, 2), "gbps": round(nbytes / us / 1e3, 1), "max_rel_err": float(f"{err:.2e}")}
+        tiled = [K.gemv_tile_repack(m.packed, m.sz, 128) for m in mats]
+        K.gemv_w4a16_tiled(tiled[0], x, y, N, Kd)
+        err = (y.float() - ref).abs().max().item() / ref.abs().max().item()
+        assert err <= 5e-3, (name, "tiled", err)
+
+        def run_tiled():
+            for tw in tiled:
+                K.gemv_w4a16_tiled(tw, x, y, N, Kd)
+        us = graph_time_us(run_tiled, copies)
+        row["tensor-core, tile layout"] = {"us": round(us, 2), "gbps": round(nbytes / us / 1e3, 1),
+                                           "max_rel_err": float(f"{err:.2e}")}
+        del tiled
         rows[name] = row
         del mats
     return rows

@@ -43,6 +43,8 @@ class DecodeConfig:
     part_size: int = 0           # attention split size; 0 -> policy table, else a size that fills the SMs
     attn_version: int = 0        # accepted for compatibility; the library has one attention kernel
     gemv_stage: tuple = None     # (stage, R, warps, pf) forced everywhere; None -> the library's shape-based choice
+    tile_weights: bool = True    # keep a second copy of every matrix in the tile layout of the tensor-core GEMV
+                                 # (b200_gemv_w4a16_tile_repack) and multiply from it; costs the weights' size again
     autotune_path: str = str(ROOT / "configs" / "autotune.json")
     attn_policy_path: str = str(ROOT / "configs" / "attn_policy.json")
     shuffle_pages: bool = True
@@ -81,6 +83,7 @@ class Linear:
         self.packed, self.sz = ql.packed.to(cfg.device), ql.sz.to(cfg.device)
         self.w_ref = ql.w_ref
         self.nbytes = ql.nbytes()
+        self.tiled = None            # tile-layout copy, made by Model when DecodeConfig.tile_weights is set
 
 
 def _rope_theta(c):
@@ -143,6 +146,10 @@ class Model:
         self.norm_f = g("model.norm.weight").contiguous()
         lm = sd["lm_head.weight"] if "lm_head.weight" in sd else sd["model.embed_tokens.weight"]
         self.lm_head = Linear(shard("lm_head", lm.to(dev).half()), cfg, "lm_head", pre=pre("lm_head", "lm_head"))
+
+        if cfg.tile_weights and cfg.gemv_stage is None:
+            for lin in [lw[n] for lw in self.layers for n in ("qkv", "o", "gu", "down")] + [self.lm_head]:
+                lin.tiled = self.K.gemv_tile_repack(lin.packed, lin.sz, cfg.group)
 
         # paged KV cache [L, 2, pages, n_kv, P, D]; one block table shared by all layers (one sequence)
         self.n_pages = (cfg.max_ctx + cfg.page - 1) // cfg.page + 1
@@ -302,6 +309,9 @@ class Model:
             w16 = self.w_fp16[: lin.N * lin.K].view(lin.N, lin.K)
             self.K.dequant_w4a16(lin.packed, lin.sz, w16, self.cfg.group)
             torch.mv(w16, x, out=y)
+            return
+        if lin.tiled is not None:
+            self.K.gemv_w4a16_tiled(lin.tiled, x, y, lin.N, lin.K)
             return
         s, r, w, pf = self.gemv_cfg(lin)
         self.K.gemv_w4a16(s, r, w, pf, lin.packed, lin.sz, x, y, self.cfg.group)

@@ -21,8 +21,10 @@ dev = "cuda"
 
 GEMV_TOL, ATTN_TOL, FUSED_TOL = 5e-3, 2e-3, 2e-3
 
-# (stage, R, warps, pf): the plain kernel, every explicit configuration, and the library's own choice
-GEMV_CFGS = [(0, 1, 4, 0), (1, 1, 4, 0)] + [(2, r, w, 0) for r in (1, 2, 4, 8) for w in (1, 4, 8)] + [(2, 0, 0, 0)]
+# (stage, R, warps, pf): the plain kernel, every explicit rows-per-warp configuration, the segmented kernel (R = 16)
+# and the library's own choice (R = 0: the tensor-core kernel where K and the group size allow, else the segmented one)
+GEMV_CFGS = ([(0, 1, 4, 0), (1, 1, 4, 0)] + [(2, r, w, 0) for r in (1, 2, 4, 8) for w in (1, 4, 8)]
+             + [(2, 16, 0, 0), (2, 0, 0, 0)])
 
 
 @pytest.fixture(scope="module")
@@ -103,10 +105,30 @@ def test_gemv_real_shapes(K, name):
     for G in groups:
         ql = PQ.QuantLinear(w, G)
         ref = R.gemv_ref(ql.w_ref.cpu(), x.cpu())
-        cfgs = GEMV_CFGS if (G == 128 and N <= 12000) else [(0, 1, 4, 0), (2, 4, 4, 0), (2, 8, 2, 0), (2, 0, 0, 0)]
+        cfgs = GEMV_CFGS if (G == 128 and N <= 12000) else [(0, 1, 4, 0), (2, 4, 4, 0), (2, 8, 2, 0), (2, 16, 0, 0),
+                                                             (2, 0, 0, 0)]
         for cfg in cfgs:
             e = rel_err(gemv(K, cfg, ql.packed, ql.sz, x, N, G), ref)
             assert e <= GEMV_TOL, (name, G, cfg, e)
+
+
+@pytest.mark.parametrize("name", ["qkv", "down", "lm_head", "o70_tp8", "down70_tp2", "ragged"])
+def test_gemv_tile_layout(K, name):
+    """The tensor-core GEMV from the repacked copy: same numbers as from the quantizer's tensors, bit for bit (same
+    arithmetic in the same order, only the addresses differ), and within tolerance of the oracle."""
+    N, Kd = SHAPES[name]
+    torch.manual_seed(1)
+    w = (torch.randn(N, Kd) * 0.02).half().to(dev)
+    x = torch.randn(Kd, device=dev).half()
+    for G in (128, 256) if Kd % 256 == 0 else (128,):
+        ql = PQ.QuantLinear(w, G)
+        tiled = K.gemv_tile_repack(ql.packed, ql.sz, G)
+        assert tiled is not None and tiled.numel() == ((N + 15) // 16) * (Kd // 128) * 1088
+        y = torch.full((N,), float("nan"), dtype=torch.half, device=dev)
+        K.gemv_w4a16_tiled(tiled, x, y, N, Kd)
+        assert torch.equal(y, gemv(K, (2, 0, 0, 0), ql.packed, ql.sz, x, N, G)), (name, G)
+        assert rel_err(y, R.gemv_ref(ql.w_ref.cpu(), x.cpu())) <= GEMV_TOL
+    assert K.gemv_tile_repack(ql.packed, ql.sz, 64) is None      # groups below 128 have no tile layout
 
 
 def test_gemv_golden(K, golden):
