@@ -86,10 +86,14 @@ int b200_rope_append(void* qkv, const float* cos_t, const float* sin_t, const in
  * (scale, zero)), tiles and column blocks back to back. Every warp load is then one contiguous 512-byte read; on
  * matrices with long rows this is worth 1.5x over the row-major tensors (DRAM locality). b200_gemv_w4a16_tiled_bytes
  * gives the size of the copy (0 if K % 128 != 0), b200_gemv_w4a16_tile_repack fills it once from the quantizer's
- * tensors (group size a multiple of 128), b200_gemv_w4a16_tiled computes y = W x from it (x 8-byte aligned). */
-size_t b200_gemv_w4a16_tiled_bytes(int N, int K);
-int b200_gemv_w4a16_tile_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, void* stream);
-int b200_gemv_w4a16_tiled(const void* Wt, const void* x, void* y, int N, int K, void* stream);
+ * tensors (group size a multiple of 128), b200_gemv_w4a16_tiled computes y = W x from it (x 8-byte aligned).
+ * gate_up != 0 (repack) / swiglu != 0 (GEMV): the matrix is [gate; up] with N = 2 I rows; the copy pairs gate row i
+ * with up row i inside a tile, and the GEMV - called with N = I - stores half(silu(gate_i)) * up_i, the result of
+ * b200_gemv_w4a16 followed by b200_swiglu, in one launch. */
+size_t b200_gemv_w4a16_tiled_bytes(int N, int K, int gate_up);
+int b200_gemv_w4a16_tile_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up,
+                                void* stream);
+int b200_gemv_w4a16_tiled(const void* Wt, const void* x, void* y, int N, int K, int swiglu, void* stream);
 
 /* Like b200_bw_read, but through the path the persistent step kernel uses: each of `blocks` CTAs streams its share
  * of the buffer into a shared-memory ring of `stages` x `stage_bytes` with 1-D bulk async copies. stage_bytes a

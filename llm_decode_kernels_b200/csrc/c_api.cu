@@ -11,10 +11,11 @@
 namespace b200 {
 cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, const void* SZ, const void* x, void* y,
                                 int N, int K, int log2G, cudaStream_t st);
-size_t gemv_tiled_bytes(int N, int K);
-cudaError_t gemv_tile_repack_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G,
+size_t gemv_tiled_bytes(int N, int K, int gate_up);
+cudaError_t gemv_tile_repack_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up,
                                       cudaStream_t st);
-cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, int N, int K, cudaStream_t st);
+cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, int N, int K, int swiglu,
+                                      cudaStream_t st);
 cudaError_t dequant_w4a16_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G,
                                    cudaStream_t st);
 cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int H, float eps,
@@ -93,24 +94,25 @@ int b200_gemv_w4a16(int stage, int R, int warps, int pf, const void* Wp, const v
   return finish(b200::gemv_w4a16_dispatch(stage, R, warps, Wp, SZ, x, y, N, K, log2G, S(stream)));
 }
 
-size_t b200_gemv_w4a16_tiled_bytes(int N, int K) {
-  if (N <= 0 || K <= 0 || K % 128) return 0;
-  return b200::gemv_tiled_bytes(N, K);
+size_t b200_gemv_w4a16_tiled_bytes(int N, int K, int gate_up) {
+  if (N <= 0 || K <= 0 || K % 128 || (gate_up && N % 2)) return 0;
+  return b200::gemv_tiled_bytes(N, K, gate_up);
 }
 
-int b200_gemv_w4a16_tile_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, void* stream) {
+int b200_gemv_w4a16_tile_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up,
+                                void* stream) {
   REQUIRE(Wp && SZ && out && N > 0 && K > 0, B200_ERR_ARG);
-  REQUIRE(K % 128 == 0 && log2G >= 7 && log2G < 31 && K % (1 << log2G) == 0, B200_ERR_SHAPE);
+  REQUIRE(K % 128 == 0 && log2G >= 7 && log2G < 31 && K % (1 << log2G) == 0 && !(gate_up && N % 2), B200_ERR_SHAPE);
   REQUIRE(aligned16(Wp) && aligned16(out), B200_ERR_ALIGN);
-  return finish(b200::gemv_tile_repack_dispatch(Wp, SZ, out, N, K, log2G, S(stream)));
+  return finish(b200::gemv_tile_repack_dispatch(Wp, SZ, out, N, K, log2G, gate_up, S(stream)));
 }
 
-int b200_gemv_w4a16_tiled(const void* Wt, const void* x, void* y, int N, int K, void* stream) {
+int b200_gemv_w4a16_tiled(const void* Wt, const void* x, void* y, int N, int K, int swiglu, void* stream) {
   REQUIRE(Wt && x && y && N > 0 && K > 0, B200_ERR_ARG);
   REQUIRE(K % 128 == 0, B200_ERR_SHAPE);
   REQUIRE(K <= 65536, B200_ERR_LIMIT);
   REQUIRE(aligned16(Wt) && (reinterpret_cast<uintptr_t>(x) & 7u) == 0, B200_ERR_ALIGN);
-  return finish(b200::gemv_w4a16_tiled_dispatch(Wt, x, y, N, K, S(stream)));
+  return finish(b200::gemv_w4a16_tiled_dispatch(Wt, x, y, N, K, swiglu, S(stream)));
 }
 
 int b200_bw_read(const void* p, size_t bytes, void* sink, int blocks, int threads, int unroll, void* stream) {

@@ -366,7 +366,12 @@ struct MmaBatchRegs { uint4 wa[kMmaBatch], wb[kMmaBatch]; half2 sa[kMmaBatch], s
 // contiguous 512-byte read and a warp streams through memory in address order.
 constexpr int kTileUnitBytes = 1088;
 
-template <bool TILED>
+//
+// SWIGLU = true (tile layout only): the matrix is [gate; up] and the repack has put gate row i and up row i into the
+// same tile (slots g and g + 8), so the lane that ends up with gate_i also holds up_i and the epilogue stores
+// half(silu(gate_i)) * up_i - the rounding of swiglu_kernel - instead of the two sums: one launch and 3/4 of the
+// output traffic less per layer. N is then the number of OUTPUTS (the matrix has 2 N rows).
+template <bool TILED, bool SWIGLU>
 __global__ void __launch_bounds__(kMmaGemvThreads, 2)
 gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ, const uint2* __restrict__ X,
                       half* __restrict__ y, int N, int K, int log2G, int ksplit, int rounds) {
@@ -380,7 +385,7 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   pdl_launch_dependents();
 
-  const int ntiles = (N + 15) >> 4, tiles_per_round = kMmaGemvWarps / ksplit;
+  const int ntiles = SWIGLU ? (N + 7) >> 3 : (N + 15) >> 4, tiles_per_round = kMmaGemvWarps / ksplit;
   const int kpart = warp % ksplit, tslot = warp / ksplit;
   const int ub = (int)(((long long)nunit * kpart) / ksplit), ue = (int)(((long long)nunit * (kpart + 1)) / ksplit);
   const int ng = K >> log2G, rowU4 = K >> 5;   // (scale, zero) entries and 16-byte pieces per row
@@ -512,29 +517,47 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
         cur = nxt;
       }
     }
+    // SWIGLU: slot g = gate row, slot g + 8 = its up row, 8 outputs per tile
+    auto gated = [](float ga, float up) {
+      const half hg = __float2half(ga), hu = __float2half(up);
+      const float gf = __half2float(hg);
+      return __hmul(__float2half(gf / (1.f + expf(-gf))), hu);
+    };
     if (ksplit == 1) {
       if (t == 0 && tile < ntiles) {
-        const int ra = 16 * tile + g, rb = ra + 8;
-        if (ra < N) y[ra] = __float2half(ya);
-        if (rb < N) y[rb] = __float2half(yb);
+        if (SWIGLU) {
+          if (8 * tile + g < N) y[8 * tile + g] = gated(ya, yb);
+        } else {
+          const int ra = 16 * tile + g, rb = ra + 8;
+          if (ra < N) y[ra] = __float2half(ya);
+          if (rb < N) y[rb] = __float2half(yb);
+        }
       }
     } else {
       if (t == 0) { part[warp * 16 + g] = ya; part[warp * 16 + g + 8] = yb; }
       __syncthreads();
       if (tid < tiles_per_round * 16) {
         const int ts = tid >> 4, row = tid & 15, tl = tile - tslot + ts;   // tile - tslot: first tile of the round
-        float v = 0.f;
-        for (int k = 0; k < ksplit; ++k) v += part[(ts * ksplit + k) * 16 + row];
-        if (tl < ntiles && 16 * tl + row < N) y[16 * tl + row] = __float2half(v);
+        float v = 0.f, v8 = 0.f;
+        for (int k = 0; k < ksplit; ++k) {
+          v += part[(ts * ksplit + k) * 16 + row];
+          if (SWIGLU) v8 += part[(ts * ksplit + k) * 16 + (row | 8)];
+        }
+        if (SWIGLU) {
+          if (row < 8 && tl < ntiles && 8 * tl + row < N) y[8 * tl + row] = gated(v, v8);
+        } else if (tl < ntiles && 16 * tl + row < N) {
+          y[16 * tl + row] = __float2half(v);
+        }
       }
       __syncthreads();
     }
   }
 }
 
-static cudaError_t launch_mma(bool tiled, const void* Wp, const void* SZ, const void* x, void* y, int N, int K,
+// mode 0: row-major tensors; 1: tile layout; 2: tile layout of a [gate; up] matrix with the SwiGLU epilogue (N outputs)
+static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const void* x, void* y, int N, int K,
                               int log2G, cudaStream_t st) {
-  const int ntiles = (N + 15) / 16, nunit = K / 128;
+  const int ntiles = mode == 2 ? (N + 7) / 8 : (N + 15) / 16, nunit = K / 128;
   // ksplit warps share a row tile: the smallest split that gives the chip enough warps (measured: with enough tiles
   // a warp per tile, no barrier, is as fast as any split; short of tiles, splitting K wins), as long as a warp keeps
   // at least two units. Blocks: at most two per SM (register limit); with more tile groups than blocks every block
@@ -549,53 +572,70 @@ static cudaError_t launch_mma(bool tiled, const void* Wp, const void* SZ, const 
   const size_t smem = (size_t)K * 2 + (size_t)nunit * 4 + kMmaGemvWarps * 16 * 4 + 64;
   static size_t configured = 48 * 1024;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<false, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem);
     if (e != cudaSuccess) return e;
     configured = smem;
   }
-  if (tiled)
-    return launch_pdl(gemv_w4a16_mma_kernel<true>, dim3(blocks), dim3(kMmaGemvThreads), smem, st, (const uint4*)Wp,
-                      (const half2*)SZ, (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds);
-  return launch_pdl(gemv_w4a16_mma_kernel<false>, dim3(blocks), dim3(kMmaGemvThreads), smem, st, (const uint4*)Wp,
-                    (const half2*)SZ, (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds);
+  auto kern = mode == 2 ? gemv_w4a16_mma_kernel<true, true>
+                        : (mode == 1 ? gemv_w4a16_mma_kernel<true, false> : gemv_w4a16_mma_kernel<false, false>);
+  return launch_pdl(kern, dim3(blocks), dim3(kMmaGemvThreads), smem, st, (const uint4*)Wp, (const half2*)SZ,
+                    (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds);
 }
 
 // ---- tile layout -------------------------------------------------------------------------------------------------------
 // One thread per 16-byte piece of the output: 68 pieces per (tile, unit), see gemv_w4a16_mma_kernel. Rows past N are
 // stored as zero weights with scale 0, so they add nothing.
 __global__ void gemv_tile_repack_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ,
-                                        uint4* __restrict__ out, int N, int K, int log2G) {
+                                        uint4* __restrict__ out, int N, int K, int log2G, int pair) {
+  // pair = 0: slot r of tile T is row 16 T + r. pair = I > 0 ([gate; up] of I rows each): slot r < 8 is gate row
+  // 8 T + r, slot r >= 8 is up row I + 8 T + (r - 8).
   const int nunit = K >> 7, u = blockIdx.x, tile = blockIdx.y, idx = threadIdx.x;
   if (idx >= kTileUnitBytes / 16) return;
+  auto row_of = [&](int slot) {
+    if (!pair) return 16 * tile + slot < N ? 16 * tile + slot : -1;
+    const int i = 8 * tile + (slot & 7);
+    return i < pair ? i + (slot >= 8 ? pair : 0) : -1;
+  };
   uint4 v = make_uint4(0u, 0u, 0u, 0u);
   if (idx < 64) {
-    const int lane = idx & 31, g = lane >> 2, t = lane & 3, row = 16 * tile + g + 8 * (idx >> 5);
-    if (row < N) v = Wp[(size_t)row * (K >> 5) + 4 * u + t];
+    const int lane = idx & 31, g = lane >> 2, t = lane & 3, row = row_of(g + 8 * (idx >> 5));
+    if (row >= 0) v = Wp[(size_t)row * (K >> 5) + 4 * u + t];
   } else {
     uint32_t e[4] = {0u, 0u, 0u, 0u};
     for (int k = 0; k < 4; ++k) {
-      const int row = 16 * tile + 4 * (idx - 64) + k;
-      if (row < N) e[k] = as_u32(SZ[(size_t)row * (K >> log2G) + ((u << 7) >> log2G)]);
+      const int row = row_of(4 * (idx - 64) + k);
+      if (row >= 0) e[k] = as_u32(SZ[(size_t)row * (K >> log2G) + ((u << 7) >> log2G)]);
     }
     v = make_uint4(e[0], e[1], e[2], e[3]);
   }
   out[((size_t)tile * nunit + u) * (kTileUnitBytes / 16) + idx] = v;
 }
 
-size_t gemv_tiled_bytes(int N, int K) { return (size_t)((N + 15) / 16) * (K / 128) * kTileUnitBytes; }
+// gate_up != 0: N = 2 I rows [gate; up], paired layout (I / 8 tiles, rounded up)
+size_t gemv_tiled_bytes(int N, int K, int gate_up) {
+  const int tiles = gate_up ? (N / 2 + 7) / 8 : (N + 15) / 16;
+  return (size_t)tiles * (K / 128) * kTileUnitBytes;
+}
 
-cudaError_t gemv_tile_repack_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G,
+cudaError_t gemv_tile_repack_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up,
                                       cudaStream_t st) {
-  gemv_tile_repack_kernel<<<dim3(K / 128, (N + 15) / 16), 96, 0, st>>>((const uint4*)Wp, (const half2*)SZ, (uint4*)out,
-                                                                        N, K, log2G);
+  const int tiles = gate_up ? (N / 2 + 7) / 8 : (N + 15) / 16;
+  gemv_tile_repack_kernel<<<dim3(K / 128, tiles), 96, 0, st>>>((const uint4*)Wp, (const half2*)SZ, (uint4*)out, N, K,
+                                                               log2G, gate_up ? N / 2 : 0);
   return cudaPeekAtLastError();
 }
 
-cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, int N, int K, cudaStream_t st) {
-  return launch_mma(true, Wt, nullptr, x, y, N, K, 7, st);
+// swiglu != 0: Wt is the paired layout of a [gate; up] matrix and y receives N = I values silu(gate) * up
+cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, int N, int K, int swiglu,
+                                      cudaStream_t st) {
+  return launch_mma(swiglu ? 2 : 1, Wt, nullptr, x, y, N, K, 7, st);
 }
 
 template <int R, int UNR>
@@ -626,7 +666,7 @@ cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, con
   if (!(R == 1 || R == 2 || R == 4 || R == 8) || warps < 1 || warps > 8) {
     const bool x_ok = (reinterpret_cast<uintptr_t>(x) & 7u) == 0;
     // the library's own choice: the tensor-core kernel where the shape allows (R == 16 asks for the segmented one)
-    if (R != 16 && x_ok && K % 128 == 0 && log2G >= 7) return launch_mma(false, Wp, SZ, x, y, N, K, log2G, st);
+    if (R != 16 && x_ok && K % 128 == 0 && log2G >= 7) return launch_mma(0, Wp, SZ, x, y, N, K, log2G, st);
     if ((reinterpret_cast<uintptr_t>(y) & 3u) == 0 && x_ok)
       return launch_seg(Wp, SZ, x, y, N, K, log2G, st);   // the segmented kernel
     R = 2;   // y not 4-byte aligned (the segmented kernel stores row pairs): row-per-warp kernel

@@ -26,8 +26,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libb200decode.so"
 SIGNATURES = {
     "b200_gemv_w4a16": [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_void_p],
-    "b200_gemv_w4a16_tile_repack": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "b200_gemv_w4a16_tiled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "b200_gemv_w4a16_tile_repack": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "b200_gemv_w4a16_tiled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_bw_read": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_bw_read_bulk": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_paged_attention": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -98,7 +98,7 @@ def load_library(build_if_missing=True):
     lib.b200_decode_step_repack.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_void_p]
     lib.b200_decode_step_repack.restype = c_int
-    lib.b200_gemv_w4a16_tiled_bytes.argtypes = [c_int, c_int]
+    lib.b200_gemv_w4a16_tiled_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemv_w4a16_tiled_bytes.restype = c_size_t
     lib.b200_decode_step_xchg_bytes.argtypes = [c_int] * 7
     lib.b200_decode_step_xchg_bytes.restype = c_size_t
@@ -164,26 +164,28 @@ class Ops:
                                              sz.data_ptr(), x.data_ptr(), y.data_ptr(), N, K,
                                              _ilog2_exact(int(group), "group"), _stream()), "gemv_w4a16")
 
-    def gemv_tile_repack(self, packed, sz, group):
+    def gemv_tile_repack(self, packed, sz, group, gate_up=False):
         """Copy of a quantized matrix in the tile layout of the tensor-core GEMV (uint8 tensor), or None when the
-        shape rules it out (K % 128 != 0 or a group size that is not a multiple of 128)."""
+        shape rules it out (K % 128 != 0 or a group size that is not a multiple of 128). gate_up: the matrix is
+        [gate; up]; gate row i and up row i share a tile, for gemv_w4a16_tiled(..., swiglu=True)."""
         _cuda(packed, "packed", torch.int32), _cuda(sz, "sz", torch.float16)
         N, K = packed.shape[0], packed.shape[1] * 8
-        nbytes = int(self.lib.b200_gemv_w4a16_tiled_bytes(N, K))
+        nbytes = int(self.lib.b200_gemv_w4a16_tiled_bytes(N, K, int(gate_up)))
         if nbytes == 0 or group % 128:
             return None
         out = torch.empty(nbytes, dtype=torch.uint8, device=packed.device)
         self._check(self.lib.b200_gemv_w4a16_tile_repack(packed.data_ptr(), sz.data_ptr(), out.data_ptr(), N, K,
-                                                         _ilog2_exact(int(group), "group"), _stream()),
+                                                         _ilog2_exact(int(group), "group"), int(gate_up), _stream()),
                     "gemv_tile_repack")
         return out
 
-    def gemv_w4a16_tiled(self, tiled, x, y, N, K):
+    def gemv_w4a16_tiled(self, tiled, x, y, N, K, swiglu=False):
+        """y[N] = W x from the tile-layout copy. swiglu: the copy is a paired [gate; up] and y[N] = silu(gate) * up."""
         _cuda(tiled, "tiled", torch.uint8), _cuda(x, "x", torch.float16), _cuda(y, "y", torch.float16)
         if x.numel() != K or y.numel() != N:
             raise RuntimeError("gemv_w4a16_tiled: x must hold K and y N values")
         self._check(self.lib.b200_gemv_w4a16_tiled(tiled.data_ptr(), x.data_ptr(), y.data_ptr(), int(N), int(K),
-                                                   _stream()), "gemv_w4a16_tiled")
+                                                   int(swiglu), _stream()), "gemv_w4a16_tiled")
 
     def bw_read(self, buf, sink, blocks, threads, unroll):
         _cuda(buf, "buf"), _cuda(sink, "sink"), _aligned16(buf, "buf")

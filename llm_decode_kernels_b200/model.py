@@ -84,6 +84,7 @@ class Linear:
         self.w_ref = ql.w_ref
         self.nbytes = ql.nbytes()
         self.tiled = None            # tile-layout copy, made by Model when DecodeConfig.tile_weights is set
+        self.paired = False          # the copy pairs gate row i with up row i (GEMV with SwiGLU epilogue)
 
 
 def _rope_theta(c):
@@ -148,8 +149,14 @@ class Model:
         self.lm_head = Linear(shard("lm_head", lm.to(dev).half()), cfg, "lm_head", pre=pre("lm_head", "lm_head"))
 
         if cfg.tile_weights and cfg.gemv_stage is None:
-            for lin in [lw[n] for lw in self.layers for n in ("qkv", "o", "gu", "down")] + [self.lm_head]:
-                lin.tiled = self.K.gemv_tile_repack(lin.packed, lin.sz, cfg.group)
+            # gate|up is stored with gate row i next to up row i, so its GEMV can finish with SwiGLU (one launch less
+            # per layer) - unless that fusion is switched off for an ablation run
+            pair = cfg.fused and "swiglu" not in cfg.ablate
+            for lw in self.layers:
+                for n in ("qkv", "o", "gu", "down"):
+                    lw[n].tiled = self.K.gemv_tile_repack(lw[n].packed, lw[n].sz, cfg.group, gate_up=pair and n == "gu")
+                    lw[n].paired = pair and n == "gu" and lw[n].tiled is not None
+            self.lm_head.tiled = self.K.gemv_tile_repack(self.lm_head.packed, self.lm_head.sz, cfg.group)
 
         # paged KV cache [L, 2, pages, n_kv, P, D]; one block table shared by all layers (one sequence)
         self.n_pages = (cfg.max_ctx + cfg.page - 1) // cfg.page + 1
@@ -393,8 +400,11 @@ class Model:
             self.attention(li)
             self.linear(lw["o"], self.attn.view(-1), self.o)
             self.add_norm(self.o, lw["ln2"], 0)
-            self.linear(lw["gu"], self.normed, self.gu)
-            self.swiglu()
+            if lw["gu"].paired:   # act = SwiGLU(Wgate x, Wup x) in one launch
+                self.K.gemv_w4a16_tiled(lw["gu"].tiled, self.normed, self.act, self.I, lw["gu"].K, swiglu=True)
+            else:
+                self.linear(lw["gu"], self.normed, self.gu)
+                self.swiglu()
             self.linear(lw["down"], self.act, self.down)
             delta = self.down
         self.add_norm(delta, self.norm_f, 1)

@@ -131,6 +131,27 @@ def test_gemv_tile_layout(K, name):
     assert K.gemv_tile_repack(ql.packed, ql.sz, 64) is None      # groups below 128 have no tile layout
 
 
+@pytest.mark.parametrize("I,Kd", [(5632, 2048), (1003, 1024), (3584, 8192)])
+def test_gemv_swiglu_epilogue(K, I, Kd):
+    """[gate; up] in the paired tile layout: one launch gives exactly what the GEMV followed by the SwiGLU kernel
+    gives (same sums, same rounding points), and matches the oracle's gemv + swiglu."""
+    torch.manual_seed(2)
+    w = (torch.randn(2 * I, Kd) * 0.02).half().to(dev)
+    x = torch.randn(Kd, device=dev).half()
+    ql = PQ.QuantLinear(w, 128)
+    paired = K.gemv_tile_repack(ql.packed, ql.sz, 128, gate_up=True)
+    assert paired.numel() == ((I + 7) // 8) * (Kd // 128) * 1088
+    act = torch.full((I,), float("nan"), dtype=torch.half, device=dev)
+    K.gemv_w4a16_tiled(paired, x, act, I, Kd, swiglu=True)
+    gu = gemv(K, (2, 0, 0, 0), ql.packed, ql.sz, x, 2 * I, 128)
+    if I % 8 == 0:
+        two = torch.empty(I, dtype=torch.half, device=dev)
+        K.swiglu(gu, two)
+        assert torch.equal(act, two)
+    ref = R.swiglu_ref(R.gemv_ref(ql.w_ref.cpu(), x.cpu()))
+    assert rel_err(act, ref) <= GEMV_TOL
+
+
 def test_gemv_golden(K, golden):
     g = golden("ops")
     y = gemv(K, (2, 0, 0, 0), torch.from_numpy(g["gemv_packed"]).to(dev), torch.from_numpy(g["gemv_sz"]).to(dev),
