@@ -1,8 +1,8 @@
 """Headline benchmark: batch-1 W4A16 greedy decode, tokens per second.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--step-kernel auto|persistent|multi]
 
-Workload `tinyllama` (default): TinyLlama-1.1B-shape decoder (22 layers, hidden 2048, intermediate 5632, 32 query /
+Workload: TinyLlama-1.1B-shape decoder (22 layers, hidden 2048, intermediate 5632, 32 query /
 4 KV heads, head_dim 64, vocab 32000), random init N(0, 0.02), every linear and the LM head W4A16 RTN g128; a
 128-token prompt of uniform random ids is teacher-forced through the decode step, then 256 tokens are decoded
 greedily with the whole step replayed as one CUDA graph. Synthetic weights and ids stand in for the TinyLlama
@@ -16,6 +16,9 @@ One benchmark "step" = one pass of that workload. What is timed:
           read back to the host as it is produced. Every decode step counts as a token: 384 per pass.
 With --gpus N > 1 every rank decodes its own sequence on its own copy of the model (no collective on the data
 path: weak scaling); the time is the max over ranks and `value` the sum of all ranks' tokens over it.
+
+The other configurations (single kernels, context sweep and ablations, the tensor-parallel 70B shape) have their own
+drivers: llm_decode_kernels_b200/kernel_bench.py and llm_decode_kernels_b200/e2e_bench.py.
 
 `--impl reference` times the CPU restatement of the reference's own CPU path (its Model with backend="ref") on
 this host's cores, on a bounded sample of the same workload.
