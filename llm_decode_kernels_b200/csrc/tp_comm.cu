@@ -79,7 +79,7 @@ DEVI bool exchange_flags(const CommPeers& P, int rank, int W) {
     int i = 0;
     while ((int32_t)(ld_acquire_sys(mine) - step) < 0) {
       if (++i > kCommSpinLimit) { failed = 1; break; }
-      __nanosleep(500);
+      if (i > 256) __nanosleep(500);   // peers normally answer within microseconds: poll hard first, then back off
     }
     if (failed) atomicExch(reinterpret_cast<uint32_t*>(base + kCommErrorOff), COMM_ERR_PEER_WAIT);
   }
@@ -109,11 +109,21 @@ tp_allreduce_add_rmsnorm_kernel(const CommPeers P, int rank, int W, size_t off, 
       float acc[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-      for (int r = 0; r < W; ++r) {
-        float f[8];
-        unpack8(ld_peer16(P.p[r] + off + 16 * (size_t)i), f);
+      // all peers' pieces are requested before the first is used: one NVLink round trip instead of W
+      for (int r0 = 0; r0 < W; r0 += 8) {
+        uint4 v[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] += f[k];
+        for (int j = 0; j < 8; ++j)
+          if (r0 + j < W) v[j] = ld_peer16(P.p[r0 + j] + off + 16 * (size_t)i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (r0 + j < W) {
+            float f[8];
+            unpack8(v[j], f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += f[k];
+          }
+        }
       }
       uint4 v = reinterpret_cast<const uint4*>(x)[i];
       v.x = as_u32(__hadd2(as_h2(v.x), __floats2half2_rn(acc[0], acc[1])));
