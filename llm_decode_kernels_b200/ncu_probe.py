@@ -1,6 +1,6 @@
 """Small, self-ending workloads to run under `ncu` (the reference has bench/ncu_probe.py for the same purpose).
 
-    python -m llm_decode_kernels_b200.ncu_probe gemv  [--n 32000 --k 2048 --copies 8 --iters 3]
+    python -m llm_decode_kernels_b200.ncu_probe gemv  [--n 32000 --k 2048 --copies 8 --iters 3 --tiled | --rows 16]
     python -m llm_decode_kernels_b200.ncu_probe attn  [--ctx 8192 --batch 8 --part 256 --version 0 --iters 3]
     python -m llm_decode_kernels_b200.ncu_probe step  [--layers 4 --tokens 4]
 
@@ -24,9 +24,13 @@ def probe_gemv(a):
             for _ in range(a.copies)]
     x = torch.randn(a.k, device="cuda").half()
     y = torch.empty(a.n, dtype=torch.half, device="cuda")
+    tiled = [K.gemv_tile_repack(m.packed, m.sz, 128) for m in mats] if a.tiled else None
     for _ in range(a.iters):
-        for m in mats:
-            K.gemv_w4a16(2, 0, 0, 0, m.packed, m.sz, x, y, 128)
+        for i, m in enumerate(mats):
+            if a.tiled:
+                K.gemv_w4a16_tiled(tiled[i], x, y, a.n, a.k)
+            else:
+                K.gemv_w4a16(2, a.rows, 0, 0, m.packed, m.sz, x, y, 128)
     torch.cuda.synchronize()
     print("gemv bytes per launch:", mats[0].nbytes() + 2 * a.k + 2 * a.n)
 
@@ -70,6 +74,8 @@ if __name__ == "__main__":
     ap.add_argument("--n", type=int, default=32000)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--copies", type=int, default=8)
+    ap.add_argument("--tiled", action="store_true", help="gemv: tensor-core kernel from the tile-layout copy")
+    ap.add_argument("--rows", type=int, default=0, help="gemv: R of b200_gemv_w4a16 (0 library's choice, 16 segmented)")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=8)
