@@ -150,8 +150,8 @@ class Model:
 
         if cfg.tile_weights and cfg.gemv_stage is None:
             # gate|up is stored with gate row i next to up row i, so its GEMV can finish with SwiGLU (one launch less
-            # per layer) - unless that fusion is switched off for an ablation run
-            pair = cfg.fused and "swiglu" not in cfg.ablate
+            # per layer) - unless that fusion, or the fused dequantization, is switched off for an ablation run
+            pair = cfg.fused and not ({"swiglu", "dequant"} & set(cfg.ablate))
             for lw in self.layers:
                 for n in ("qkv", "o", "gu", "down"):
                     lw[n].tiled = self.K.gemv_tile_repack(lw[n].packed, lw[n].sz, cfg.group, gate_up=pair and n == "gu")
