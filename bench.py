@@ -276,7 +276,12 @@ def run_b200_arm(args, rank, world, local_rank):
     if m.persistent:
         launches_per_token = 1                       # decode_step_kernel
     else:
-        launches_per_token = 1 + m.L * (2 + 4 + 1 + 1 + (1 if m.max_splits > 1 else 0) + 1) + 3
+        # embed; per layer: (2 norms unless fused into the GEMVs) + 4 GEMVs + rope/append + attention (+ combine)
+        # (+ SwiGLU unless it is the gate|up GEMV's epilogue); final norm (unless fused), LM head, argmax
+        norms = 0 if m.norm_in_gemv else 1
+        swiglu = 0 if m.layers[0]["gu"].paired else 1
+        launches_per_token = (1 + m.L * (2 * norms + 4 + 1 + 1 + (1 if m.max_splits > 1 else 0) + swiglu)
+                              + norms + 2)
     assert m.step_error() == 0, "a bounded wait inside the step kernel gave up: the numbers would be meaningless"
 
     ctx_mid = PROMPT_LEN + NEW_TOKENS // 2

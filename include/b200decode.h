@@ -95,6 +95,13 @@ int b200_gemv_w4a16_tile_repack(const void* Wp, const void* SZ, void* out, int N
                                 void* stream);
 int b200_gemv_w4a16_tiled(const void* Wt, const void* x, void* y, int N, int K, int swiglu, void* stream);
 
+/* b200_add_rmsnorm followed by b200_gemv_w4a16_tiled, in one launch: r = x_in + delta (fp16 add; delta may be NULL),
+ * x = norm_w * half(float(r) * rsqrt(mean(r^2) + eps)), y = W x (or SwiGLU of it). Every thread block normalises
+ * its own copy of the K activations while its first weights are in flight; r goes to x_out, which must not be
+ * x_in. All vectors fp16 [K], 8-byte aligned. */
+int b200_gemv_w4a16_tiled_norm(const void* Wt, const void* x_in, const void* delta, const void* norm_w, float eps,
+                               void* x_out, void* y, int N, int K, int swiglu, void* stream);
+
 /* Like b200_bw_read, but through the path the persistent step kernel uses: each of `blocks` CTAs streams its share
  * of the buffer into a shared-memory ring of `stages` x `stage_bytes` with 1-D bulk async copies. stage_bytes a
  * multiple of 128, stage_bytes * stages <= 226 KB. *sink becomes 0xdead000x if a bounded wait inside gives up. */

@@ -16,6 +16,8 @@ cudaError_t gemv_tile_repack_dispatch(const void* Wp, const void* SZ, void* out,
                                       cudaStream_t st);
 cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, int N, int K, int swiglu,
                                       cudaStream_t st);
+cudaError_t gemv_w4a16_tiled_norm_dispatch(const void* Wt, const void* x_in, const void* delta, const void* norm_w,
+                                           float eps, void* x_out, void* y, int N, int K, int swiglu, cudaStream_t st);
 cudaError_t dequant_w4a16_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G,
                                    cudaStream_t st);
 cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int H, float eps,
@@ -113,6 +115,17 @@ int b200_gemv_w4a16_tiled(const void* Wt, const void* x, void* y, int N, int K, 
   REQUIRE(K <= 65536, B200_ERR_LIMIT);
   REQUIRE(aligned16(Wt) && (reinterpret_cast<uintptr_t>(x) & 7u) == 0, B200_ERR_ALIGN);
   return finish(b200::gemv_w4a16_tiled_dispatch(Wt, x, y, N, K, swiglu, S(stream)));
+}
+
+int b200_gemv_w4a16_tiled_norm(const void* Wt, const void* x_in, const void* delta, const void* norm_w, float eps,
+                               void* x_out, void* y, int N, int K, int swiglu, void* stream) {
+  REQUIRE(Wt && x_in && norm_w && x_out && y && N > 0 && K > 0 && x_out != x_in, B200_ERR_ARG);
+  REQUIRE(K % 128 == 0, B200_ERR_SHAPE);
+  REQUIRE(K <= 65536, B200_ERR_LIMIT);
+  auto aligned8 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; };
+  REQUIRE(aligned16(Wt) && aligned8(x_in) && aligned8(norm_w) && aligned8(x_out) && (!delta || aligned8(delta)),
+          B200_ERR_ALIGN);
+  return finish(b200::gemv_w4a16_tiled_norm_dispatch(Wt, x_in, delta, norm_w, eps, x_out, y, N, K, swiglu, S(stream)));
 }
 
 int b200_bw_read(const void* p, size_t bytes, void* sink, int blocks, int threads, int unroll, void* stream) {

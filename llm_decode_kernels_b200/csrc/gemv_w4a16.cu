@@ -371,17 +371,30 @@ constexpr int kTileUnitBytes = 1088;
 // same tile (slots g and g + 8), so the lane that ends up with gate_i also holds up_i and the epilogue stores
 // half(silu(gate_i)) * up_i - the rounding of swiglu_kernel - instead of the two sums: one launch and 3/4 of the
 // output traffic less per layer. N is then the number of OUTPUTS (the matrix has 2 N rows).
-template <bool TILED, bool SWIGLU>
+//
+// NORM = true: the residual add and RMSNorm that precede the GEMV in a decoder layer run inside the staging of x,
+// in every block (K values: nothing next to the weights the block streams), with the rounding of add_rmsnorm_kernel:
+//     r = X +_fp16 delta (delta may be null);  x = nw *_fp16 half(float(r) * rsqrt(mean(r^2) + eps));  y = W x
+// Block 0 also stores r to x_out, the residual stream for the rest of the layer. x_out must not alias X: the other
+// blocks are still reading X. One launch less in front of the qkv, the gate|up and the LM-head GEMV.
+struct NormArgs {
+  const uint2* delta;   // [K] fp16 or null
+  const uint2* nw;      // [K] fp16 norm weight
+  uint2* x_out;         // [K] fp16
+  float eps;
+};
+
+template <bool TILED, bool SWIGLU, bool NORM>
 __global__ void __launch_bounds__(kMmaGemvThreads, 2)
 gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ, const uint2* __restrict__ X,
-                      half* __restrict__ y, int N, int K, int log2G, int ksplit, int rounds) {
+                      half* __restrict__ y, int N, int K, int log2G, int ksplit, int rounds, const NormArgs na) {
   extern __shared__ __align__(16) uint8_t mma_smem[];
   const int nunit = K >> 7;                                                // 128-weight units per row
   uint4* xin = reinterpret_cast<uint4*>(mma_smem);                         // [K/8] staged x, 16 bytes = one word's 8
   uint4* zeros = xin + (K >> 3);                                           // 64 zero bytes: B of the lanes with g != 0
   float* part = reinterpret_cast<float*>(zeros + 4);                       // [kMmaGemvWarps][16]
   float* xsg = part + kMmaGemvWarps * 16;                                  // [nunit] sum of x over each unit
-  __shared__ float red[kMmaGemvWarps];
+  __shared__ float red[kMmaGemvWarps], red2[kMmaGemvWarps];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   pdl_launch_dependents();
 
@@ -445,13 +458,47 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
   }
   pdl_wait();
 
-  // ---- stage x: max|x| -> power-of-two scale -> (x0 x1) 2^s, (x2 x3) 2^(s-4), ... and the unit sums
+  // ---- stage x: (residual add + RMSNorm ->) max|x| -> power-of-two scale -> (x0 x1) 2^s, (x2 x3) 2^(s-4), ... and
+  // the unit sums
   float mx = 0.f;
-  for (int i = tid; i < (K >> 2); i += kMmaGemvThreads) {
-    const uint2 v = __ldg(X + i);
-    reinterpret_cast<uint2*>(xin)[i] = v;
-    const float2 a = __half22float2(__habs2(as_h2(v.x))), b = __half22float2(__habs2(as_h2(v.y)));
-    mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)));
+  if (NORM) {
+    float ss = 0.f;
+    for (int i = tid; i < (K >> 2); i += kMmaGemvThreads) {
+      uint2 v = __ldg(X + i);
+      if (na.delta) {
+        const uint2 d = __ldg(na.delta + i);
+        v.x = as_u32(__hadd2(as_h2(v.x), as_h2(d.x)));
+        v.y = as_u32(__hadd2(as_h2(v.y), as_h2(d.y)));
+      }
+      reinterpret_cast<uint2*>(xin)[i] = v;
+      if (blockIdx.x == 0) na.x_out[i] = v;
+      const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
+      ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(b.x, b.x, fmaf(b.y, b.y, ss))));
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red2[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMmaGemvWarps; ++k) tot += red2[k];
+    const float rinv = rsqrtf(tot / (float)K + na.eps);
+    for (int i = tid; i < (K >> 2); i += kMmaGemvThreads) {   // this thread's own granules again
+      const uint2 r = reinterpret_cast<uint2*>(xin)[i], w = __ldg(na.nw + i);
+      const float2 a = __half22float2(as_h2(r.x)), b = __half22float2(as_h2(r.y));
+      uint2 v;
+      v.x = as_u32(__hmul2(as_h2(w.x), __floats2half2_rn(a.x * rinv, a.y * rinv)));
+      v.y = as_u32(__hmul2(as_h2(w.y), __floats2half2_rn(b.x * rinv, b.y * rinv)));
+      reinterpret_cast<uint2*>(xin)[i] = v;
+      const float2 c = __half22float2(__habs2(as_h2(v.x))), d = __half22float2(__habs2(as_h2(v.y)));
+      mx = fmaxf(mx, fmaxf(fmaxf(c.x, c.y), fmaxf(d.x, d.y)));
+    }
+  } else {
+    for (int i = tid; i < (K >> 2); i += kMmaGemvThreads) {
+      const uint2 v = __ldg(X + i);
+      reinterpret_cast<uint2*>(xin)[i] = v;
+      const float2 a = __half22float2(__habs2(as_h2(v.x))), b = __half22float2(__habs2(as_h2(v.y)));
+      mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)));
+    }
   }
   mx = warp_max(mx);
   if (lane == 0) red[warp] = mx;
@@ -556,7 +603,7 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
 
 // mode 0: row-major tensors; 1: tile layout; 2: tile layout of a [gate; up] matrix with the SwiGLU epilogue (N outputs)
 static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const void* x, void* y, int N, int K,
-                              int log2G, cudaStream_t st) {
+                              int log2G, cudaStream_t st, const NormArgs* norm = nullptr) {
   const int ntiles = mode == 2 ? (N + 7) / 8 : (N + 15) / 16, nunit = K / 128;
   // ksplit warps share a row tile: the smallest split that gives the chip enough warps (measured: with enough tiles
   // a warp per tile, no barrier, is as fast as any split; short of tiles, splitting K wins), as long as a warp keeps
@@ -572,30 +619,31 @@ static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const vo
   const size_t smem = (size_t)K * 2 + (size_t)nunit * 4 + kMmaGemvWarps * 16 * 4 + 64;
   static size_t configured = 48 * 1024;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<false, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)smem);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemv_w4a16_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)smem);
+    cudaError_t e = cudaSuccess;
+    void (*all[])(const uint4*, const half2*, const uint2*, half*, int, int, int, int, int, const NormArgs) = {
+        gemv_w4a16_mma_kernel<false, false, false>, gemv_w4a16_mma_kernel<true, false, false>,
+        gemv_w4a16_mma_kernel<true, true, false>, gemv_w4a16_mma_kernel<true, false, true>,
+        gemv_w4a16_mma_kernel<true, true, true>};
+    for (auto k : all)
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     configured = smem;
   }
-  auto kern = mode == 2 ? gemv_w4a16_mma_kernel<true, true>
-                        : (mode == 1 ? gemv_w4a16_mma_kernel<true, false> : gemv_w4a16_mma_kernel<false, false>);
+  const NormArgs na = norm ? *norm : NormArgs{nullptr, nullptr, nullptr, 0.f};
+  auto kern = mode == 0 ? gemv_w4a16_mma_kernel<false, false, false>
+              : norm    ? (mode == 2 ? gemv_w4a16_mma_kernel<true, true, true> : gemv_w4a16_mma_kernel<true, false, true>)
+                        : (mode == 2 ? gemv_w4a16_mma_kernel<true, true, false> : gemv_w4a16_mma_kernel<true, false, false>);
   // Dependent launch pays for the small matrices of a step (TinyLlama shape, all GEMVs: 764 instead of 846 us per
   // token) and costs on large ones (70B shape, 16 layers: 2616 instead of 2227 us per token when the GEMVs use it):
   // matrices beyond 24 MB are launched the ordinary way.
   const size_t weight_bytes = (size_t)(mode == 2 ? 2 * N : N) * K / 2;
   if (weight_bytes > ((size_t)24 << 20)) {
     kern<<<blocks, kMmaGemvThreads, smem, st>>>((const uint4*)Wp, (const half2*)SZ, (const uint2*)x, (half*)y, N, K,
-                                                log2G, ksplit, rounds);
+                                                log2G, ksplit, rounds, na);
     return cudaPeekAtLastError();
   }
   return launch_pdl(kern, dim3(blocks), dim3(kMmaGemvThreads), smem, st, (const uint4*)Wp, (const half2*)SZ,
-                    (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds);
+                    (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds, na);
 }
 
 // ---- tile layout -------------------------------------------------------------------------------------------------------
@@ -645,6 +693,13 @@ cudaError_t gemv_tile_repack_dispatch(const void* Wp, const void* SZ, void* out,
 cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, int N, int K, int swiglu,
                                       cudaStream_t st) {
   return launch_mma(swiglu ? 2 : 1, Wt, nullptr, x, y, N, K, 7, st);
+}
+
+// residual add + RMSNorm + GEMV (+ SwiGLU) in one launch: see NormArgs
+cudaError_t gemv_w4a16_tiled_norm_dispatch(const void* Wt, const void* x_in, const void* delta, const void* norm_w,
+                                           float eps, void* x_out, void* y, int N, int K, int swiglu, cudaStream_t st) {
+  const NormArgs na = {(const uint2*)delta, (const uint2*)norm_w, (uint2*)x_out, eps};
+  return launch_mma(swiglu ? 2 : 1, Wt, nullptr, x_in, y, N, K, 7, st, &na);
 }
 
 template <int R, int UNR>

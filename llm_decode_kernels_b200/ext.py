@@ -28,6 +28,8 @@ SIGNATURES = {
                         c_void_p],
     "b200_gemv_w4a16_tile_repack": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "b200_gemv_w4a16_tiled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_gemv_w4a16_tiled_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                                   c_int, c_void_p],
     "b200_bw_read": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_bw_read_bulk": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_paged_attention": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -186,6 +188,22 @@ class Ops:
             raise RuntimeError("gemv_w4a16_tiled: x must hold K and y N values")
         self._check(self.lib.b200_gemv_w4a16_tiled(tiled.data_ptr(), x.data_ptr(), y.data_ptr(), int(N), int(K),
                                                    int(swiglu), _stream()), "gemv_w4a16_tiled")
+
+    def gemv_w4a16_tiled_norm(self, tiled, x_in, delta, norm_w, eps, x_out, y, N, K, swiglu=False):
+        """add_rmsnorm + gemv_w4a16_tiled in one launch: x_out = x_in + delta (delta may be None),
+        y = W (norm_w * rmsnorm(x_out)); x_out must be a different buffer from x_in."""
+        _cuda(tiled, "tiled", torch.uint8)
+        for t_, n_ in ((x_in, "x_in"), (norm_w, "norm_w"), (x_out, "x_out"), (y, "y")):
+            _cuda(t_, n_, torch.float16)
+        if x_in.numel() != K or x_out.numel() != K or norm_w.numel() != K or y.numel() != N:
+            raise RuntimeError("gemv_w4a16_tiled_norm: vectors must hold K values and y N")
+        d = 0
+        if delta is not None:
+            _cuda(delta, "delta", torch.float16)
+            d = delta.data_ptr()
+        self._check(self.lib.b200_gemv_w4a16_tiled_norm(tiled.data_ptr(), x_in.data_ptr(), d, norm_w.data_ptr(),
+                                                        float(eps), x_out.data_ptr(), y.data_ptr(), int(N), int(K),
+                                                        int(swiglu), _stream()), "gemv_w4a16_tiled_norm")
 
     def bw_read(self, buf, sink, blocks, threads, unroll):
         _cuda(buf, "buf"), _cuda(sink, "sink"), _aligned16(buf, "buf")

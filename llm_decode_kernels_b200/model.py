@@ -43,6 +43,8 @@ class DecodeConfig:
     part_size: int = 0           # attention split size; 0 -> policy table, else a size that fills the SMs
     attn_version: int = 0        # accepted for compatibility; the library has one attention kernel
     gemv_stage: tuple = None     # (stage, R, warps, pf) forced everywhere; None -> the library's shape-based choice
+    fuse_norm_gemv: bool = True  # residual add + RMSNorm inside the GEMV that consumes them (b200_gemv_w4a16_tiled_norm):
+                                 # two launches less per layer; needs tile_weights, one GPU, no ablation switch
     tile_weights: bool = True    # keep a second copy of every matrix in the tile layout of the tensor-core GEMV
                                  # (b200_gemv_w4a16_tile_repack) and multiply from it; costs the weights' size again
     autotune_path: str = str(ROOT / "configs" / "autotune.json")
@@ -174,6 +176,7 @@ class Model:
         self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
         self.history = torch.zeros(cfg.max_ctx + 2, dtype=torch.long, device=dev)  # token chosen at each position
         self.x = torch.empty(self.H, **h16)
+        self.x_alt = torch.empty(self.H, **h16)    # second residual buffer of the norm-fused GEMVs (they ping-pong)
         self.normed = torch.empty(self.H, **h16)
         self.qkv = torch.empty((self.n_q + 2 * self.n_kv) * self.D, **h16)
         self.attn = torch.empty(self.n_q, self.D, **h16)
@@ -206,6 +209,9 @@ class Model:
                 self.comm = TP.PeerComm(self.K, self.tp_rank, self.tp, [2 * self.H, 2 * self.H, 2 * self.V], dev,
                                         cfg.tp_group)
                 self.o, self.down, self.logits_local = self.comm.slot(0), self.comm.slot(1), self.comm.slot(2)
+        heads = [lw[n] for lw in self.layers for n in ("qkv", "gu")] + [self.lm_head]
+        self.norm_in_gemv = (cfg.fuse_norm_gemv and self.tp == 1 and not self.off
+                             and all(lin.tiled is not None for lin in heads))
         self.set_attention_partition(cfg.max_ctx)
 
     # ------------------------------------------------------------------ attention partitioning
@@ -393,6 +399,9 @@ class Model:
             self.K.decode_step(self._step_desc)
             return
         self.K.embed_row(self.emb, self.tok, self.x)
+        if self.norm_in_gemv:
+            self.step_norm_in_gemv()
+            return
         delta = None
         for li, lw in enumerate(self.layers):
             self.add_norm(delta, lw["ln1"], 1)
@@ -414,6 +423,31 @@ class Model:
         elif self.tp > 1:
             torch.distributed.all_gather_into_tensor(self.logits, self.logits_local, group=self.cfg.tp_group)
         self.K.argmax(self.logits, self.tok, self.pos, self.history)
+
+    def step_norm_in_gemv(self):
+        """The layers with residual add + RMSNorm done inside the qkv / gate|up / LM-head GEMVs: 7 launches per layer
+        (qkv, rope+append, attention, combine, o, gate|up+SwiGLU, down) instead of 10. The residual stream alternates
+        between self.x and self.x_alt: a fused GEMV reads one and writes the other."""
+        K, cur, nxt, delta = self.K, self.x, self.x_alt, None
+        for li, lw in enumerate(self.layers):
+            K.gemv_w4a16_tiled_norm(lw["qkv"].tiled, cur, delta, lw["ln1"], self.eps, nxt, self.qkv, lw["qkv"].N,
+                                    lw["qkv"].K)
+            cur, nxt = nxt, cur
+            self.attention(li)
+            self.linear(lw["o"], self.attn.view(-1), self.o)
+            gu = lw["gu"]
+            if gu.paired:
+                K.gemv_w4a16_tiled_norm(gu.tiled, cur, self.o, lw["ln2"], self.eps, nxt, self.act, self.I, gu.K,
+                                        swiglu=True)
+            else:
+                K.gemv_w4a16_tiled_norm(gu.tiled, cur, self.o, lw["ln2"], self.eps, nxt, self.gu, gu.N, gu.K)
+                self.swiglu()
+            cur, nxt = nxt, cur
+            self.linear(lw["down"], self.act, self.down)
+            delta = self.down
+        K.gemv_w4a16_tiled_norm(self.lm_head.tiled, cur, delta, self.norm_f, self.eps, nxt, self.logits_local,
+                                self.lm_head.N, self.lm_head.K)
+        K.argmax(self.logits, self.tok, self.pos, self.history)
 
     def capture(self):
         """Capture step() into a CUDA graph (two warm-up steps on a side stream first, as torch requires).

@@ -152,6 +152,32 @@ def test_gemv_swiglu_epilogue(K, I, Kd):
     assert rel_err(act, ref) <= GEMV_TOL
 
 
+@pytest.mark.parametrize("N,Kd,swiglu", [(2560, 2048, False), (5632, 2048, True), (3000, 1024, False)])
+def test_gemv_with_norm_prologue(K, N, Kd, swiglu):
+    """Residual add + RMSNorm inside the GEMV's staging: the residual it stores is bit-identical to add_rmsnorm's,
+    the product within tolerance of oracle add_rmsnorm -> gemv (-> swiglu); with and without a delta."""
+    torch.manual_seed(3)
+    rows = 2 * N if swiglu else N
+    ql = PQ.QuantLinear((torch.randn(rows, Kd) * 0.02).half().to(dev), 128)
+    tiled = K.gemv_tile_repack(ql.packed, ql.sz, 128, gate_up=swiglu)
+    nw = (1 + 0.1 * torch.randn(Kd, device=dev)).half()
+    for with_delta in (True, False):
+        x_in = torch.randn(Kd, device=dev).half()
+        delta = (0.5 * torch.randn(Kd, device=dev)).half() if with_delta else None
+        x_out = torch.full((Kd,), float("nan"), dtype=torch.half, device=dev)
+        y = torch.full((N,), float("nan"), dtype=torch.half, device=dev)
+        K.gemv_w4a16_tiled_norm(tiled, x_in, delta, nw, 1e-5, x_out, y, N, Kd, swiglu=swiglu)
+        xr, normed = x_in.clone(), torch.empty(Kd, dtype=torch.half, device=dev)
+        K.add_rmsnorm(xr, delta, nw, normed, 1e-5)
+        assert torch.equal(x_out, xr)
+        rx, rn = R.add_rmsnorm_ref(x_in.cpu(), None if delta is None else delta.cpu(), nw.cpu(), 1e-5)
+        ref = R.gemv_ref(ql.w_ref.cpu(), rn)
+        ref = R.swiglu_ref(ref) if swiglu else ref
+        assert rel_err(y, ref) <= GEMV_TOL, (N, Kd, swiglu, with_delta)
+    with pytest.raises(RuntimeError):
+        K.gemv_w4a16_tiled_norm(tiled, x_in, None, nw, 1e-5, x_in, y, N, Kd, swiglu=swiglu)   # x_out must differ
+
+
 def test_gemv_golden(K, golden):
     g = golden("ops")
     y = gemv(K, (2, 0, 0, 0), torch.from_numpy(g["gemv_packed"]).to(dev), torch.from_numpy(g["gemv_sz"]).to(dev),
