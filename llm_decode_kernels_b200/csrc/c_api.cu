@@ -36,6 +36,10 @@ cudaError_t bw_read_bulk_dispatch(const void* p, size_t bytes, void* sink, int b
 cudaError_t repack_stream_dispatch(const void* W, const void* SZ, void* out, int N, int K, int log2G, int gu, int ncta,
                                    int stage_w, cudaStream_t st);
 cudaError_t paged_attention_status(int* code);
+cudaError_t rope_paged_attention_dispatch(void* qkv, const float* cos_t, const float* sin_t, void* kc, void* vc,
+                                          const int* bt, const int* pos, int n_q, int n_kv, int D, int log2P, int PS,
+                                          int max_splits, float* o_part, float* m_part, float* l_part, void* out,
+                                          cudaStream_t st);
 cudaError_t tp_allreduce_add_rmsnorm_dispatch(const void* const* peers, int rank, int W, size_t off, void* x,
                                               const void* w, void* out, int H, float eps, cudaStream_t st);
 cudaError_t tp_allgather_dispatch(const void* const* peers, int rank, int W, size_t off, void* dst, int n,
@@ -180,6 +184,22 @@ int b200_paged_attention(int version, const void* q, const void* kc, const void*
   REQUIRE(version >= 1 && version <= 3, B200_ERR_ARG);
   return attention_entry(version, q, kc, vc, bt, 1 << 30, pos, 1, n_q, n_kv, 64, log2P, PS, max_splits, o_part, m_part,
                          l_part, out, stream);
+}
+
+int b200_rope_paged_attention(void* qkv, const float* cos_t, const float* sin_t, void* kc, void* vc, const int* bt,
+                              const int* pos, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
+                              float* o_part, float* m_part, float* l_part, void* out, void* stream) {
+  REQUIRE(qkv && cos_t && sin_t && kc && vc && bt && pos && out, B200_ERR_ARG);
+  REQUIRE(n_q > 0 && n_kv > 0 && PS > 0 && max_splits > 0 && max_splits <= 65535 && log2P >= 0 && log2P < 16,
+          B200_ERR_ARG);
+  REQUIRE(max_splits == 1 || (o_part && m_part && l_part), B200_ERR_ARG);
+  REQUIRE(D == 64 || D == 128, B200_ERR_SHAPE);
+  REQUIRE(n_q % n_kv == 0, B200_ERR_SHAPE);
+  const int hpg = n_q / n_kv;
+  REQUIRE(hpg == 1 || hpg == 2 || hpg == 4 || hpg == 8, B200_ERR_SHAPE);
+  REQUIRE(aligned16(kc) && aligned16(vc) && aligned16(qkv), B200_ERR_ALIGN);
+  return finish(b200::rope_paged_attention_dispatch(qkv, cos_t, sin_t, kc, vc, bt, pos, n_q, n_kv, D, log2P, PS,
+                                                    max_splits, o_part, m_part, l_part, out, S(stream)));
 }
 
 int b200_paged_attention_status(int* code) {

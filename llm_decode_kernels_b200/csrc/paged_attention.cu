@@ -500,12 +500,24 @@ paged_attn_staged_kernel(const half* __restrict__ q, const half* __restrict__ kc
 constexpr int kMmaThreads = kAttnThreads + 32;   // four arithmetic warps + one warp that only issues copies
 constexpr int kBtCache = 1024;                   // block-table entries of a split kept in shared memory
 
-template <int D, int HPG, int KH>
+//
+// ROPE = true folds the step's RoPE + KV-append (rope_append_kernel) into this kernel: `q` is then the raw qkv vector
+// of the step ([B, (n_q + 2 n_kv) D], nothing rotated yet). Every block rotates its own query heads while it builds the
+// Q fragments. The new token (position pos = ctx - 1) is not in the cache yet: the warp that owns its 16-token block
+// in the last split rotates k, patches the K and V rows of the stage in shared memory once the page copy has landed,
+// and stores the same rows to the cache in global memory for the steps to come. One launch less per layer.
+struct RopeArgs {
+  const float *cos_t, *sin_t;   // [max_pos, D/2]
+  half *kc_w, *vc_w;            // the caches, writable
+};
+
+template <int D, int HPG, int KH, bool ROPE>
 __global__ void __launch_bounds__(kMmaThreads, D == 64 ? 4 : 2)
 paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, const half* __restrict__ vc,
                       const int* __restrict__ bt, int bt_stride, const int* __restrict__ pos_ptr, int n_kv, int log2P,
                       int PS, float scale, float* __restrict__ o_part, float* __restrict__ m_part,
-                      float* __restrict__ l_part, half* __restrict__ out, int max_splits) {
+                      float* __restrict__ l_part, half* __restrict__ out, int max_splits, const RopeArgs ra) {
+  static_assert(!ROPE || KH == 1, "the fused RoPE path is written for one kv head per block");
   pdl_launch_dependents();
   pdl_wait();
   constexpr int TS = kStageTokens / KH;    // tokens per ring stage (of each of the KH heads)
@@ -593,7 +605,26 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
   auto row_of = [&](int j) { return (size_t)(((((j >> log2P) * KH) + kh) << log2P) + (j & pmask)) * D; };
   // Q as A fragments: row g = head g of the group (zero beyond HPG), k-step kk holds dims t D/4 + 4 kk + {0,1 | 2,3}
   uint32_t qa[KS][2];
-  {
+  const int pos = ctx - 1;
+  if (ROPE) {
+    // rotate-half RoPE on the fly: dim d pairs with d +- D/2; fp32 math, fp16 result (the rounding of rope_append)
+    const int qkv_stride = (n_q + 2 * n_kv) * D;
+    const half* qh = q + (size_t)b * qkv_stride + ((size_t)(kvh0 + kh) * HPG + (g < HPG ? g : 0)) * D;
+    const float* cs = ra.cos_t + (size_t)pos * (D / 2);
+    const float* sn = ra.sin_t + (size_t)pos * (D / 2);
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+      half r[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int d = t * (D / 4) + 4 * kk + e, dl = d < D / 2 ? d : d - D / 2;
+        const float a = __half2float(qh[dl]), bb = __half2float(qh[dl + D / 2]), c = cs[dl], sv = sn[dl];
+        r[e] = __float2half(d < D / 2 ? a * c - bb * sv : bb * c + a * sv);
+      }
+      qa[kk][0] = g < HPG ? as_u32(__halves2half2(r[0], r[1])) : 0u;
+      qa[kk][1] = g < HPG ? as_u32(__halves2half2(r[2], r[3])) : 0u;
+    }
+  } else {
     const half* qh = q + ((size_t)b * n_q + (kvh0 + kh) * HPG + (g < HPG ? g : 0)) * D + t * (D / 4);
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
@@ -602,6 +633,11 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
       qa[kk][1] = g < HPG ? v.y : 0u;
     }
   }
+  // ROPE: where the new token sits. Its block is the last live split (if the context is within the prepared cap),
+  // its tile i_new, its row j_new, and the warp that owns that row's 16-token block patches it.
+  const int rel_new = pos - t0;
+  const bool has_new = ROPE && split == nsplit - 1 && rel_new >= 0 && rel_new < t1 - t0;
+  const int i_new = has_new ? rel_new / TS : -1, j_new = has_new ? rel_new % TS : 0;
   const float sl2 = scale * 1.44269504088896340736f;   // scores are kept in units of log2(e)
   float m = -CUDART_INF_F, l = 0.f, acc[NB][4];
 #pragma unroll
@@ -617,6 +653,25 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
     const half* vt = kt + HALF_STAGE;
     const int nt = min(TS, t1 - t0 - i * TS);
     const int tok0 = tb * 16;
+    if (ROPE && ok && i == i_new && (j_new >> 4) == tb) {
+      // the new token: rotated k and raw v into the stage (the copy brought the slot's old bytes) and into the cache
+      const int qkv_stride = (n_q + 2 * n_kv) * D;
+      const half* kraw = q + (size_t)b * qkv_stride + ((size_t)n_q + kvh0 + kh) * D;
+      const half* vraw = kraw + (size_t)n_kv * D;
+      half* krow = const_cast<half*>(kt) + row_of(j_new);
+      half* vrow = const_cast<half*>(vt) + row_of(j_new);
+      const size_t grow = ((((size_t)__ldg(btb + (pos >> log2P)) * n_kv + kvh0 + kh) << log2P) + (pos & pmask)) * D;
+      for (int dl = lane; dl < D / 2; dl += 32) {
+        const float a = __half2float(kraw[dl]), bb = __half2float(kraw[dl + D / 2]);
+        const float c = ra.cos_t[(size_t)pos * (D / 2) + dl], sv = ra.sin_t[(size_t)pos * (D / 2) + dl];
+        const half k0 = __float2half(a * c - bb * sv), k1 = __float2half(bb * c + a * sv);
+        const half v0 = vraw[dl], v1 = vraw[dl + D / 2];
+        krow[dl] = k0; krow[dl + D / 2] = k1; vrow[dl] = v0; vrow[dl + D / 2] = v1;
+        ra.kc_w[grow + dl] = k0; ra.kc_w[grow + dl + D / 2] = k1;
+        ra.vc_w[grow + dl] = v0; ra.vc_w[grow + dl + D / 2] = v1;
+      }
+      __syncwarp();
+    }
     if (ok && tok0 < nt) {
       // ---- scores of 16 tokens: two n-blocks of 8
       float s[2][4];
@@ -792,11 +847,23 @@ struct AttnArgs {
 template <int D, int HPG, int KH>
 static cudaError_t launch_mma(const AttnArgs& a, int dev, cudaStream_t st) {
   static bool configured[64] = {};
-  const cudaError_t e = allow_ring(paged_attn_mma_kernel<D, HPG, KH>, attn_ring_bytes<D>(), &configured[dev]);
+  const cudaError_t e = allow_ring(paged_attn_mma_kernel<D, HPG, KH, false>, attn_ring_bytes<D>(), &configured[dev]);
   if (e != cudaSuccess) return e;
-  B200_LAUNCH(paged_attn_mma_kernel<D, HPG, KH>, dim3(a.n_kv / KH, a.max_splits, a.B), dim3(kMmaThreads),
+  B200_LAUNCH(paged_attn_mma_kernel<D, HPG, KH, false>, dim3(a.n_kv / KH, a.max_splits, a.B), dim3(kMmaThreads),
               attn_ring_bytes<D>(), st, a.q, a.kc, a.vc, a.bt, a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale,
-              a.o_part, a.m_part, a.l_part, a.out, a.max_splits);
+              a.o_part, a.m_part, a.l_part, a.out, a.max_splits, RopeArgs{nullptr, nullptr, nullptr, nullptr});
+  return cudaPeekAtLastError();
+}
+
+// the same kernel with RoPE + KV-append folded in: a.q is the raw qkv vector of the step
+template <int D, int HPG>
+static cudaError_t launch_mma_rope(const AttnArgs& a, const RopeArgs& r, int dev, cudaStream_t st) {
+  static bool configured[64] = {};
+  const cudaError_t e = allow_ring(paged_attn_mma_kernel<D, HPG, 1, true>, attn_ring_bytes<D>(), &configured[dev]);
+  if (e != cudaSuccess) return e;
+  B200_LAUNCH(paged_attn_mma_kernel<D, HPG, 1, true>, dim3(a.n_kv, a.max_splits, a.B), dim3(kMmaThreads),
+              attn_ring_bytes<D>(), st, a.q, a.kc, a.vc, a.bt, a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale,
+              a.o_part, a.m_part, a.l_part, a.out, a.max_splits, r);
   return cudaPeekAtLastError();
 }
 
@@ -860,6 +927,45 @@ cudaError_t paged_attention_dispatch(int version, const void* q, const void* kc,
   if (max_splits > 1) {
     B200_LAUNCH(paged_attn_combine_kernel, dim3(n_q, B), dim3(D), 0, st, o_part, m_part, l_part, pos, PS, max_splits,
                 D, (half*)out);
+    e = cudaPeekAtLastError();
+  }
+  return e;
+}
+
+cudaError_t rope_append_dispatch(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt,
+                                 int bt_stride, void* kc, void* vc, int B, int n_q, int n_kv, int D, int log2P,
+                                 cudaStream_t st);
+
+// RoPE + KV-append + attention (+ combine) for one sequence. Where the ring kernel does not apply (page or split
+// size), the two stand-alone kernels run one after the other: same result, one launch more.
+cudaError_t rope_paged_attention_dispatch(void* qkv, const float* cos_t, const float* sin_t, void* kc, void* vc,
+                                          const int* bt, const int* pos, int n_q, int n_kv, int D, int log2P, int PS,
+                                          int max_splits, float* o_part, float* m_part, float* l_part, void* out,
+                                          cudaStream_t st) {
+  const int hpg = n_q / n_kv;
+  const bool ring_ok = log2P >= 3 && log2P <= 6 && PS % (1 << log2P) == 0;
+  if (!ring_ok) {
+    const cudaError_t e = rope_append_dispatch(qkv, cos_t, sin_t, pos, bt, 1 << 30, kc, vc, 1, n_q, n_kv, D, log2P, st);
+    if (e != cudaSuccess) return e;
+    return paged_attention_dispatch(0, qkv, kc, vc, bt, 1 << 30, pos, 1, n_q, n_kv, D, log2P, PS, max_splits, o_part,
+                                    m_part, l_part, out, st);
+  }
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  const AttnArgs a = {(const half*)qkv, (const half*)kc, (const half*)vc, bt, 1 << 30, pos, n_kv, log2P, PS,
+                      1.0f / sqrtf((float)D), o_part, m_part, l_part, (half*)out, max_splits, 1};
+  const RopeArgs r = {cos_t, sin_t, (half*)kc, (half*)vc};
+  cudaError_t e = cudaErrorInvalidValue;
+#define B200_ROPE_CASE(DD, H) \
+  if (D == DD && hpg == H) e = launch_mma_rope<DD, H>(a, r, dev, st);
+  B200_ROPE_CASE(64, 1) B200_ROPE_CASE(64, 2) B200_ROPE_CASE(64, 4) B200_ROPE_CASE(64, 8)
+  B200_ROPE_CASE(128, 1) B200_ROPE_CASE(128, 2) B200_ROPE_CASE(128, 4) B200_ROPE_CASE(128, 8)
+#undef B200_ROPE_CASE
+  if (e != cudaSuccess) return e;
+  if (max_splits > 1) {
+    B200_LAUNCH(paged_attn_combine_kernel, dim3(n_q, 1), dim3(D), 0, st, o_part, m_part, l_part, pos, PS, max_splits, D,
+                (half*)out);
     e = cudaPeekAtLastError();
   }
   return e;

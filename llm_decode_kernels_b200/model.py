@@ -43,6 +43,7 @@ class DecodeConfig:
     part_size: int = 0           # attention split size; 0 -> policy table, else a size that fills the SMs
     attn_version: int = 0        # accepted for compatibility; the library has one attention kernel
     gemv_stage: tuple = None     # (stage, R, warps, pf) forced everywhere; None -> the library's shape-based choice
+    fuse_rope_attention: bool = True   # RoPE + KV-append inside the attention kernel (b200_rope_paged_attention)
     fuse_norm_gemv: bool = True  # residual add + RMSNorm inside the GEMV that consumes them (b200_gemv_w4a16_tiled_norm):
                                  # two launches less per layer; needs tile_weights, one GPU, no ablation switch
     tile_weights: bool = True    # keep a second copy of every matrix in the tile layout of the tensor-core GEMV
@@ -380,6 +381,9 @@ class Model:
                                            self.bt.view(1, -1), self.pos, self.part_size, self.o_part.unsqueeze(0),
                                            self.m_part.unsqueeze(0), self.l_part.unsqueeze(0),
                                            self.attn.view(1, self.n_q, self.D))
+        elif self.cfg.fuse_rope_attention:   # RoPE, cache append and attention in one partial-kernel launch
+            self.K.rope_paged_attention(self.qkv, self.cos, self.sin, self.pos, self.bt, kc, vc, self.n_q, self.n_kv,
+                                        self.part_size, self.o_part, self.m_part, self.l_part, self.attn)
         elif self.D == 64:
             self.K.rope_append(self.qkv, self.cos, self.sin, self.pos, self.bt, kc, vc, self.n_q, self.n_kv)
             self.K.paged_attention(self.qkv[: self.n_q * self.D], kc, vc, self.bt, self.pos, self.part_size,

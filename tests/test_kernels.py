@@ -286,6 +286,39 @@ def test_attention_page_sizes_and_poisoned_tail(K, page):
     assert K.paged_attention_status() == 0
 
 
+@pytest.mark.parametrize("D,n_q,n_kv,page", [(64, 32, 4, 16), (128, 8, 2, 16), (64, 8, 8, 32), (64, 16, 4, 4)])
+def test_rope_attention_in_one_launch(K, D, n_q, n_kv, page):
+    """b200_rope_paged_attention against b200_rope_append(_batched) followed by b200_paged_attention_batched: the
+    attention output and both caches bit for bit (page 4: the entry point falls back to the two kernels)."""
+    torch.manual_seed(D + page)
+    cos, sin = (t.to(dev) for t in R.rope_tables(3000, D))
+    for ctx, PS in ((1, 64), (17, 64), (64, 64), (65, 64), (300, 128), (1000, 256), (2049, 512)):
+        n_pages = (ctx + page - 1) // page + 2
+        kc = torch.randn(n_pages, n_kv, page, D, device=dev).half()
+        vc = torch.randn(n_pages, n_kv, page, D, device=dev).half()
+        bt = torch.randperm(n_pages, device=dev).int()
+        qkv = torch.randn((n_q + 2 * n_kv) * D, device=dev).half()
+        pos = torch.tensor([ctx - 1], dtype=torch.int32, device=dev)
+        S = (ctx + PS - 1) // PS + 1
+        bufs = lambda: (torch.full((n_q, S, D), float("nan"), device=dev), torch.full((n_q, S), float("nan"), device=dev),
+                        torch.full((n_q, S), float("nan"), device=dev), torch.empty(n_q, D, dtype=torch.half, device=dev))
+        # reference path: two kernels (rotates q in place, so on a copy)
+        q2, kc2, vc2 = qkv.clone(), kc.clone(), vc.clone()
+        K.rope_append_batched(q2.view(1, -1), cos, sin, pos, bt.view(1, -1), kc2, vc2, n_q, n_kv)
+        o2, m2, l2, out2 = bufs()
+        K.paged_attention_batched(q2[: n_q * D].view(1, n_q, D), kc2, vc2, bt.view(1, -1), pos, PS, o2.unsqueeze(0),
+                                  m2.unsqueeze(0), l2.unsqueeze(0), out2.view(1, n_q, D))
+        # one launch
+        q1, kc1, vc1 = qkv.clone(), kc.clone(), vc.clone()
+        o1, m1, l1, out1 = bufs()
+        K.rope_paged_attention(q1, cos, sin, pos, bt, kc1, vc1, n_q, n_kv, PS, o1, m1, l1, out1)
+        assert torch.equal(out1, out2), (D, n_q, n_kv, page, ctx, PS)
+        assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2), (ctx, PS)
+        if page >= 8:
+            assert torch.equal(q1, qkv)      # the fused kernel leaves qkv alone
+    assert K.paged_attention_status() == 0
+
+
 def test_attention_golden(K, golden):
     g = golden("ops")
     T = lambda k: torch.from_numpy(g[k]).to(dev)
