@@ -166,6 +166,26 @@ def test_ablation_switches_keep_the_numbers(off):
         Model(sd, c, DecodeConfig(max_ctx=96, ablate=("everything",)))
 
 
+def test_optional_fusions_do_not_change_the_tokens():
+    """fuse_rope_attention (off by default) and fuse_norm_gemv (on by default): same greedy stream either way, up to
+    the first position where the logits of the two runs are within the noise floor of each other."""
+    c = hf_cfg(512, 2, 8, 2, 1024, 1500)
+    sd = random_state(c, 31)
+    torch.manual_seed(2)
+    prompt = torch.randint(0, c.vocab_size, (12,)).tolist()
+    runs = {}
+    for name, kw in (("default", {}), ("rope fused", dict(fuse_rope_attention=True)),
+                     ("norm unfused", dict(fuse_norm_gemv=False))):
+        m = Model(sd, c, DecodeConfig(max_ctx=96, seed=2, step_kernel="multi", **kw))
+        assert m.norm_in_gemv == (name != "norm unfused")
+        m.prepare(96, use_graph=True, part_size=32)
+        m.reset(0)
+        runs[name] = m.teacher_force(prompt + list(range(30)), collect_logits=True).float().cpu()
+    scale = runs["default"].abs().max().item()
+    assert torch.equal(runs["rope fused"], runs["default"])          # same arithmetic, one launch less
+    assert (runs["norm unfused"] - runs["default"]).abs().max().item() <= KERNEL_TOL * scale
+
+
 def test_capture_in_mid_sequence_keeps_the_cache():
     c = hf_cfg(256, 2, 4, 1, 512, 500)
     m = Model(random_state(c, 3), c, DecodeConfig(max_ctx=128, seed=1))
