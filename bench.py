@@ -248,10 +248,15 @@ def run_b200_arm(args, rank, world, local_rank):
             for l in lins}
     gemv_bytes = sum(l.nbytes + 2 * l.K + 2 * l.N for l in lins)
 
-    def gemv_mix():
+    def gemv_mix():   # every GEMV of one token, the way Model.linear() issues it in the multi-kernel step
         for l in lins:
             x, y = bufs[(l.N, l.K)]
-            K.gemv_w4a16(2, 0, 0, 0, l.packed, l.sz, x, y, GROUP)
+            if l.tiled is None:
+                K.gemv_w4a16(2, 0, 0, 0, l.packed, l.sz, x, y, GROUP)
+            elif l.paired:
+                K.gemv_w4a16_tiled(l.tiled, x, y[: l.N // 2], l.N // 2, l.K, swiglu=True)
+            else:
+                K.gemv_w4a16_tiled(l.tiled, x, y, l.N, l.K)
 
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
@@ -289,7 +294,8 @@ def run_b200_arm(args, rank, world, local_rank):
     us_per_token = dev_ms * 1e3 / (args.steps * NEW_TOKENS)
     gemv_roofline = {"kernel": "gemv_w4a16_mma_kernel", "achieved": round(achieved, 1), "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "launches": len(lins), "bytes_per_launch_mix": gemv_bytes,
-                     "how": "the 89 GEMVs of one token replayed as one graph, CUDA events, 50 replays"}
+                     "how": "the 89 GEMVs of one token (tile-layout copies, gate|up with its SwiGLU epilogue) replayed as one "
+                            "graph, CUDA events, 50 replays"}
     if m.persistent:
         # the dominant kernel IS the step: algorithmic bytes of one token / the kernel's average duration in the timed
         # region (one launch per graph replay, so the event-timed replay is the launch)
