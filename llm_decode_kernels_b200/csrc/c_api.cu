@@ -197,7 +197,7 @@ int b200_rope_paged_attention(void* qkv, const float* cos_t, const float* sin_t,
   REQUIRE(n_q % n_kv == 0, B200_ERR_SHAPE);
   const int hpg = n_q / n_kv;
   REQUIRE(hpg == 1 || hpg == 2 || hpg == 4 || hpg == 8, B200_ERR_SHAPE);
-  REQUIRE(aligned16(kc) && aligned16(vc) && aligned16(qkv), B200_ERR_ALIGN);
+  REQUIRE(aligned16(kc) && aligned16(vc) && aligned16(qkv) && aligned16(cos_t) && aligned16(sin_t), B200_ERR_ALIGN);
   return finish(b200::rope_paged_attention_dispatch(qkv, cos_t, sin_t, kc, vc, bt, pos, n_q, n_kv, D, log2P, PS,
                                                     max_splits, o_part, m_part, l_part, out, S(stream)));
 }

@@ -607,19 +607,34 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
   uint32_t qa[KS][2];
   const int pos = ctx - 1;
   if (ROPE) {
-    // rotate-half RoPE on the fly: dim d pairs with d +- D/2; fp32 math, fp16 result (the rounding of rope_append)
+    // rotate-half RoPE on the fly: dim d pairs with d +- D/2; fp32 math, fp16 result (the rounding of rope_append).
+    // This lane's D/4 dims, their partners and the matching cos / sin entries arrive as 16-byte loads, all
+    // independent, so the prologue costs one memory round trip.
+    constexpr int D4 = D / 4;
     const int qkv_stride = (n_q + 2 * n_kv) * D;
     const half* qh = q + (size_t)b * qkv_stride + ((size_t)(kvh0 + kh) * HPG + (g < HPG ? g : 0)) * D;
-    const float* cs = ra.cos_t + (size_t)pos * (D / 2);
-    const float* sn = ra.sin_t + (size_t)pos * (D / 2);
+    const bool lower = t < 2;                       // this lane's dims lie in the first half of the head
+    const int dl0 = (t & 1) * D4;                   // their index among the D/2 rotation pairs
+    __align__(16) half own[D4], mate[D4];
+    __align__(16) float cs[D4], sn[D4];
+#pragma unroll
+    for (int v = 0; v < D4 / 8; ++v) {
+      reinterpret_cast<uint4*>(own)[v] = *reinterpret_cast<const uint4*>(qh + t * D4 + 8 * v);
+      reinterpret_cast<uint4*>(mate)[v] = *reinterpret_cast<const uint4*>(qh + t * D4 + (lower ? D / 2 : -(D / 2)) + 8 * v);
+    }
+#pragma unroll
+    for (int v = 0; v < D4 / 4; ++v) {
+      reinterpret_cast<float4*>(cs)[v] = *reinterpret_cast<const float4*>(ra.cos_t + (size_t)pos * (D / 2) + dl0 + 4 * v);
+      reinterpret_cast<float4*>(sn)[v] = *reinterpret_cast<const float4*>(ra.sin_t + (size_t)pos * (D / 2) + dl0 + 4 * v);
+    }
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
       half r[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int d = t * (D / 4) + 4 * kk + e, dl = d < D / 2 ? d : d - D / 2;
-        const float a = __half2float(qh[dl]), bb = __half2float(qh[dl + D / 2]), c = cs[dl], sv = sn[dl];
-        r[e] = __float2half(d < D / 2 ? a * c - bb * sv : bb * c + a * sv);
+        const int i = 4 * kk + e;
+        const float a = __half2float(lower ? own[i] : mate[i]), bb = __half2float(lower ? mate[i] : own[i]);
+        r[e] = __float2half(lower ? a * cs[i] - bb * sn[i] : bb * cs[i] + a * sn[i]);
       }
       qa[kk][0] = g < HPG ? as_u32(__halves2half2(r[0], r[1])) : 0u;
       qa[kk][1] = g < HPG ? as_u32(__halves2half2(r[2], r[3])) : 0u;

@@ -84,7 +84,8 @@ def run_ctx(a):
     max_ctx = 8192 + a.tokens + 16
 
     def build(**kw):
-        return Model(sd, c, DecodeConfig(group=128, quant=quant, qparams=qparams, max_ctx=max_ctx, seed=0, **kw))
+        return Model(sd, c, DecodeConfig(group=128, quant=quant, qparams=qparams, max_ctx=max_ctx, seed=0,
+                                         fuse_rope_attention=a.fuse_rope, **kw))
 
     m = build()
     m.kv.normal_()
@@ -175,6 +176,7 @@ def main():
     ap.add_argument("--gemv", default="tiled", choices=["tiled", "rowmajor", "segmented"],
                     help="tp: tensor-core GEMV from the tile layout (default) / from the row-major tensors / the "
                          "segmented CUDA-core GEMV")
+    ap.add_argument("--fuse-rope", action="store_true", help="ctx: RoPE + KV-append inside the attention kernel")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     if a.tokens is None:
