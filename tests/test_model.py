@@ -167,14 +167,14 @@ def test_ablation_switches_keep_the_numbers(off):
 
 
 def test_optional_fusions_do_not_change_the_tokens():
-    """fuse_rope_attention (off by default) and fuse_norm_gemv (on by default): same greedy stream either way, up to
-    the first position where the logits of the two runs are within the noise floor of each other."""
+    """fuse_rope_attention and fuse_norm_gemv (both on by default) switched off one at a time: the separate RoPE
+    kernel gives the same bits, the separate add+RMSNorm kernel the same logits within the kernel tolerance."""
     c = hf_cfg(512, 2, 8, 2, 1024, 1500)
     sd = random_state(c, 31)
     torch.manual_seed(2)
     prompt = torch.randint(0, c.vocab_size, (12,)).tolist()
     runs = {}
-    for name, kw in (("default", {}), ("rope fused", dict(fuse_rope_attention=True)),
+    for name, kw in (("default", {}), ("rope unfused", dict(fuse_rope_attention=False)),
                      ("norm unfused", dict(fuse_norm_gemv=False))):
         m = Model(sd, c, DecodeConfig(max_ctx=96, seed=2, step_kernel="multi", **kw))
         assert m.norm_in_gemv == (name != "norm unfused")
@@ -182,7 +182,7 @@ def test_optional_fusions_do_not_change_the_tokens():
         m.reset(0)
         runs[name] = m.teacher_force(prompt + list(range(30)), collect_logits=True).float().cpu()
     scale = runs["default"].abs().max().item()
-    assert torch.equal(runs["rope fused"], runs["default"])          # same arithmetic, one launch less
+    assert torch.equal(runs["rope unfused"], runs["default"])        # same arithmetic, one launch more
     assert (runs["norm unfused"] - runs["default"]).abs().max().item() <= KERNEL_TOL * scale
 
 
