@@ -501,6 +501,9 @@ def test_embed_and_argmax(K):
     lg = -torch.rand(77, device=dev).half() - 1                    # all negative
     K.argmax(lg, tok)
     assert int(tok) == R.argmax_ref(lg.cpu())
+    lg = torch.randn(4099, device=dev).half()[3:]                  # not 16-byte aligned: the scalar scan
+    K.argmax(lg, tok)
+    assert int(tok) == R.argmax_ref(lg.cpu())
 
 
 def test_bw_read_runs(K):
