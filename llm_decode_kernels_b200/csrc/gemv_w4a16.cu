@@ -4,7 +4,14 @@
 // kernels/bindings.cpp:27-38). Same data layout: packed int32 [N, K/8], (scale, zero) half2 [N, K/G],
 // x fp16 [K], y fp16 [N]; fp32 accumulation across 32-weight chunks.
 //
-// Work split: one warp owns R consecutive rows over the whole K, lane l owns the 16-byte chunks
+// Four kernels, in the order they were written; each later one exists because a measurement said so:
+//   gemv_w4a16_plain_kernel  (stage 0)   one thread per weight, the readable baseline
+//   gemv_w4a16_kernel<R,UNR> (R 1..8)    rows per warp, magic-number nibble decode, described next
+//   gemv_w4a16_seg_kernel    (R = 16)    segmented, x in registers, nibbles multiplied as fp16 subnormals
+//   gemv_w4a16_mma_kernel    (R = 0)     the default: masked nibbles as tensor-core operands, optional tile layout,
+//                                        SwiGLU epilogue and residual add + RMSNorm prologue
+//
+// Rows-per-warp kernel. Work split: one warp owns R consecutive rows over the whole K, lane l owns the 16-byte chunks
 // l, l+32, ... of each row (one chunk = 32 weights, always inside one group because G >= 32). The block
 // first stages x into shared memory, pre-scaled as dot_word() wants it, so the inner loop needs no
 // activation arithmetic and x is read from L2 once per block instead of once per row. All weight
@@ -131,7 +138,7 @@ __global__ void dequant_w4a16_kernel(const uint32_t* __restrict__ Wp, const half
   out[i] = o;
 }
 
-// ---- segmented GEMV: the library's default ------------------------------------------------------------------------------
+// ---- segmented GEMV (R = 16): the fastest CUDA-core kernel ---------------------------------------------------------------
 // Same arithmetic as the GEMV phases of the persistent step kernel (masked nibbles as fp16 subnormals, zero point
 // folded into one FMA per chunk; see common.cuh), laid out for one launch per matrix:
 //   * a CTA of 8 warps owns a tile of consecutive units (unit = two consecutive rows);

@@ -7,10 +7,11 @@
 // of tokens [i P, (i+1) P) of sequence b; context length of sequence b = pos[b] + 1, read on the device so one
 // captured graph serves every step. Split s of a sequence owns tokens [s PS, min(ctx, (s+1) PS)).
 //
-// Two partial kernels share the grid (n_kv, max_splits, B), 128 threads; a block handles ALL heads of one kv
-// group, so every K/V byte is fetched from HBM once.
+// Three partial kernels (the `version` of the entry points) share the grid (n_kv, max_splits, B); a block handles ALL
+// heads of one kv group, so every K/V byte is fetched from HBM once. Version 3, paged_attn_mma_kernel, is the default
+// and is described where it is defined; it builds on version 2:
 //
-// paged_attn_staged_kernel (the one that runs for pages of 8..64 tokens and splits that start on a page boundary):
+// paged_attn_staged_kernel (version 2; like version 3 for pages of 8..64 tokens and splits that start on a page boundary):
 // the split's K and V pages are pulled into a shared-memory ring by bulk async copies (cp.async.bulk + mbarrier
 // transaction counts), one copy per page, issued by the lanes of warp 0 several 64-token tiles ahead of the
 // arithmetic. A decode-attention block has little to compute and a lot to fetch; with register loads the bytes in
