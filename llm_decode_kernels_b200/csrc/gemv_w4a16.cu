@@ -641,10 +641,11 @@ static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const vo
               : norm    ? (mode == 2 ? gemv_w4a16_mma_kernel<true, true, true> : gemv_w4a16_mma_kernel<true, false, true>)
                         : (mode == 2 ? gemv_w4a16_mma_kernel<true, true, false> : gemv_w4a16_mma_kernel<true, false, false>);
   // Dependent launch pays for the small matrices of a step (TinyLlama shape, all GEMVs: 764 instead of 846 us per
-  // token) and costs on large ones (70B shape, 16 layers: 2616 instead of 2227 us per token when the GEMVs use it):
-  // matrices beyond 24 MB are launched the ordinary way.
+  // token) and costs on large ones. 70B shape cut to 16 layers (matrices of 33, 44, 125 and 250 MB), us per token
+  // with dependent launch up to 24 / 40 / 64 / 140 MB / always: 2158 / 2130 / 2129 / 2220 / 2556. Matrices beyond
+  // 64 MB are launched the ordinary way.
   const size_t weight_bytes = (size_t)(mode == 2 ? 2 * N : N) * K / 2;
-  if (weight_bytes > ((size_t)24 << 20)) {
+  if (weight_bytes > ((size_t)64 << 20)) {
     kern<<<blocks, kMmaGemvThreads, smem, st>>>((const uint4*)Wp, (const half2*)SZ, (const uint2*)x, (half*)y, N, K,
                                                 log2G, ksplit, rounds, na);
     return cudaPeekAtLastError();
