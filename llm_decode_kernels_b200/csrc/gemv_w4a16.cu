@@ -643,13 +643,12 @@ static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const vo
                         : (mode == 2 ? gemv_w4a16_mma_kernel<true, true, false> : gemv_w4a16_mma_kernel<true, false, false>);
   // Dependent launch pays for the small matrices of a step (TinyLlama shape, all GEMVs: 764 instead of 846 us per
   // token) and costs on large ones. 70B shape cut to 16 layers on one GPU (matrices of 33, 44, 125 and 250 MB), us per
-  // token with dependent launch up to 24 / 40 / 64 / 140 MB / always: 2158 / 2130 / 2129 / 2220 / 2556. The
-  // tensor-parallel runs of the full shape were slower with 64 than with 24 MB (TP4 6.75 against 5.97 ms, TP8 6.70
-  // against 5.54 ms per token, measured on different machines), so the cut-off is 24 MB; the environment variable
-  // B200_PDL_MAX_MB moves it for A/B runs.
+  // token with dependent launch up to 24 / 40 / 64 / 140 MB / always: 2158 / 2130 / 2129 / 2220 / 2556; the full
+  // shape on two GPUs, 24 against 64 MB on the same machine, twice: 7.83, 7.96 against 7.74, 7.73 ms per token. The
+  // cut-off is 64 MB; the environment variable B200_PDL_MAX_MB moves it for A/B runs.
   static const size_t pdl_max_mb = [] {
     const char* e = getenv("B200_PDL_MAX_MB");
-    return e ? (size_t)atoi(e) : (size_t)24;
+    return e ? (size_t)atoi(e) : (size_t)64;
   }();
   const size_t weight_bytes = (size_t)(mode == 2 ? 2 * N : N) * K / 2;
   if (weight_bytes > (pdl_max_mb << 20)) {
