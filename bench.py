@@ -17,8 +17,17 @@ One benchmark "step" = one pass of that workload. What is timed:
 With --gpus N > 1 every rank decodes its own sequence on its own copy of the model (no collective on the data
 path: weak scaling); the time is the max over ranks and `value` the sum of all ranks' tokens over it.
 
-The other configurations (single kernels, context sweep and ablations, the tensor-parallel 70B shape) have their own
-drivers: llm_decode_kernels_b200/kernel_bench.py and llm_decode_kernels_b200/e2e_bench.py.
+Before anything is timed, the step kernel that will be timed decodes 40 tokens of a 2-layer model of the same widths
+and its logits are compared with the CPU oracle on identical weights; if they differ beyond the tolerance no line is
+printed ("parity_checked" in the line says what was compared).
+
+The line also carries, beside the headline:
+  kernels : the single-kernel configurations - the 5632 x 2048 W4A16 GEMV and paged attention at batch 1, contexts
+            128 .. 8192, and batch 8 - timed on cold data (llm_decode_kernels_b200/kernel_bench.py: headline_kernels)
+  tp      : the Llama-3-70B-shape model, context 4096, 128 tokens, tensor-parallel over the N ranks of this run
+            (N = 1: one GPU holds the whole model): tok/s, ms per token, bytes and HBM fraction per GPU; strong
+            scaling, collectives on the data path (llm_decode_kernels_b200/e2e_bench.py: tp_record)
+The context sweep and the fusion ablations have their own driver: llm_decode_kernels_b200/e2e_bench.py ctx.
 
 `--impl reference` times the CPU restatement of the reference's own CPU path (its Model with backend="ref") on
 this host's cores, on a bounded sample of the same workload.
@@ -137,7 +146,7 @@ def run_reference_arm(args, rank):
         return
     threads = os.cpu_count() or 1
     budget = 150.0 / max(1, args.steps + args.warmup) * args.steps   # whole run within a few minutes
-    r = cpu_reference_leg(min(budget, 90.0), threads, layers_sample=None if args.cpu_full else 4)
+    r = cpu_reference_leg(min(budget, 90.0), threads, layers_sample=None if args.cpu_full else 2)
     line = {"impl": "reference", "metric": "batch-1 decode tok/s (W4A16)", "value": round(r["value"], 4),
             "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(r["s_per_token"] * 1e3 * (PROMPT_LEN + NEW_TOKENS), 2), "higher_is_better": True,
@@ -168,6 +177,50 @@ def peak_hbm_gbs():
     return 6650.0, "fallback"
 
 
+# Measured with ncu on the same kernel, TinyLlama shape cut to 6 layers (profiles/decode_step_kernel_tinyllama_6layers.md):
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch over the algorithmic bytes of that launch. Traffic grows
+# with the layers in proportion to the bytes, so the 22-layer figure is this ratio times the step's bytes.
+STEP_TRAFFIC_OVER_ALGORITHMIC = None
+
+
+def parity_gate(dev, step_kernel, n_tokens=40):
+    """The accuracy gate in front of the speed numbers: a 2-layer model of the benchmark's widths (hidden 2048,
+    intermediate 5632, 32/4 heads x 64, vocabulary 32000) through the step kernel that is about to be timed, against
+    the CPU oracle on the same packed weights and block table. Raises if the logits differ by more than 1.5 % of the
+    largest logit or a greedy token differs outside the oracle's own near-tie margin."""
+    from llm_decode_kernels_b200.model import DecodeConfig, Model
+    from oracle import model_oracle as MO
+    c = types.SimpleNamespace(**{**TINYLLAMA, "num_hidden_layers": 2})
+    sd = random_llama_state(c, "cpu", 3)
+    m = Model(sd, c, DecodeConfig(group=GROUP, max_ctx=64, page=16, device=dev, seed=5, step_kernel=step_kernel))
+    packed = {f"layers.{i}.{k}": (lw[k].packed.cpu(), lw[k].sz.cpu()) for i, lw in enumerate(m.layers)
+              for k in ("qkv", "o", "gu", "down")}
+    packed["lm_head"] = (m.lm_head.packed.cpu(), m.lm_head.sz.cpu())
+    ocfg = types.SimpleNamespace(group=GROUP, quant="rtn", qparams=None, max_ctx=64, page=16, shuffle_pages=True)
+    o = MO.OracleModel(sd, c, ocfg, packed=packed, block_table=m.bt.cpu())
+    g = torch.Generator().manual_seed(11)
+    stream = torch.randint(0, c.vocab_size, (n_tokens,), generator=g).tolist()
+    ref = o.teacher_force(stream, collect_logits=True).float()
+    m.prepare(64, use_graph=True)
+    m.reset(0)
+    got = m.teacher_force(stream, collect_logits=True).float().cpu()
+    assert m.step_error() == 0, "a bounded wait inside the step gave up during the parity check"
+    scale = ref.abs().max().item()
+    err = (got - ref).abs().max().item() / scale
+    flips = 0
+    for t in range(n_tokens):
+        a, b = int(got[t].argmax()), int(ref[t].argmax())
+        if a != b:
+            flips += 1
+            if ref[t, b] - ref[t, a] > 2e-2 * scale:
+                raise SystemExit(f"parity check failed: token {t} differs from the oracle outside the noise floor")
+    if not err <= 1.5e-2:
+        raise SystemExit(f"parity check failed: logits differ from the oracle by {err:.3e} of the largest logit")
+    return {"against": "CPU oracle, identical packed weights and block table", "layers": 2, "widths": "benchmark's own",
+            "tokens": n_tokens, "step_kernel": "persistent" if m.persistent else "multi",
+            "max_logit_err_rel": float(f"{err:.3e}"), "tolerance": 1.5e-2, "near_tie_flips": flips}
+
+
 def run_b200_arm(args, rank, world, local_rank):
     from llm_decode_kernels_b200 import ext
     from llm_decode_kernels_b200.model import DecodeConfig, Model
@@ -177,6 +230,7 @@ def run_b200_arm(args, rank, world, local_rank):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device(dev))
+    parity = parity_gate(dev, args.step_kernel) if rank == 0 else None
     c = types.SimpleNamespace(**TINYLLAMA)
     sd = random_llama_state(c, dev, 0)
     cfg = DecodeConfig(group=GROUP, max_ctx=PROMPT_LEN + NEW_TOKENS, page=16, device=dev, seed=0,
@@ -302,17 +356,35 @@ def run_b200_arm(args, rank, world, local_rank):
         step_achieved = step_bytes / (us_per_token * 1e-6) / 1e9
         roofline = {"bound": "hbm", "kernel": "decode_step_kernel", "achieved": round(step_achieved, 1), "peak": peak,
                     "peak_source": f"{peak_kind} copy bandwidth", "unit": "GB/s", "frac": round(step_achieved / peak, 4),
-                    "traffic": None, "bytes_per_launch": step_bytes,
-                    "how": "weights + KV bytes of one token at context 256 / CUDA-event time per graph replay"}
+                    "traffic": (round(STEP_TRAFFIC_OVER_ALGORITHMIC * step_bytes)
+                                if STEP_TRAFFIC_OVER_ALGORITHMIC else None),
+                    "bytes_per_launch": step_bytes,
+                    "how": "weights + KV bytes of one token at context 256 / CUDA-event time per graph replay; traffic "
+                           "= ncu dram bytes of a 6-layer launch scaled by the bytes"}
     else:
         roofline = dict(gemv_roofline, bound="hbm", peak=peak, peak_source=f"{peak_kind} copy bandwidth", traffic=None)
+    if m.persistent and parity is not None:
+        assert parity["step_kernel"] == "persistent"
+    # ---- the single-kernel configurations and the tensor-parallel 70B shape, recorded beside the headline
+    kernels = None
+    if rank == 0 and not args.no_kernels:
+        from llm_decode_kernels_b200.kernel_bench import headline_kernels
+        kernels = headline_kernels(K, peak)
+    persistent = m.persistent
+    del m, gg, bufs, lins
+    torch.cuda.empty_cache()
+    tp = None
+    if not args.no_tp:
+        from llm_decode_kernels_b200.e2e_bench import tp_record
+        barrier()
+        tp = tp_record(rank, world, local_rank, dist)
     if rank == 0:
         line = {"metric": "batch-1 decode tok/s (W4A16)", "value": round(value, 2), "unit": "tok/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4),
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "f16 storage, f32 accumulate (int4 weights)", "data": "synthetic",
                 "config": workload_config(),
-                "us_per_token": round(us_per_token, 3), "step_kernel": "persistent" if m.persistent else "multi",
+                "us_per_token": round(us_per_token, 3), "step_kernel": "persistent" if persistent else "multi",
                 "step_roofline": {"bytes_per_token": step_bytes,
                                   "floor_us_at_peak": round(step_bytes / (peak * 1e9) * 1e6, 2),
                                   "frac_of_peak": round(step_bytes / (dev_ms * 1e-3 / (args.steps * NEW_TOKENS))
@@ -325,7 +397,7 @@ def run_b200_arm(args, rank, world, local_rank):
                         "ms_per_step": round(e2e_s / args.steps * 1e3, 3)},
                 "gpu_launches": launches_per_token * NEW_TOKENS * args.steps,
                 "clocks": sampler.summary(), "wall_s_timed_region": round(t_wall, 3),
-                "sample_tokens": toks[:8]}
+                "sample_tokens": toks[:8], "parity_checked": parity, "kernels": kernels, "tp": tp}
         if world == 1 and not args.no_cpu:
             r = cpu_reference_leg(args.cpu_seconds, os.cpu_count() or 1, layers_sample=2)
             line["cpu_baseline"] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in r.items()
@@ -345,6 +417,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="time budget of the cpu_baseline leg")
     ap.add_argument("--cpu-full", action="store_true", help="reference arm: build all 22 layers on the CPU")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the single-kernel configurations")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel 70B-shape record")
     ap.add_argument("--step-kernel", default="auto", choices=["auto", "persistent", "multi"],
                     help="how Model runs a decode step (see DecodeConfig.step_kernel)")
     args = ap.parse_args()

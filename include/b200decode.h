@@ -95,6 +95,14 @@ int b200_gemv_w4a16_tile_repack(const void* Wp, const void* SZ, void* out, int N
                                 void* stream);
 int b200_gemv_w4a16_tiled(const void* Wt, const void* x, void* y, int N, int K, int swiglu, void* stream);
 
+/* Launch shape of the tensor-core GEMV for one matrix shape, found by measurement instead of the built-in heuristic
+ * (the counterpart of the per-shape (stage, R, warps, pf) table the reference grows with scripts/autotune.py:1-58 and
+ * reads in runtime/model.py:174-178). layout: 0 row-major tensors (b200_gemv_w4a16 with R = 0), 1 tile layout,
+ * 2 paired gate|up tile layout (N = outputs). ksplit in {1, 2, 4, 8} warps share a 16-row tile by splitting K;
+ * blocks = thread blocks to launch at most. ksplit = 0 forgets the shape. Host-side table of the process (128 shapes,
+ * B200_ERR_LIMIT beyond); set it up before launching from other threads. */
+int b200_gemv_w4a16_tune(int layout, int N, int K, int ksplit, int blocks);
+
 /* b200_add_rmsnorm followed by b200_gemv_w4a16_tiled, in one launch: r = x_in + delta (fp16 add; delta may be NULL),
  * x = norm_w * half(float(r) * rsqrt(mean(r^2) + eps)), y = W x (or SwiGLU of it). Every thread block normalises
  * its own copy of the K activations while its first weights are in flight; r goes to x_out, which must not be
@@ -157,10 +165,11 @@ int b200_rope_append_batched(void* qkv, const float* cos_t, const float* sin_t, 
 int b200_dequant_w4a16(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, void* stream);
 
 /* x[H] = emb[tok[0], :]; tok is int64 [1] on the device (the reference's step does this with
- * torch.index_select, runtime/model.py:218). emb, x 16B; H % 8 == 0. */
-int b200_embed_row(const void* emb, const long long* tok, void* x, int H, void* stream);
+ * torch.index_select, runtime/model.py:218). emb fp16 [V, H], x 16B; H % 8 == 0. A token outside [0, V) reads row 0
+ * instead of memory outside the table. */
+int b200_embed_row(const void* emb, const long long* tok, void* x, int H, int V, void* stream);
 
-/* tok[0] = index of the largest fp16 logit (lowest index on ties, NaNs skipped). If pos != NULL: when history
+/* tok[0] = index of the largest fp16 logit (lowest index on ties, NaNs skipped; 0 if every logit is NaN). If pos != NULL: when history
  * != NULL, history[pos[0]] = tok[0] (int64 array long enough for every position); then pos[0] += 1.
  * (torch.argmax and `pos += 1` in the reference's step, runtime/model.py:232-233.) */
 int b200_argmax(const void* logits, int V, long long* tok, int* pos, long long* history, void* stream);
@@ -175,8 +184,8 @@ int b200_argmax(const void* logits, int V, long long* tok, int* pos, long long* 
 /* One decoder layer. An array of L of these lives in DEVICE memory. Matrix order in w[]:
  * 0 = [q;k;v] ((n_q + 2 n_kv) D x H), 1 = o (H x n_q D), 2 = [gate;up] (2I x H), 3 = down (H x I). */
 typedef struct b200_step_layer {
-  const void* w[4];  /* the matrix in stream layout, made by b200_decode_step_repack (same size as packed + sz) */
-  const void* sz[4]; /* unused (the stream layout carries scale/zero); set to NULL */
+  const void* w[4];  /* the matrix in tile layout (b200_gemv_w4a16_tile_repack); w[2] with gate_up = 1 */
+  const void* sz[4]; /* unused (the tile layout carries scale/zero); set to NULL */
   const void* ln1;   /* fp16 [H] */
   const void* ln2;   /* fp16 [H] */
   void* kc;          /* fp16 [pages, n_kv, P, D] */
@@ -190,7 +199,7 @@ typedef struct b200_step_desc {
   float eps;
   const void* emb;     /* fp16 [vocab, H] */
   const void* norm_f;  /* fp16 [H] */
-  const void* w_head;  /* LM head [V, H] in stream layout (b200_decode_step_repack) */
+  const void* w_head;  /* LM head [V, H] in tile layout (b200_gemv_w4a16_tile_repack, gate_up = 0) */
   const void* sz_head; /* unused; NULL */
   const float* cos_t;  /* fp32 [max_pos, D/2] */
   const float* sin_t;
@@ -203,25 +212,20 @@ typedef struct b200_step_desc {
   void* ctrl;          /* 16 bytes, zeroed once: {uint32 completed steps, int32 error, int32 abort, pad} */
   int ctx_cap;         /* largest context (pos + 1) this launch may see */
   int grid;            /* CTAs = SMs of the device */
-  long long* trace;    /* NULL, or int64 [grid, 16 + 16 L]: per-CTA globaltimer (ns) at every phase boundary */
+  long long* trace;    /* NULL. (A library built with -DB200_STEP_TRACE, which the normal build never is, fills an
+                        * int64 [grid, 8 + 21 (L + 1)] array here with per-CTA globaltimer values inside every phase.) */
 } b200_step_desc;
-
-/* Rearrange one quantized matrix for the step kernel ("stream layout"): out (N * (K/2 + 4 K/G) bytes, 16B) receives,
- * CTA slice after CTA slice and ring stage after ring stage, each stage's packed rows followed by their (scale, zero)
- * rows, so that the kernel's producer fetches a stage with ONE bulk copy. Wp int32 [N, K/8], SZ half2 [N, K/G] are
- * the quantizer's tensors and are not modified. gate_up != 0: the matrix is [gate; up] (N = 2I rows) and row i is
- * paired with row I + i. kmax = max(H, n_q D, I) of the model and grid = the CTA count b200_decode_step will be
- * launched with; both fix the stage size and must match the launch. K % 128 == 0 and (K/G) % 4 == 0. */
-int b200_decode_step_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up, int kmax,
-                            int grid, void* stream);
 
 /* Bytes of exchange memory a step of these dimensions needs. */
 size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D, int grid);
 
-/* Launch one step. B200_ERR_SHAPE if the dimensions do not fit the kernel's shared-memory plan (use the
- * per-operator entry points then), B200_ERR_LIMIT if ctx_cap is beyond what the in-kernel attention holds.
+/* Launch one step. B200_ERR_SHAPE if the dimensions do not fit the kernel (H, n_q D and I multiples of 128, group size
+ * a multiple of 128, pages of at most 64 tokens, the shared-memory plan; use the per-operator entry points then),
+ * B200_ERR_LIMIT if ctx_cap is beyond what the in-kernel attention holds.
  * Waits inside the kernel are bounded: if one gives up, ctrl.error becomes non-zero (1 tag poll, 2 ring full,
- * 3 ring empty) and the step's outputs are invalid; the caller checks it after synchronising. */
+ * 3 ring empty) and the step's outputs are invalid; the caller checks it after synchronising. ctrl.error = 4: tok was
+ * outside [0, V) - row 0 of the embedding was used instead and the step completed. A logit vector with no comparable
+ * entry (all NaN) yields token 0, as an in-range answer like torch.argmax's. */
 int b200_decode_step(const b200_step_desc* d, void* stream);
 
 /* ---- tensor-parallel exchange over NVLink peer memory (one process per GPU, all GPUs in one node) ----
@@ -242,7 +246,11 @@ int b200_comm_import(const void* handle64, void** ptr);
 int b200_comm_unimport(void* ptr);
 /* Zero the block's header (flags, step counter, error word). Call on every rank, between two host-side barriers. */
 int b200_comm_reset(void* base);
-/* *code = 0, or 1 once a bounded wait for a peer ran out (that call's outputs are invalid). Synchronises. */
+/* How many polls an exchange kernel of this rank spends on one peer before it gives up (0 = the default, about four
+ * seconds). A rank that knows its peers answer within microseconds can set a bound of milliseconds, so that a peer
+ * that has died is reported quickly. Kept across b200_comm_reset. Synchronises. */
+int b200_comm_set_wait_limit(void* base, unsigned int polls);
+/* *code = 0, or 1 once a bounded wait for a peer ran out (that call's outputs are untouched and invalid). Synchronises. */
 int b200_comm_error(const void* base, int* code);
 
 /* Replaces "NCCL all-reduce, then add_rmsnorm" after a row-split projection. Every rank's GEMV has written its

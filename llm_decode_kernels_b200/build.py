@@ -15,7 +15,6 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-OBJ = CSRC / "_obj"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libb200decode.so"
 
@@ -39,8 +38,12 @@ def _newest_header():
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
-def build(force=False, verbose=False):
-    """Compile what is stale and link. Returns the path of the shared library."""
+def build(force=False, verbose=False, defines=(), lib=LIB):
+    """Compile what is stale and link. Returns the path of the shared library. `defines` (macro names) and `lib`
+    make a variant of the library next to the normal one, with its own object directory: step_trace.py builds
+    libb200decode_trace.so with B200_STEP_TRACE this way."""
+    lib = Path(lib)
+    OBJ = CSRC / ("_obj" if not defines else "_obj_" + "_".join(sorted(defines)).lower())
     OBJ.mkdir(exist_ok=True)
     hdr = _newest_header()
     jobs = []
@@ -51,7 +54,7 @@ def build(force=False, verbose=False):
 
     def compile_one(job):
         src, obj = job
-        cmd = [nvcc(), *NVCC_FLAGS, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -64,13 +67,13 @@ def build(force=False, verbose=False):
             if r.returncode:
                 raise RuntimeError(f"nvcc failed on {src.name}")
     objs = [OBJ / (s.stem + ".o") for s in sources()]
-    if jobs or not LIB.exists():
-        cmd = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *map(str, objs)]
+    if jobs or not lib.exists():
+        cmd = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(lib), *map(str, objs)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
-            raise RuntimeError("link of libb200decode.so failed")
-    return LIB
+            raise RuntimeError(f"link of {lib.name} failed")
+    return lib
 
 
 if __name__ == "__main__":

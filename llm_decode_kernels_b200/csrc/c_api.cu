@@ -5,13 +5,13 @@
 #include "../../include/b200decode.h"
 #include "common.cuh"
 #include "decode_step.h"
-#include <stdlib.h>
 #include <string.h>
 
 namespace b200 {
 cudaError_t gemv_w4a16_dispatch(int stage, int R, int warps, const void* Wp, const void* SZ, const void* x, void* y,
                                 int N, int K, int log2G, cudaStream_t st);
 size_t gemv_tiled_bytes(int N, int K, int gate_up);
+bool gemv_mma_tune(int mode, int N, int K, int ksplit, int blocks);
 cudaError_t gemv_tile_repack_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up,
                                       cudaStream_t st);
 cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, int N, int K, int swiglu,
@@ -26,15 +26,13 @@ cudaError_t swiglu_dispatch(const void* gu, void* out, int I, cudaStream_t st);
 cudaError_t rope_append_dispatch(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt,
                                  int bt_stride, void* kc, void* vc, int B, int n_q, int n_kv, int D, int log2P,
                                  cudaStream_t st);
-cudaError_t embed_row_dispatch(const void* emb, const long long* tok, void* x, int H, cudaStream_t st);
+cudaError_t embed_row_dispatch(const void* emb, const long long* tok, void* x, int H, int V, cudaStream_t st);
 cudaError_t argmax_dispatch(const void* logits, int V, long long* tok, int* pos, long long* history,
                             cudaStream_t st);
 cudaError_t bw_read_dispatch(const void* p, size_t bytes, void* sink, int blocks, int threads, int unroll,
                              cudaStream_t st);
 cudaError_t bw_read_bulk_dispatch(const void* p, size_t bytes, void* sink, int blocks, int stage_bytes, int stages,
                                   cudaStream_t st);
-cudaError_t repack_stream_dispatch(const void* W, const void* SZ, void* out, int N, int K, int log2G, int gu, int ncta,
-                                   int stage_w, cudaStream_t st);
 cudaError_t paged_attention_status(int* code);
 cudaError_t rope_paged_attention_dispatch(void* qkv, const float* cos_t, const float* sin_t, void* kc, void* vc,
                                           const int* bt, const int* pos, int n_q, int n_kv, int D, int log2P, int PS,
@@ -47,6 +45,7 @@ cudaError_t tp_allgather_dispatch(const void* const* peers, int rank, int W, siz
 int comm_header_bytes();
 int comm_max_ranks();
 int comm_error_offset();
+int comm_limit_offset();
 cudaError_t paged_attention_dispatch(int version, const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
                                      const int* pos, int B, int n_q, int n_kv, int D, int log2P, int PS,
                                      int max_splits, float* o_part, float* m_part, float* l_part, void* out,
@@ -64,6 +63,10 @@ inline int finish(cudaError_t e) {
 }
 inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 }  // namespace
+
+namespace b200 {
+void record_cuda_error(cudaError_t e) { g_last_cuda = e; }
+}  // namespace b200
 
 #define REQUIRE(cond, code) \
   do {                      \
@@ -130,6 +133,12 @@ int b200_gemv_w4a16_tiled_norm(const void* Wt, const void* x_in, const void* del
   REQUIRE(aligned16(Wt) && aligned8(x_in) && aligned8(norm_w) && aligned8(x_out) && (!delta || aligned8(delta)),
           B200_ERR_ALIGN);
   return finish(b200::gemv_w4a16_tiled_norm_dispatch(Wt, x_in, delta, norm_w, eps, x_out, y, N, K, swiglu, S(stream)));
+}
+
+int b200_gemv_w4a16_tune(int layout, int N, int K, int ksplit, int blocks) {
+  REQUIRE(layout >= 0 && layout <= 2 && N > 0 && K > 0 && K % 128 == 0, B200_ERR_ARG);
+  REQUIRE(ksplit == 0 || ((ksplit == 1 || ksplit == 2 || ksplit == 4 || ksplit == 8) && blocks > 0), B200_ERR_ARG);
+  return b200::gemv_mma_tune(layout, N, K, ksplit, blocks) ? B200_OK : B200_ERR_LIMIT;
 }
 
 int b200_bw_read(const void* p, size_t bytes, void* sink, int blocks, int threads, int unroll, void* stream) {
@@ -244,27 +253,14 @@ int b200_dequant_w4a16(const void* Wp, const void* SZ, void* out, int N, int K, 
   return finish(b200::dequant_w4a16_dispatch(Wp, SZ, out, N, K, log2G, S(stream)));
 }
 
-int b200_embed_row(const void* emb, const long long* tok, void* x, int H, void* stream) {
-  REQUIRE(emb && tok && x && H > 0, B200_ERR_ARG);
+int b200_embed_row(const void* emb, const long long* tok, void* x, int H, int V, void* stream) {
+  REQUIRE(emb && tok && x && H > 0 && V > 0, B200_ERR_ARG);
   REQUIRE(H % 8 == 0, B200_ERR_SHAPE);
   REQUIRE(aligned16(emb) && aligned16(x), B200_ERR_ALIGN);
-  return finish(b200::embed_row_dispatch(emb, tok, x, H, S(stream)));
+  return finish(b200::embed_row_dispatch(emb, tok, x, H, V, S(stream)));
 }
 
 static inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
-// Bytes of packed rows one ring stage of the step kernel holds: at least two rows of the widest matrix.
-static inline int step_stage_w(int kmax) { return align_up(kmax > 32768 ? kmax : 32768, 128); }
-
-int b200_decode_step_repack(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, int gate_up, int kmax,
-                            int grid, void* stream) {
-  REQUIRE(Wp && SZ && out && N > 0 && K > 0 && grid > 0 && kmax >= K, B200_ERR_ARG);
-  REQUIRE(K % 128 == 0 && log2G >= 5 && log2G <= 10 && K % (1 << log2G) == 0 && ((K >> log2G) % 4) == 0,
-          B200_ERR_SHAPE);
-  REQUIRE(!gate_up || N % 2 == 0, B200_ERR_SHAPE);
-  REQUIRE(aligned16(Wp) && aligned16(SZ) && aligned16(out), B200_ERR_ALIGN);
-  return finish(b200::repack_stream_dispatch(Wp, SZ, out, N, K, log2G, gate_up ? 1 : 0, grid, step_stage_w(kmax),
-                                             S(stream)));
-}
 
 size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D, int grid) {
   const size_t per_layer = (size_t)(n_q + 2 * n_kv) * D + (size_t)n_q * D + H + I + H;
@@ -279,18 +275,17 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
   REQUIRE(d->L > 0 && d->H > 0 && d->I > 0 && d->n_q > 0 && d->n_kv > 0 && d->V > 0 && d->grid > 0 && d->ctx_cap > 0,
           B200_ERR_ARG);
   REQUIRE(d->D == 64 || d->D == 128, B200_ERR_SHAPE);
-  REQUIRE(d->n_q % d->n_kv == 0 && d->log2G >= 5 && d->log2G <= 10 && d->log2P >= 0 && d->log2P < 16, B200_ERR_SHAPE);
-  const int n_att = d->n_q * d->D;
+  // the tile layout holds one (scale, zero) per row and 128 columns: group sizes are multiples of 128
+  REQUIRE(d->n_q % d->n_kv == 0 && d->log2G >= 7 && d->log2G < 31 && d->log2P >= 0 && d->log2P < 16, B200_ERR_SHAPE);
+  const int n_att = d->n_q * d->D, n_qkv = (d->n_q + 2 * d->n_kv) * d->D;
   const int Ks[3] = {d->H, n_att, d->I};
   int kmax = 0;
   for (int K : Ks) {
-    // rows are copied with 16-byte-granular bulk copies: packed row and scale/zero row must both be multiples of 16 B
-    REQUIRE(K % 128 == 0 && K % (1 << d->log2G) == 0 && ((K >> d->log2G) % 4) == 0, B200_ERR_SHAPE);
+    REQUIRE(K % 128 == 0 && K % (1 << d->log2G) == 0, B200_ERR_SHAPE);
     kmax = K > kmax ? K : kmax;
   }
-  REQUIRE(d->H % 8 == 0 && d->I % 8 == 0, B200_ERR_SHAPE);
-  REQUIRE(aligned16(d->emb) && aligned16(d->norm_f) && aligned16(d->w_head) &&
-              aligned16(d->xchg) && aligned16(d->ctrl),
+  REQUIRE(aligned16(d->emb) && aligned16(d->norm_f) && aligned16(d->w_head) && aligned16(d->xchg) &&
+              aligned16(d->ctrl) && aligned16(d->layers),
           B200_ERR_ALIGN);
   REQUIRE(d->ctx_cap <= (1 << 20), B200_ERR_LIMIT);
 
@@ -302,41 +297,34 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
   p.cos_t = d->cos_t; p.sin_t = d->sin_t; p.bt = d->bt; p.tok = d->tok; p.pos = d->pos; p.history = d->history;
   p.logits = (half*)d->logits; p.xchg = (uint32_t*)d->xchg; p.ctrl = (b200::StepCtrl*)d->ctrl;
   p.trace = d->trace;
-  {
-    const char* dbg = getenv("B200_STEP_DEBUG");   // timing experiments only; see decode_step.h
-    p.debug = dbg ? atoi(dbg) : 0;
-  }
   // shared-memory plan
   const int ncw = b200::decode_step_consumer_warps();
-  p.resid_bytes = align_up(2 * d->H, 128);
-  p.xin_bytes = align_up(2 * kmax, 128);
-  p.xsum_bytes = align_up((kmax / 32) * 4, 128);
-  p.att_bytes = align_up((4 * d->D + ncw * d->D + 2 * ncw + 64) * 4, 128);
+  const int resid_bytes = align_up(2 * d->H, 128);
+  const int xin_bytes = align_up(2 * kmax, 128);
+  const int xsum_bytes = align_up((kmax / 128) * 4, 128);
+  const int att_bytes = align_up((4 * d->D + ncw * d->D + 2 * ncw + d->D + 64) * 4, 128);
+  int part_bytes;
   {
-    // partial sums of one slice: 2 rows per unit, one float per 1024-weight segment of each row
-    const int n_qkv = (d->n_q + 2 * d->n_kv) * d->D;
-    const int units[5] = {(n_qkv + 1) / 2, (d->H + 1) / 2, d->I, (d->H + 1) / 2, (d->V + 1) / 2};
-    const int ks[5] = {d->H, n_att, d->H, d->I, d->H};
-    int floats = 0;
-    for (int i = 0; i < 5; ++i) {
-      const int per_cta = (units[i] + d->grid - 1) / d->grid, segs = (ks[i] / 32 + 31) / 32;
-      floats = 2 * per_cta * segs > floats ? 2 * per_cta * segs : floats;
-    }
-    p.part_bytes = align_up(floats * 4, 128);
+    // partial sums: one float per consumer warp and row slot of the CTA's tiles (16 slots per tile); the layer
+    // phases alternate between two buffers, the LM head uses the same area as one
+    auto tiles_per_cta = [&](int tiles) { return (tiles + d->grid - 1) / d->grid; };
+    const int layer_tiles[4] = {(n_qkv + 15) / 16, (d->H + 15) / 16, (d->I + 7) / 8, (d->H + 15) / 16};
+    int mt = 1;
+    for (int t : layer_tiles) mt = tiles_per_cta(t) > mt ? tiles_per_cta(t) : mt;
+    p.part_stride = 16 * mt + 1;                                      // odd pitch: the warps' rows start in
+    p.part_stride_head = 16 * tiles_per_cta((d->V + 15) / 16) + 1;    // different banks
+    const int a = 2 * ncw * p.part_stride, b = ncw * p.part_stride_head;
+    part_bytes = align_up((a > b ? a : b) * 4, 128);
   }
-  p.table_bytes = align_up(d->L * (int)sizeof(b200::StepLayer), 128);
-  REQUIRE(aligned16(d->layers), B200_ERR_ALIGN);
-  p.stage_w = step_stage_w(kmax);
-  // attention copies whole KV pages into a stage: at least one page of K and of V must fit
-  REQUIRE(((4 * d->D) << d->log2P) <= p.stage_w, B200_ERR_SHAPE);
-  int max_sz = 0;
-  for (int K : Ks) {
-    const int rowbytes = K / 2, ups = p.stage_w / (2 * rowbytes) > 1 ? p.stage_w / (2 * rowbytes) : 1;
-    const int sz = 2 * ups * ((K >> d->log2G) * 4);
-    max_sz = sz > max_sz ? sz : max_sz;
-  }
-  p.stage_bytes = p.stage_w + align_up(max_sz, 128);
-  const size_t fixed = b200::decode_step_smem_fixed(p);
+  const int table_bytes = align_up(d->L * (int)sizeof(b200::StepLayer), 128);
+  p.ups = 32;
+  p.stage_w = p.ups * b200::kTileUnitBytes;
+  p.stage_bytes = align_up(p.stage_w, 128);
+  // attention copies whole KV pages into a stage, K rows in one half and V rows in the other
+  const int P = 1 << d->log2P;
+  REQUIRE(P <= b200::decode_step_max_kv_tokens() && 4 * d->D * P <= p.stage_w, B200_ERR_SHAPE);
+  const size_t fixed = b200::decode_step_plan_smem(p, resid_bytes, xin_bytes, xsum_bytes, att_bytes, part_bytes,
+                                                   table_bytes);
   const size_t budget = 227 * 1024;
   REQUIRE(fixed + 2 * (size_t)p.stage_bytes <= budget, B200_ERR_SHAPE);
   int ns = (int)((budget - fixed) / p.stage_bytes);
@@ -393,7 +381,15 @@ int b200_comm_unimport(void* ptr) {
 
 int b200_comm_reset(void* base) {
   REQUIRE(base, B200_ERR_ARG);
-  cudaError_t e = cudaMemset(base, 0, b200::comm_header_bytes());
+  // flags, step counter and error word; the wait bound (b200_comm_set_wait_limit) is a setting and stays
+  cudaError_t e = cudaMemset(base, 0, b200::comm_limit_offset());
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  return finish(e);
+}
+
+int b200_comm_set_wait_limit(void* base, unsigned int polls) {
+  REQUIRE(base, B200_ERR_ARG);
+  cudaError_t e = cudaMemcpy((char*)base + b200::comm_limit_offset(), &polls, sizeof(polls), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   return finish(e);
 }

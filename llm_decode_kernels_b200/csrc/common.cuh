@@ -1,5 +1,7 @@
-// Device helpers shared by every kernel of the decode step. Target: sm_100a (B200), fp16 storage,
-// fp32 accumulation, no tensor-core instructions (the batch-1 step is a stream of GEMVs).
+// Device helpers shared by every kernel of the decode step. Target: sm_100a (B200), fp16 storage, fp32
+// accumulation. The GEMV and attention kernels feed warp-level mma.sync.m16n8k16 with operands taken straight from
+// the packed format (see "tensor-core operands" below); nothing here uses the 64-row-and-up tcgen05 MMAs, which a
+// batch-1 step cannot fill.
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -40,8 +42,6 @@ DEVI float warp_max(float v) {
 DEVI void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 DEVI void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-bool pdl_enabled();   // false when the environment variable B200_PDL is set to 0 (for A/B timing)
-
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                               Args... args) {
@@ -54,8 +54,23 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is a per-device setting: launchers remember, per device, the size
+// they have already allowed. `state` is a function-local static array of kMaxDevices zeros.
+constexpr int kMaxDevices = 64;
+template <typename Kern>
+inline cudaError_t allow_dynamic_smem(Kern kern, size_t bytes, size_t* state) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool tracked = dev >= 0 && dev < kMaxDevices;
+  if (bytes <= 48 * 1024 || (tracked && bytes <= state[dev])) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && tracked) state[dev] = bytes;
+  return e;
 }
 
 // launch_pdl(...) inside a function that returns cudaError_t: a refused launch is returned at once
@@ -184,6 +199,27 @@ DEVI void chunk_two_rows(uint4 wa, uint4 wb, half2 sza, half2 szb, const XChunk&
   p0 = fmaf(sa.x, fmaf((fa0.x + fa0.y) + (fa1.x + fa1.y), resc, -sa.y * x.xs), p0);
   p1 = fmaf(sb.x, fmaf((fb0.x + fb0.y) + (fb1.x + fb1.y), resc, -sb.y * x.xs), p1);
 }
+
+// ---- tensor-core operands ------------------------------------------------------------------------------------------
+// mma.sync.m16n8k16, fp16 inputs, fp32 accumulators. Lane (g = lane / 4, t = lane % 4) holds
+//   A: a0 = A[g][2t, 2t+1], a1 = A[g+8][2t, 2t+1], a2 = A[g][2t+8, 2t+9], a3 = A[g+8][2t+8, 2t+9]
+//   B: b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g]        C: c0, c1 = C[g][2t, 2t+1], c2, c3 = C[g+8][2t, 2t+1]
+DEVI void mma16816_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D = A * B (no accumulator input: the first MMA of a unit starts from zero without clearing registers)
+DEVI void mma16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// Bytes of one (16-row tile, 128-column unit) block of the tile layout (gemv_tile_repack_kernel): 512 B for row
+// slots 0-7 (lane l's 16 bytes at 16 l), 512 B for row slots 8-15, 16 x (scale, zero).
+constexpr int kTileUnitBytes = 1088;
 
 // Order key for greedy argmax over fp16 logits: larger value wins, then the lower index. One max-reduction
 // over these keys settles value and tie-break together.

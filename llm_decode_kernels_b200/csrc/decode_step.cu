@@ -4,38 +4,50 @@
 // while the same step as 225 separate launches (the reference's structure, runtime/model.py:216-233) costs ~900 us
 // of launch and pipeline-drain latency. Here one CTA per SM stays resident for the whole step:
 //
-//   * a producer warp streams this CTA's slice of every weight matrix - and, on the CTAs that do attention, the K/V
-//     pages of their head - in the order the step consumes them, into a shared-memory ring with 1-D bulk async
+//   * a producer warp streams this CTA's row tiles of every weight matrix - and, on the CTAs that do attention, the
+//     K/V pages of their head - in the order the step consumes them, into a shared-memory ring with 1-D bulk async
 //     copies (cp.async.bulk + mbarrier transaction counts). Neither weights nor cached K/V depend on this step's
 //     activations, so the producer runs ahead of the computation by the depth of the ring and HBM never idles
 //     while CTAs wait for each other;
-//   * 16 consumer warps do the arithmetic out of the ring: one warp per pair of output rows, x staged once per
-//     phase in shared memory, fp32 accumulation, warp-shuffle reduction;
+//   * 16 consumer warps do the arithmetic out of the ring on the tensor cores (see "inner product" below), with the
+//     row length K split across the warps: warp w owns the 128-column units w, w + 16, ... of every row tile, so it
+//     needs only its own 128-element pieces of the activation vector, fetches exactly those, and keeps them in
+//     registers - no CTA-wide staging pass and no barrier in front of a GEMV. The warps' partial sums meet in shared
+//     memory once per matrix;
 //   * CTAs exchange activation vectors through global memory WITHOUT grid barriers: every fp16 result is stored
 //     as a 32-bit word (tag << 16 | value) whose tag is this step's epoch; a consumer polls the words it needs until
 //     all carry the current tag. One store + one load crosses the chip instead of fence + atomic + poll + load.
-//     Every CTA keeps its own copy of the residual stream in shared memory and redoes the (tiny) residual add and
-//     RMSNorm, so those never touch global memory.
+//     Every CTA keeps its own copy of the residual stream in shared memory (each warp its own units of it) and redoes
+//     the (tiny) residual add and RMSNorm, so those never touch global memory.
 //
-// Inner product without per-weight dequantization. A nibble masked in place is an fp16 SUBNORMAL: bits 0..3 of a
-// half are q * 2^-24, bits 4..7 are q * 2^-20. So (word & 0x000F000F) and (word & 0x00F000F0) are ready-made half2
-// operands; one shift by 8 exposes the other four nibbles. x is staged multiplied by 2^s (pairs under the low mask)
-// or 2^(s-4) (pairs under the high mask), s chosen per phase from max|x| so nothing overflows, which makes every
-// product q * x * 2^(s-24). With xsum = sum of x over a 32-weight chunk,
-//     sum (q - z) * scale * x = scale * (2^(24-s) * sum q x'  -  z * xsum),
-// so the zero point costs one FMA per chunk instead of one subtraction per weight: 9 integer/half2 operations per
-// 8 weights in the loop. The per-element weight this stands for is the format's dequantized weight
-// (dequant_w4a16 in gemv_w4a16.cu proves the format bit-exactly).
+// Weights are read from the tile layout of the tensor-core GEMV (gemv_tile_repack_kernel in gemv_w4a16.cu): per
+// 16-row tile and 128-column unit one 1088-byte block, tiles back to back. A CTA owns a contiguous range of tiles of
+// each matrix, so its share is one contiguous byte range and a ring stage is ONE bulk copy of up to `ups` blocks.
+// The gate|up matrix uses the paired form of the layout (gate row i and up row i in one tile), which puts both
+// halves of a SwiGLU output into the same thread.
+//
+// Inner product. A nibble masked in place is an fp16 SUBNORMAL: bits 0..3 of a half are q * 2^-24, bits 4..7 are
+// q * 2^-20. So (word & 0x000F000F) and (word & 0x00F000F0) are ready-made fp16 pairs, one shift by 8 exposes the
+// other four nibbles of a word, and a 16-row x 128-column block of W is 8 mma.m16n8k16 whose A registers are masked
+// words, with x in column 0 of B. The low-mask and the high-mask products go to two separate fp32 accumulators
+// (one MMA each per word), so x is used as it is - no scaling by max|x|, hence no reduction over the vector in
+// front of the GEMV:
+//     sum_k (q_k - z) * s * x_k  =  s * (2^24 * acc_lo + 2^20 * acc_hi - z * sum_k x_k)        per 128-column unit.
+// The per-element weight this stands for is the format's dequantized weight (dequant_w4a16 in gemv_w4a16.cu proves
+// the format bit-exactly); accumulation is fp32 throughout.
 //
 // Phases per layer (the reference's operator order, with the same rounding points as its fused kernels):
 //   A  resid += down[l-1] (layer 0: resid = embedding row);  x = RMSNorm(resid) * ln1;  qkv = Wqkv x
 //   B  attention: CTA h < n_q takes query head h: RoPE on q and k, append k, v to the paged cache, then per-warp
 //      online softmax over the cached tokens (from the ring) plus the new token, merged once across warps
 //   C  o = Wo attn
-//   D  resid += o;  x = RMSNorm(resid) * ln2;  act = SwiGLU(Wgate x, Wup x)   (gate row i and up row i on one warp)
+//   D  resid += o;  x = RMSNorm(resid) * ln2;  act = SwiGLU(Wgate x, Wup x)
 //   E  down = Wdown act
 // then resid += down;  x = RMSNorm(resid) * norm_f;  logits = Whead x;  per-CTA argmax candidates; CTA 0 merges
 // them (lowest index wins ties), writes tok, history[pos], pos + 1 and the new epoch.
+// Barriers over the consumer threads per phase: one for sum(resid^2) where a norm precedes the GEMV, one between the
+// warps' partial sums and the threads that add them up; the partial-sum buffer alternates between phases so that no
+// third one is needed.
 //
 // Every wait (mbarrier or tag poll) is bounded. A wait that runs out records a code in StepCtrl::error, raises an
 // abort flag that all later waits honour at once, and the CTA leaves after its copies in flight have landed; the
@@ -55,8 +67,10 @@ constexpr int kMaxStages = 16;
 constexpr int kSpinLimit = 1 << 18;         // polls / try_waits before a wait gives up (tens of milliseconds)
 constexpr int kHeaderBytes = 2048;
 constexpr int kMaxKvTokens = 64;            // cached tokens per ring stage in attention (16 warps x 4 tokens)
+constexpr int kPollBatch = 4;               // exchange granules a lane keeps in flight while it polls (plain staging)
+constexpr int kNormBatch = 2;               // the same where a norm follows: units of the residual stream per pass
 
-enum : int { ERR_POLL = 1, ERR_FULL = 2, ERR_EMPTY = 3 };
+enum : int { ERR_POLL = 1, ERR_FULL = 2, ERR_EMPTY = 3, ERR_TOKEN = 4 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------------
 DEVI uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -110,34 +124,56 @@ DEVI uint4 ld_poll4(const uint32_t* p) {
 DEVI void st_tagged(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-DEVI void st_tagged2(uint32_t* p, uint32_t a, uint32_t b) {
-  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
-}
 
 // ---- shared state of one CTA -----------------------------------------------------------------------------------
+// Shared memory: [0, 128) full barriers, [128, 256) empty barriers, 256 abort flag, 272 sum scratch, 512 slices;
+// from kHeaderBytes on: residual stream, then the areas whose offsets the host put into StepParams (off_*).
+// Pointers into it are formed where they are used (one add of a kernel parameter) instead of being carried in
+// registers through the whole step: with 17 warps a thread has 96 registers.
 struct Cta {
-  uint64_t* full;
-  uint64_t* empty;
-  volatile int* abort;   // shared-memory flag, CTA-wide
-  float* red;            // 2 * kNCW floats of reduction scratch
-  half* resid;           // [H] residual stream, private copy
-  uint4* xin;            // [Kmax / 8] activations of the running GEMV, scaled, 16-byte chunks swizzled (see swz)
-  float* xsum;           // [Kmax / 32] sum of the unscaled activations of each 32-weight chunk
-  float* att;            // attention scratch
-  float* part;           // [rows of the largest slice][segments] partial dot products of the running GEMV
-  uint8_t* ring;
-  StepCtrl* ctrl;
+  uint8_t* smem;
+  const StepParams* p;   // the kernel's parameter block (constant bank)
   uint32_t tagw;         // (tag << 16)
-  int ns;                // ring stages
-  int nopoll;            // debug: take exchange words as they are (timing experiments only)
-  int stage_bytes;
+#ifdef B200_STEP_TRACE
+  long long* tr;         // this CTA's row of the trace array (thread 0 stamps), or null
+#endif
+  DEVI uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem) + i; }
+  DEVI uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem) + kMaxStages + i; }
+  DEVI volatile int* abort() const { return reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8); }
+  // kNCW floats: the warps' shares of sum(resid^2)
+  DEVI float* red() const { return reinterpret_cast<float*>(smem + 2 * kMaxStages * 8 + 16); }
+  // [H] residual stream, private copy of the CTA; unit u belongs to warp u % kNCW
+  DEVI half* resid() const { return reinterpret_cast<half*>(smem + kHeaderBytes); }
+  // [Kmax] activations of the running GEMV, natural order; unit u is written and read by one warp only
+  DEVI half* xin() const { return reinterpret_cast<half*>(smem + p->off_xin); }
+  DEVI float* xsum() const { return reinterpret_cast<float*>(smem + p->off_xsum); }   // [Kmax / 128] unit sums
+  DEVI float* att() const { return reinterpret_cast<float*>(smem + p->off_att); }     // attention scratch
+  // partial dot products, [warp][row slot], two buffers used by alternate phases
+  DEVI float* part() const { return reinterpret_cast<float*>(smem + p->off_part); }
+  DEVI uint8_t* stage(int slot) const { return smem + p->off_ring + (size_t)slot * p->stage_bytes; }
+  DEVI StepCtrl* ctrl() const { return p->ctrl; }
 };
 
+// Phase stamps of the instrumented build (-DB200_STEP_TRACE): thread 0 of the CTA stores the nanosecond timer at slot
+// `at` of the CTA's trace row. The normal build compiles these calls to nothing.
+#ifdef B200_STEP_TRACE
+DEVI void stamp(const Cta& c, int at) {
+  if (c.tr && threadIdx.x == 0) {
+    long long t_;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
+    c.tr[at] = t_;
+  }
+}
+#else
+DEVI void stamp(const Cta&, int) {}
+#endif
+constexpr int kTraceHead = 8, kTracePerPhase = 5, kTracePerLayer = 4 * kTracePerPhase + 1;
+
 DEVI void raise(const Cta& c, int code) {
-  if (!*c.abort) {
-    *c.abort = 1;
-    atomicCAS(&c.ctrl->error, 0, code);
-    c.ctrl->abort = 1;
+  if (!*c.abort()) {
+    *c.abort() = 1;
+    atomicCAS(&c.ctrl()->error, 0, code);
+    c.ctrl()->abort = 1;
   }
 }
 
@@ -148,133 +184,150 @@ DEVI bool wait_bar(const Cta& c, uint64_t* bar, uint32_t parity, int code, unsig
 #pragma unroll 1
   for (int i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*c.abort) return false;
+    if (*c.abort()) return false;
     if (nap) __nanosleep(nap);
   }
   raise(c, code);
   return false;
 }
 
-// Poll 4 tagged words until all carry this step's tag; returns the 4 fp16 payloads packed as 2 x half2.
-DEVI uint2 poll4(const Cta& c, const uint32_t* p) {
-  uint4 v = ld_poll4(p);
-  int spins = 0;
-  while (!c.nopoll && ((((v.x ^ c.tagw) | (v.y ^ c.tagw) | (v.z ^ c.tagw) | (v.w ^ c.tagw)) >> 16) != 0)) {
-    if (*c.abort) break;
-    if (++spins > kSpinLimit) { raise(c, ERR_POLL); break; }
-    if ((spins & 255) == 0 && ((volatile StepCtrl*)c.ctrl)->abort) { *c.abort = 1; break; }
-    v = ld_poll4(p);
-  }
-  return make_uint2((v.x & 0xFFFFu) | (v.y << 16), (v.z & 0xFFFFu) | (v.w << 16));
+// ---- tagged exchange words -----------------------------------------------------------------------------------------
+// A word of step s carries tag (s mod 65535) + 1, so a word left over from step s - 65535 would pass for a fresh one.
+// That cannot happen: every exchange word (every output row of every phase of every layer, and the argmax
+// candidates) is rewritten in every step, so a word is never more than one step old when it is polled.
+DEVI bool tags_ok(const Cta& c, uint4 v) {
+  return ((((v.x ^ c.tagw) | (v.y ^ c.tagw) | (v.z ^ c.tagw) | (v.w ^ c.tagw)) >> 16) == 0);
 }
+DEVI uint2 payload(uint4 v) { return make_uint2((v.x & 0xFFFFu) | (v.y << 16), (v.z & 0xFFFFu) | (v.w << 16)); }
 
-// Block-wide (consumer threads) sum and max in one barrier pair.
-DEVI void consumer_sum_max(const Cta& c, float s, float m, int tid, float& s_all, float& m_all) {
-  s = warp_sum(s);
-  m = warp_max(m);
-  if ((tid & 31) == 0) { c.red[tid >> 5] = s; c.red[kNCW + (tid >> 5)] = m; }
-  consumer_sync();
-  float ts = 0.f, tm = 0.f;
+// Poll nb (<= NB, warp-uniform) granules of 4 tagged words, `stride` words apart, until all carry this
+// step's tag; all loads of a round are in flight together. out[k] = the 4 fp16 payloads of granule k as 2 x half2.
+template <int NB>
+DEVI void poll_many(const Cta& c, const uint32_t* base, int stride, int nb, uint2 (&out)[NB]) {
+  constexpr int kPollBatch = NB;
+  uint4 v[kPollBatch];
 #pragma unroll
-  for (int k = 0; k < kNCW; ++k) { ts += c.red[k]; tm = fmaxf(tm, c.red[kNCW + k]); }
-  consumer_sync();
-  s_all = ts;
-  m_all = tm;
-}
-
-// ---- x staging ---------------------------------------------------------------------------------------------------
-// Store granule g (4 activations as 2 x half2, unscaled) scaled into xin and add its sum into xsum (8 granules of
-// consecutive threads make one 32-weight chunk).
-DEVI void put_granule(const Cta& c, int g, uint2 v, const XScale& sc, int tid) {
-  const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
-  float s = (a.x + a.y) + (b.x + b.y);
-  s += __shfl_xor_sync(0xffffffffu, s, 1);
-  s += __shfl_xor_sync(0xffffffffu, s, 2);
-  s += __shfl_xor_sync(0xffffffffu, s, 4);
-  if ((tid & 7) == 0) c.xsum[g >> 3] = s;
-  uint2 o;
-  o.x = as_u32(__hmul2(as_h2(v.x), sc.lo));
-  o.y = as_u32(__hmul2(as_h2(v.y), sc.hi));
-  reinterpret_cast<uint2*>(c.xin)[2 * swz(g >> 1) + (g & 1)] = o;
-}
-
-DEVI float absmax4(uint2 v) {
-  const float2 a = __half22float2(__habs2(as_h2(v.x))), b = __half22float2(__habs2(as_h2(v.y)));
-  return fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y));
-}
-
-// x <- E[0..n) (tagged). n % 32 == 0. Returns the factor that undoes the staging scale.
-DEVI float stage_x_plain(const Cta& c, const uint32_t* E, int n, int tid) {
-  uint2* raw = reinterpret_cast<uint2*>(c.xin);   // pass 1 parks the unscaled granules at their final place
-  float mx = 0.f;
-  for (int g = tid; g < (n >> 2); g += kNT) {
-    const uint2 v = poll4(c, E + 4 * g);
-    raw[2 * swz(g >> 1) + (g & 1)] = v;
-    mx = fmaxf(mx, absmax4(v));
+  for (int k = 0; k < kPollBatch; ++k)
+    if (k < nb) v[k] = ld_poll4(base + (size_t)k * stride);
+  int spins = 0;
+  for (;;) {
+    bool ok = true;
+#pragma unroll
+    for (int k = 0; k < kPollBatch; ++k)
+      if (k < nb && !tags_ok(c, v[k])) ok = false;
+    if (ok || *c.abort()) break;
+    if (++spins > kSpinLimit) { raise(c, ERR_POLL); break; }
+    if ((spins & 255) == 0 && ((volatile StepCtrl*)c.ctrl())->abort) { *c.abort() = 1; break; }
+#pragma unroll
+    for (int k = 0; k < kPollBatch; ++k)
+      if (k < nb && !tags_ok(c, v[k])) v[k] = ld_poll4(base + (size_t)k * stride);
   }
-  float dummy, xmax;
-  consumer_sum_max(c, 0.f, mx, tid, dummy, xmax);
-  const XScale sc = scale_for(xmax);
-  for (int g = tid; g < (n >> 2); g += kNT) put_granule(c, g, raw[2 * swz(g >> 1) + (g & 1)], sc, tid);
-  consumer_sync();
-  return sc.resc;
+#pragma unroll
+  for (int k = 0; k < kPollBatch; ++k)
+    if (k < nb) out[k] = payload(v[k]);
+}
+DEVI uint2 poll4(const Cta& c, const uint32_t* p) {
+  uint2 out[1];
+  poll_many<1>(c, p, 0, 1, out);
+  return out[0];
+}
+
+// ---- x staging, per warp ------------------------------------------------------------------------------------------
+// Warp w stages the units w, w + 16, ... of the activation vector: lane l holds granule l (4 values) of a unit.
+DEVI void put_unit(const Cta& c, int u, uint2 v, int lane) {
+  reinterpret_cast<uint2*>(c.xin())[32 * u + lane] = v;
+  const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
+  const float s = warp_sum((a.x + a.y) + (b.x + b.y));
+  if (lane == 0) c.xsum()[u] = s;
+}
+
+// x <- E[0..K) (tagged).
+DEVI void stage_plain(const Cta& c, const uint32_t* E, int K, int warp, int lane) {
+  const int nunit = K >> 7;
+  for (int u0 = warp; u0 < nunit; u0 += kNCW * kPollBatch) {
+    const int nb = min(kPollBatch, (nunit - u0 + kNCW - 1) / kNCW);
+    uint2 v[kPollBatch];
+    poll_many(c, E + 128 * u0 + 4 * lane, 128 * kNCW, nb, v);
+#pragma unroll
+    for (int k = 0; k < kPollBatch; ++k)
+      if (k < nb) put_unit(c, u0 + kNCW * k, v[k], lane);
+  }
+  __syncwarp();
 }
 
 // resid <- resid + delta (delta tagged; or resid <- emb row when E == nullptr), then
-// x <- w * half(float(resid) * rsqrt(mean(resid^2) + eps)).  H % 32 == 0.
-DEVI float stage_x_norm(const Cta& c, const uint32_t* E, const half* emb_row, const half* w, int H, float eps,
-                        int tid) {
-  uint2* rs = reinterpret_cast<uint2*>(c.resid);
+// x <- w * half(float(resid) * rsqrt(mean(resid^2) + eps)).  One barrier over the consumer threads (the sum).
+DEVI void stage_norm(const Cta& c, const uint32_t* E, const half* emb_row, const half* w, int H, float eps, int warp,
+                     int lane) {
+  const int nunit = H >> 7;
+  uint2* rs = reinterpret_cast<uint2*>(c.resid());
   const uint2* wg = reinterpret_cast<const uint2*>(w);
-  float ss = 0.f, mw = 0.f;
-  for (int g = tid; g < (H >> 2); g += kNT) {
-    const uint2 wv = __ldg(wg + g);   // issued before the poll: its latency hides behind the wait
-    uint2 r;
-    if (E) {
-      const uint2 d = poll4(c, E + 4 * g);
-      r = rs[g];
-      r.x = as_u32(__hadd2(as_h2(r.x), as_h2(d.x)));
-      r.y = as_u32(__hadd2(as_h2(r.y), as_h2(d.y)));
-    } else {
-      r = __ldg(reinterpret_cast<const uint2*>(emb_row) + g);
+  // the norm weights of the first batch are requested before the poll: their latency hides behind the wait
+  uint2 wv0[kNormBatch];
+#pragma unroll
+  for (int k = 0; k < kNormBatch; ++k)
+    if (warp + kNCW * k < nunit) wv0[k] = __ldg(wg + 32 * (warp + kNCW * k) + lane);
+  float ss = 0.f;
+  for (int u0 = warp; u0 < nunit; u0 += kNCW * kNormBatch) {
+    const int nb = min(kNormBatch, (nunit - u0 + kNCW - 1) / kNCW);
+    uint2 d[kNormBatch];
+    if (E) poll_many(c, E + 128 * u0 + 4 * lane, 128 * kNCW, nb, d);
+#pragma unroll
+    for (int k = 0; k < kNormBatch; ++k) {
+      if (k < nb) {
+        const int idx = 32 * (u0 + kNCW * k) + lane;
+        uint2 r;
+        if (E) {
+          r = rs[idx];
+          r.x = as_u32(__hadd2(as_h2(r.x), as_h2(d[k].x)));
+          r.y = as_u32(__hadd2(as_h2(r.y), as_h2(d[k].y)));
+        } else {
+          r = __ldg(reinterpret_cast<const uint2*>(emb_row) + idx);
+        }
+        rs[idx] = r;
+        const float2 a = __half22float2(as_h2(r.x)), b = __half22float2(as_h2(r.y));
+        ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(b.x, b.x, fmaf(b.y, b.y, ss))));
+      }
     }
-    rs[g] = r;
-    const float2 a = __half22float2(as_h2(r.x)), b = __half22float2(as_h2(r.y));
-    ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(b.x, b.x, fmaf(b.y, b.y, ss))));
-    mw = fmaxf(mw, absmax4(make_uint2(as_u32(__hmul2(as_h2(r.x), as_h2(wv.x))), as_u32(__hmul2(as_h2(r.y), as_h2(wv.y))))));
   }
-  float tot, mwall;
-  consumer_sum_max(c, ss, mw, tid, tot, mwall);
+  ss = warp_sum(ss);
+  if (lane == 0) c.red()[warp] = ss;
+  consumer_sync();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < kNCW; ++k) tot += c.red()[k];
   const float rinv = rsqrtf(tot / (float)H + eps);
-  const XScale sc = scale_for(mwall * rinv * 1.01f);
-  for (int g = tid; g < (H >> 2); g += kNT) {
-    const uint2 r = rs[g];   // this thread's own writes
-    const uint2 wv = __ldg(wg + g);
+  int j = 0;
+  for (int u = warp; u < nunit; u += kNCW, ++j) {
+    const int idx = 32 * u + lane;
+    const uint2 r = rs[idx];   // this lane's own write
+    uint2 wv;
+    if (j < kNormBatch) {
+      wv = wv0[0];
+#pragma unroll
+      for (int k = 1; k < kNormBatch; ++k)
+        if (j == k) wv = wv0[k];
+    } else {
+      wv = __ldg(wg + idx);
+    }
     const float2 a = __half22float2(as_h2(r.x)), b = __half22float2(as_h2(r.y));
     uint2 o;
     o.x = as_u32(__hmul2(as_h2(wv.x), __floats2half2_rn(a.x * rinv, a.y * rinv)));
     o.y = as_u32(__hmul2(as_h2(wv.y), __floats2half2_rn(b.x * rinv, b.y * rinv)));
-    put_granule(c, g, o, sc, tid);
+    put_unit(c, u, o, lane);
   }
-  consumer_sync();
-  return sc.resc;
-}
-
-// One entry point for both kinds of staging (a single call site keeps a single copy of the code).
-DEVI float stage_x(const Cta& c, const uint32_t* E, const half* emb_row, const half* nw, int n, float eps, int tid) {
-  return nw ? stage_x_norm(c, E, emb_row, nw, n, eps, tid) : stage_x_plain(c, E, n, tid);
+  __syncwarp();
 }
 
 // ---- GEMV phase -----------------------------------------------------------------------------------------------------
-// A weight matrix in "stream layout" (see repack_stream_kernel): for every CTA, for every ring stage of its slice,
-// the packed rows of the stage followed by their (scale, zero) rows, contiguous - one bulk copy per stage.
+// A weight matrix in tile layout. N = outputs (for gate|up: I, each output made of a gate and an up row).
 struct Mat {
-  const uint8_t* stream;
-  int N, K;            // N rows (for gate|up: N = I units, rows i and I + i)
-  int gu;              // 1: gate|up pairing
+  const uint8_t* base;
+  int N, K;
+  int paired;          // 1: gate|up tiles (8 gate rows + their 8 up rows)
 };
 
-struct Slice { int ub, ue, ups, nstages, rowbytes, szrow; };
+struct Slice { int t0, nt; };   // this CTA's tiles [t0, t0 + nt) of a matrix
 
 // Position in the ring. Stages are used strictly in order by producer and consumers alike, so a slot index and a
 // parity bit that flips on wrap-around replace a stage counter (and the divisions by the ring size it would need).
@@ -288,47 +341,30 @@ DEVI void advance(RingPos& r, int ns) {
   if (++r.slot == ns) { r.slot = 0; r.parity ^= 1u; }
 }
 
-// How the consumer warps split a matrix with rows of K weights: see consume().
-struct WarpMap { int segs, sper, seg0, group, rank, upsmod; };
-DEVI WarpMap warp_map(int K, int ups, int warp) {
-  WarpMap w;
-  const int U = K >> 5;
-  w.segs = (U + 31) >> 5;
-  w.sper = (w.segs + kNCW - 1) / kNCW;
-  w.seg0 = w.sper == 1 ? warp % w.segs : warp;
-  w.group = w.sper == 1 ? (kNCW - w.seg0 + w.segs - 1) / w.segs : 1;
-  w.rank = w.sper == 1 ? warp / w.segs : 0;
-  w.upsmod = ups % w.group;
-  return w;
-}
-
-DEVI Slice slice_of(const Mat& m, int log2G, int stage_w, int cta, int ncta) {
+// Whole tiles are dealt to the CTAs as evenly as they go: a GEMV phase of the step is a handful of tile-units per
+// warp, so one tile more or less on a CTA moves the phase by a tenth of a microsecond, and no row of padding is
+// ever streamed.
+DEVI Slice slice_of(int rows, int paired, int cta, int ncta) {
+  const int tiles = paired ? (rows + 7) >> 3 : (rows + 15) >> 4;
+  const int base = tiles / ncta, rem = tiles % ncta;
   Slice s;
-  s.rowbytes = m.K >> 1;
-  s.szrow = (m.K >> log2G) << 2;
-  const int units = m.gu ? m.N : (m.N + 1) >> 1;
-  const int base = units / ncta, rem = units % ncta;
-  s.ub = cta * base + min(cta, rem);
-  s.ue = s.ub + base + (cta < rem ? 1 : 0);
-  s.ups = max(1, stage_w / (2 * s.rowbytes));
-  s.nstages = (s.ue - s.ub + s.ups - 1) / s.ups;
+  s.t0 = cta * base + min(cta, rem);
+  s.nt = base + (cta < rem ? 1 : 0);
   return s;
 }
 
-// Producer: issue every stage of one matrix slice (one copy each; a bulk copy costs ~0.2 us to issue whatever its
-// size, so several small copies per stage would make the producer the bottleneck). `it` is the running stage
-// counter of the step.
+// Producer: issue every stage of one matrix slice, one copy each (a bulk copy costs ~0.2 us to issue whatever its
+// size, so several small copies per stage would make the producer the bottleneck).
 DEVI void produce(const Cta& c, const Mat& m, const Slice& s, RingPos& rp, int lane) {
-  const size_t rowall = (size_t)s.rowbytes + s.szrow;
-  for (int st = 0; st < s.nstages; ++st, advance(rp, c.ns)) {
+  const int nunit = m.K >> 7, NU = s.nt * nunit;
+  const uint8_t* src = m.base + (size_t)s.t0 * nunit * kTileUnitBytes;
+  for (int i0 = 0; i0 < NU; i0 += c.p->ups, advance(rp, c.p->ns)) {
     const int slot = rp.slot;
-    if (!wait_bar(c, &c.empty[slot], rp.parity, ERR_EMPTY, 200)) return;
+    if (!wait_bar(c, c.empty(slot), rp.parity, ERR_EMPTY, 200)) return;
     if (lane == 0) {
-      const int u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups);
-      const int r0 = 2 * u0, r1 = m.gu ? 2 * u1 : min(m.N, 2 * u1);   // gate|up: two rows per unit, always
-      const uint32_t bytes = (uint32_t)((r1 - r0) * rowall);
-      mbar_expect_tx(&c.full[slot], bytes);
-      bulk_g2s(c.ring + (size_t)slot * c.stage_bytes, m.stream + (size_t)r0 * rowall, bytes, &c.full[slot]);
+      const uint32_t bytes = (uint32_t)(min(c.p->ups, NU - i0) * kTileUnitBytes);
+      mbar_expect_tx(c.full(slot), bytes);
+      bulk_g2s(c.stage(slot), src + (size_t)i0 * kTileUnitBytes, bytes, c.full(slot));
     }
   }
 }
@@ -345,167 +381,138 @@ DEVI void produce_kv(const Cta& c, const StepParams& p, const StepLayer& ly, int
   const int tps = kv_tokens_per_stage(p), pps = tps >> p.log2P;
   const uint32_t page_bytes = (uint32_t)(p.D * 2) << p.log2P;
   const int nst = (pos + tps - 1) / tps;
-  for (int st = 0; st < nst; ++st, advance(rp, c.ns)) {
+  for (int st = 0; st < nst; ++st, advance(rp, c.p->ns)) {
     const int slot = rp.slot;
-    if (!wait_bar(c, &c.empty[slot], rp.parity, ERR_EMPTY, 200)) return;
+    if (!wait_bar(c, c.empty(slot), rp.parity, ERR_EMPTY, 200)) return;
     const int pg0 = st * pps, npg = min(pps, ((pos + (1 << p.log2P) - 1) >> p.log2P) - pg0);
-    uint8_t* dst = c.ring + (size_t)slot * c.stage_bytes;
-    if (lane == 0) mbar_expect_tx(&c.full[slot], 2 * npg * page_bytes);
+    uint8_t* dst = c.stage(slot);
+    if (lane == 0) mbar_expect_tx(c.full(slot), 2 * npg * page_bytes);
     __syncwarp();
     if (lane < npg) {
       const size_t off = ((size_t)p.bt[pg0 + lane] * p.n_kv + kvh) * page_bytes;
-      bulk_g2s(dst + lane * page_bytes, reinterpret_cast<const uint8_t*>(ly.kc) + off, page_bytes, &c.full[slot]);
+      bulk_g2s(dst + lane * page_bytes, reinterpret_cast<const uint8_t*>(ly.kc) + off, page_bytes, c.full(slot));
       bulk_g2s(dst + (size_t)tps * p.D * 2 + lane * page_bytes, reinterpret_cast<const uint8_t*>(ly.vc) + off,
-               page_bytes, &c.full[slot]);
+               page_bytes, c.full(slot));
     }
   }
 }
 
-DEVI XChunk load_xchunk(const Cta& c, int u) {
-  const int sw = (u >> 1) & 3;
-  XChunk r;
-  r.x0 = c.xin[4 * u + (0 ^ sw)];
-  r.x1 = c.xin[4 * u + (1 ^ sw)];
-  r.x2 = c.xin[4 * u + (2 ^ sw)];
-  r.x3 = c.xin[4 * u + (3 ^ sw)];
-  r.xs = c.xsum[u];
-  return r;
-}
-
-// Sum p0 over the warp and p1 over the warp with 6 shuffles instead of 10: the first exchange leaves the lower
-// half-warp holding p0 partials and the upper one p1 partials. Result: lane 0 has sum p0, lane 16 has sum p1.
-DEVI float reduce_pair(float p0, float p1, int lane) {
-  const bool up = lane & 16;
-  float v = up ? p1 : p0;
-  v += __shfl_xor_sync(0xffffffffu, up ? p0 : p1, 16);
+// Consumer side of one matrix slice, one warp's share. The slice is the sequence of tile-unit blocks
+// (tile 0 unit 0, tile 0 unit 1, ..., tile 1 unit 0, ...), `ups` of them per ring stage; warp w takes the blocks of
+// units w, w + 16, ... of every tile. Lane (g, t) reads 16 bytes of row slot g and of row slot g + 8 (columns
+// 32 t .. 32 t + 31 of the unit), lanes (0, t) carry the matching 32 activations as the B operand, the other lanes
+// zeros; 8 MMAs per block. When the warp has passed its last unit of a tile, lanes t == 0 leave the two partial sums
+// of rows g and g + 8 in part[warp][16 * tile + row slot]. A warp whose units do not exist (K < 2048) only keeps the
+// ring's barriers moving.
+DEVI void gemv(const Cta& c, const Mat& m, const Slice& s, float* part, int pstride, RingPos& rp, int warp, int lane,
+               int trace_at) {
+  const int g = lane >> 2, t = lane & 3;
+  const int nunit = m.K >> 7, NU = s.nt * nunit;
+  const bool active = warp < nunit;
+  int tl = 0, u = warp, idx = warp;   // the warp's next block: local tile, unit, place in the sequence
+  int cur_u = -1;
+  uint4 xv[4];
 #pragma unroll
-  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
+  for (int j = 0; j < 4; ++j) xv[j] = make_uint4(0u, 0u, 0u, 0u);
+  float xs = 0.f, ya = 0.f, yb = 0.f;
+  for (int i0 = 0; i0 < NU; i0 += c.p->ups, advance(rp, c.p->ns)) {
+    const int slot = rp.slot;
+    const bool ok = wait_bar(c, c.full(slot), rp.parity, ERR_FULL);
+    if (i0 == 0) stamp(c, trace_at);   // the first stage of the matrix is in shared memory
+    const int end = min(NU, i0 + c.p->ups);
+    const uint8_t* sb = c.stage(slot);
+    if (ok && active) {
+      while (idx < end) {
+        if (u != cur_u) {   // K > 2048: several units per warp, the activations of the next one come from xin
+          if (g == 0) {
+            const uint4* xp = reinterpret_cast<const uint4*>(c.xin()) + 16 * u + 4 * t;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xv[j] = xp[j];
+          }
+          xs = c.xsum()[u];
+          cur_u = u;
+        }
+        const uint8_t* tu = sb + (size_t)(idx - i0) * kTileUnitBytes;
+        const uint4 wa = *reinterpret_cast<const uint4*>(tu + 16 * lane);
+        const uint4 wb = *reinterpret_cast<const uint4*>(tu + 512 + 16 * lane);
+        const uint32_t A[4] = {wa.x, wa.y, wa.z, wa.w}, B[4] = {wb.x, wb.y, wb.z, wb.w};
+        float cl[4], ch[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t a8 = A[j] >> 8, b8 = B[j] >> 8;
+          // word j = columns 8 j .. 8 j + 7 of this lane's 32: (e0 e1) and (e4 e5) under the low mask, (e2 e3) and
+          // (e6 e7) under the high mask; xv[j] = (x0 x1, x2 x3, x4 x5, x6 x7)
+          if (j == 0) {
+            mma16816_zero(cl, A[j] & 0x000F000Fu, B[j] & 0x000F000Fu, a8 & 0x000F000Fu, b8 & 0x000F000Fu, xv[j].x,
+                          xv[j].z);
+            mma16816_zero(ch, A[j] & 0x00F000F0u, B[j] & 0x00F000F0u, a8 & 0x00F000F0u, b8 & 0x00F000F0u, xv[j].y,
+                          xv[j].w);
+          } else {
+            mma16816_acc(cl, A[j] & 0x000F000Fu, B[j] & 0x000F000Fu, a8 & 0x000F000Fu, b8 & 0x000F000Fu, xv[j].x,
+                         xv[j].z);
+            mma16816_acc(ch, A[j] & 0x00F000F0u, B[j] & 0x00F000F0u, a8 & 0x00F000F0u, b8 & 0x00F000F0u, xv[j].y,
+                         xv[j].w);
+          }
+        }
+        if (t == 0) {   // column 0 of the product: c[0] = row slot g, c[2] = row slot g + 8
+          const float2 sa = __half22float2(*reinterpret_cast<const half2*>(tu + 1024 + 4 * g));
+          const float2 sc = __half22float2(*reinterpret_cast<const half2*>(tu + 1024 + 4 * (g + 8)));
+          ya = fmaf(sa.x, fmaf(cl[0], 16777216.f, fmaf(ch[0], 1048576.f, -sa.y * xs)), ya);
+          yb = fmaf(sc.x, fmaf(cl[2], 16777216.f, fmaf(ch[2], 1048576.f, -sc.y * xs)), yb);
+        }
+        u += kNCW;
+        if (u >= nunit) {
+          if (t == 0) {
+            part[warp * pstride + 16 * tl + g] = ya;
+            part[warp * pstride + 16 * tl + g + 8] = yb;
+          }
+          ya = yb = 0.f;
+          ++tl;
+          u = warp;
+          idx = tl * nunit + warp;
+        } else {
+          idx += kNCW;
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(c.empty(slot));
+  }
 }
 
 enum : int { OUT_TAGGED = 0, OUT_SWIGLU = 1, OUT_LOGITS = 2 };
 
-// Consumer side of one matrix slice. A row is cut into segments of 32 chunks (1024 weights); every warp is bound to
-// ONE segment for the whole slice (warp w -> segment w mod segs) and lane l to chunk l of it, so the lane's 32
-// activations sit in registers and are loaded once per slice; the warps that share a segment split the units
-// (pairs of rows) round robin. Per unit a lane reads two 16-byte weight chunks and two (scale, zero) words, runs the
-// 72-instruction core, and the warp leaves two partial sums in shared memory (c.part). After one barrier per slice
-// thread i finishes unit i: it adds the segments in a fixed order (deterministic) and emits the output.
-// When a row has more than 16 segments (K > 16384) a warp owns several segments and reloads x between them.
+// After the barrier that follows gemv(): thread i adds the warps' partial sums of row slot i in a fixed order
+// (deterministic) and emits the output.
 //   OUT_TAGGED: E[row] <- tagged y.  OUT_SWIGLU: E[i] <- tagged half(silu(gate_i)) * up_i.
 //   OUT_LOGITS: logits[row] <- y, and `best` tracks this thread's maximum.
-DEVI void consume(const Cta& c, const Mat& m, const Slice& s, const WarpMap& wm_, int log2G, float resc, RingPos& rp,
-                  const int OUT, uint32_t* E, half* logits, unsigned long long& best, int tid) {
-  const int lane = tid & 31;
-  const int U = m.K >> 5, segs = wm_.segs;
-  const int sper = wm_.sper;     // segments per warp (1 unless K > 16384)
-  const int seg0 = wm_.seg0;     // first (usually only) segment of this warp
-  const int group = wm_.group;   // warps sharing seg0
-  const int rank = wm_.rank;     // this warp's place among them
-  XChunk x;
-  int u = 32 * seg0 + lane;
-  if (u < U) x = load_xchunk(c, u);
-  const int g = (u << 5) >> log2G;
-  int joff = 0;   // (index of the stage's first unit within the slice) mod group
-  for (int st = 0; st < s.nstages; ++st, advance(rp, c.ns)) {
-    const int slot = rp.slot;
-    const bool ok = wait_bar(c, &c.full[slot], rp.parity, ERR_FULL);
-    const int u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups), nu = u1 - u0;
-    const uint8_t* base = c.ring + (size_t)slot * c.stage_bytes;
-    const uint8_t* szbase = base + (size_t)((m.gu ? 2 * u1 : min(m.N, 2 * u1)) - 2 * u0) * s.rowbytes;
-    if (ok) {
-      const int ui0 = u0 - s.ub;   // index of the stage's first unit within the slice
-      if (sper == 1) {
-        // two units per trip: twice the independent work between dependent shuffles, one combined reduction
-        for (int j = rank - joff + (rank < joff ? group : 0); j < nu; j += 2 * group) {
-          const int j2 = j + group < nu ? j + group : j;   // second unit of the trip (repeats the first at the tail)
-          int sa0, sa1, sb0, sb1;
-          if (m.gu) { sa0 = j; sa1 = nu + j; sb0 = j2; sb1 = nu + j2; }
-          else {
-            sa0 = 2 * j; sa1 = 2 * (u0 + j) + 1 < m.N ? sa0 + 1 : sa0;
-            sb0 = 2 * j2; sb1 = 2 * (u0 + j2) + 1 < m.N ? sb0 + 1 : sb0;
-          }
-          float p0 = 0.f, p1 = 0.f, q0 = 0.f, q1 = 0.f;
-          if (u < U) {
-            const uint4 wa0 = reinterpret_cast<const uint4*>(base + (size_t)sa0 * s.rowbytes)[u];
-            const uint4 wa1 = reinterpret_cast<const uint4*>(base + (size_t)sa1 * s.rowbytes)[u];
-            const uint4 wb0 = reinterpret_cast<const uint4*>(base + (size_t)sb0 * s.rowbytes)[u];
-            const uint4 wb1 = reinterpret_cast<const uint4*>(base + (size_t)sb1 * s.rowbytes)[u];
-            const half2 za0 = reinterpret_cast<const half2*>(szbase + (size_t)sa0 * s.szrow)[g];
-            const half2 za1 = reinterpret_cast<const half2*>(szbase + (size_t)sa1 * s.szrow)[g];
-            const half2 zb0 = reinterpret_cast<const half2*>(szbase + (size_t)sb0 * s.szrow)[g];
-            const half2 zb1 = reinterpret_cast<const half2*>(szbase + (size_t)sb1 * s.szrow)[g];
-            chunk_two_rows(wa0, wa1, za0, za1, x, resc, p0, p1);
-            if (j2 != j) chunk_two_rows(wb0, wb1, zb0, zb1, x, resc, q0, q1);   // warp-uniform: no second unit at the tail
-          }
-          // 4 sums with 7 shuffles: quarter q of the warp ends up holding value q
-          const int qd = lane >> 3;
-          float v0 = (qd & 2) ? q0 : p0, v1 = (qd & 2) ? q1 : p1;          // this half-warp's pair
-          const float o0 = (qd & 2) ? p0 : q0, o1 = (qd & 2) ? p1 : q1;    // the other half-warp's pair
-          v0 += __shfl_xor_sync(0xffffffffu, o0, 16);
-          v1 += __shfl_xor_sync(0xffffffffu, o1, 16);
-          float v = (qd & 1) ? v1 : v0;
-          v += __shfl_xor_sync(0xffffffffu, (qd & 1) ? v0 : v1, 8);
-          v += __shfl_xor_sync(0xffffffffu, v, 4);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
-          v += __shfl_xor_sync(0xffffffffu, v, 1);
-          if ((lane & 7) == 0) {
-            const int jj = (qd & 2) ? j2 : j;
-            if (!(qd & 2) || j2 != j) c.part[((ui0 + jj) * 2 + (qd & 1)) * segs + seg0] = v;
-          }
-        }
-      } else {
-        for (int j = 0; j < nu; ++j) {
-          int slot0, slot1;
-          if (m.gu) { slot0 = j; slot1 = nu + j; }
-          else { slot0 = 2 * j; slot1 = 2 * (u0 + j) + 1 < m.N ? slot0 + 1 : slot0; }
-          const uint4* w0 = reinterpret_cast<const uint4*>(base + (size_t)slot0 * s.rowbytes);
-          const uint4* w1 = reinterpret_cast<const uint4*>(base + (size_t)slot1 * s.rowbytes);
-          const half2* z0 = reinterpret_cast<const half2*>(szbase + (size_t)slot0 * s.szrow);
-          const half2* z1 = reinterpret_cast<const half2*>(szbase + (size_t)slot1 * s.szrow);
-          for (int seg = seg0; seg < segs; seg += kNCW) {
-            const int uu = 32 * seg + lane;
-            float p0 = 0.f, p1 = 0.f;
-            if (uu < U) {
-              const XChunk xx = load_xchunk(c, uu);
-              const int gg = (uu << 5) >> log2G;
-              chunk_two_rows(w0[uu], w1[uu], z0[gg], z1[gg], xx, resc, p0, p1);
-            }
-            const float v = reduce_pair(p0, p1, lane);
-            if ((lane & 15) == 0) c.part[((ui0 + j) * 2 + (lane >> 4)) * segs + seg] = v;
-          }
-        }
-      }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&c.empty[slot]);
-    joff += wm_.upsmod;
-    if (joff >= group) joff -= group;
-  }
-  consumer_sync();
-  for (int i = tid; i < s.ue - s.ub; i += kNT) {
-    float y0 = 0.f, y1 = 0.f;
-    for (int k = 0; k < segs; ++k) { y0 += c.part[(2 * i) * segs + k]; y1 += c.part[(2 * i + 1) * segs + k]; }
-    const half h0 = __float2half(y0), h1 = __float2half(y1);
-    const int unit = s.ub + i;
-    if (OUT == OUT_SWIGLU) {
+DEVI void reduce_emit(const Cta& c, const Mat& m, const Slice& s, const float* part, int pstride, const int OUT,
+                      uint32_t* E, half* logits, unsigned long long& best, int tid) {
+  const int nwa = min(kNCW, m.K >> 7);
+  if (OUT == OUT_SWIGLU) {
+    for (int i = tid; i < 8 * s.nt; i += kNT) {
+      const int slot = 16 * (i >> 3) + (i & 7), o = 8 * s.t0 + i;
+      if (o >= m.N) continue;
+      float ga = 0.f, up = 0.f;
+      for (int k = 0; k < nwa; ++k) { ga += part[k * pstride + slot]; up += part[k * pstride + slot + 8]; }
+      const half h0 = __float2half(ga), h1 = __float2half(up);
       const float gf = __half2float(h0);
       const half sl = __float2half(__fdividef(gf, 1.f + __expf(-gf)));
-      st_tagged(E + unit, c.tagw | (uint32_t)__half_as_ushort(__hmul(sl, h1)));
+      st_tagged(E + o, c.tagw | (uint32_t)__half_as_ushort(__hmul(sl, h1)));
+    }
+    return;
+  }
+  for (int i = tid; i < 16 * s.nt; i += kNT) {
+    const int row = 16 * s.t0 + i;
+    if (row >= m.N) continue;
+    float y = 0.f;
+    for (int k = 0; k < nwa; ++k) y += part[k * pstride + i];
+    const half h = __float2half(y);
+    if (OUT == OUT_TAGGED) {
+      st_tagged(E + row, c.tagw | (uint32_t)__half_as_ushort(h));
     } else {
-      const int row0 = 2 * unit, row1 = row0 + 1;
-      if (OUT == OUT_TAGGED) {
-        if (row1 < m.N) st_tagged2(E + row0, c.tagw | (uint32_t)__half_as_ushort(h0),
-                                   c.tagw | (uint32_t)__half_as_ushort(h1));
-        else st_tagged(E + row0, c.tagw | (uint32_t)__half_as_ushort(h0));
-      } else {
-        logits[row0] = h0;
-        if (!__hisnan(h0)) { const unsigned long long key = argmax_key(h0, row0); best = key > best ? key : best; }
-        if (row1 < m.N) {
-          logits[row1] = h1;
-          if (!__hisnan(h1)) { const unsigned long long key = argmax_key(h1, row1); best = key > best ? key : best; }
-        }
-      }
+      logits[row] = h;
+      if (!__hisnan(h)) { const unsigned long long key = argmax_key(h, row); best = key > best ? key : best; }
     }
   }
 }
@@ -516,17 +523,18 @@ DEVI void consume(const Cta& c, const Mat& m, const Slice& s, const WarpMap& wm_
 // dims [c D/8, (c+1) D/8) of it; each warp keeps a private online-softmax state, merged once at the end.
 template <int D>
 DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly, const uint32_t* Eqkv, uint32_t* Eattn,
-                         int h, int pos, float cs, float sn, int page_new, RingPos& rp, int tid) {
+                         int h, int pos, RingPos& rp, int tid) {
   constexpr int D2 = D / 2, G4 = D / 4, DPL = D / 8;
   const int warp = tid >> 5, lane = tid & 31, ts = lane >> 3, ch = lane & 7;
   const int hpg = p.n_q / p.n_kv, kvh = h / hpg;
-  float* qf = c.att;                                         // [D] rotated q * 1/sqrt(D)
-  half* knew = reinterpret_cast<half*>(c.att + D);           // [D] rotated k of this step
+  float* qf = c.att();                                         // [D] rotated q * 1/sqrt(D)
+  half* knew = reinterpret_cast<half*>(c.att() + D);           // [D] rotated k of this step
   half* vnew = knew + D;                                     // [D]
   half* raw = vnew + D;                                      // [3 D] un-rotated q, k, v
-  float* wo = c.att + 4 * D;                                 // [kNCW][D] per-warp outputs
+  float* wo = c.att() + 4 * D;                                 // [kNCW][D] per-warp outputs
   float* wm = wo + kNCW * D;                                 // [kNCW] per-warp max
   float* wl = wm + kNCW;                                     // [kNCW] per-warp sum
+  const float* rope = wl + kNCW;                             // [D/2] cos, [D/2] sin, then the page of this step's token
   const int pmask = (1 << p.log2P) - 1;
 
   if (tid < 3 * G4) {
@@ -537,6 +545,8 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
   consumer_sync();
   if (tid < 2 * D) {
     const int slot_new = pos & pmask;
+    const int page_new = reinterpret_cast<const int*>(rope)[D];
+    const float cs = rope[tid % D2], sn = rope[D2 + tid % D2];
     const size_t row_new = ((((size_t)page_new * p.n_kv + kvh) << p.log2P) + slot_new) * D;
     if (tid < D) {
       const int i = tid % D2;
@@ -595,10 +605,10 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
 
   const int tps = kv_tokens_per_stage(p);
   const int nst = (pos + tps - 1) / tps;
-  for (int st = 0; st < nst; ++st, advance(rp, c.ns)) {
+  for (int st = 0; st < nst; ++st, advance(rp, c.p->ns)) {
     const int slot = rp.slot;
-    const bool ok = wait_bar(c, &c.full[slot], rp.parity, ERR_FULL);
-    const half* kbase = reinterpret_cast<const half*>(c.ring + (size_t)slot * c.stage_bytes);
+    const bool ok = wait_bar(c, c.full(slot), rp.parity, ERR_FULL);
+    const half* kbase = reinterpret_cast<const half*>(c.stage(slot));
     const half* vbase = kbase + (size_t)tps * D;
     const int nt = min(tps, pos - st * tps);
     if (ok) {
@@ -609,7 +619,7 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&c.empty[slot]);
+    if (lane == 0) mbar_arrive(c.empty(slot));
   }
   if (warp == 0) fold(knew + ch * DPL, vnew + ch * DPL, ts == 0);   // the token of this step
 
@@ -651,40 +661,26 @@ template <int D>
 __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_constant__ StepParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   Cta c;
-  c.full = reinterpret_cast<uint64_t*>(smem);
-  c.empty = c.full + kMaxStages;
-  c.abort = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
-  c.red = reinterpret_cast<float*>(smem + 2 * kMaxStages * 8 + 16);
-  c.resid = reinterpret_cast<half*>(smem + kHeaderBytes);
-  c.xin = reinterpret_cast<uint4*>(smem + kHeaderBytes + p.resid_bytes);
-  c.xsum = reinterpret_cast<float*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes);
-  c.att = reinterpret_cast<float*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes);
-  c.part = reinterpret_cast<float*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes + p.att_bytes);
+  c.smem = smem;
+  c.p = &p;
   // the per-layer pointer table, copied once from global memory: every phase starts from these pointers, and a
   // global load in front of each would put an L2 round trip on the critical path ~10 times per layer
-  StepLayer* lys = reinterpret_cast<StepLayer*>(smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes +
-                                                p.att_bytes + p.part_bytes);
-  c.ring = smem + kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes + p.att_bytes + p.part_bytes + p.table_bytes;
-  c.ctrl = p.ctrl;
-  c.ns = p.ns;
-  c.nopoll = p.debug & 1;
-  c.stage_bytes = p.stage_bytes;
+  StepLayer* lys = reinterpret_cast<StepLayer*>(smem + p.off_table);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x, ncta = gridDim.x;
 
   if (tid == 0) {
-    for (int i = 0; i < p.ns; ++i) { mbar_init(&c.full[i], 1); mbar_init(&c.empty[i], kNCW); }
-    *c.abort = 0;
+    for (int i = 0; i < p.ns; ++i) { mbar_init(c.full(i), 1); mbar_init(c.empty(i), kNCW); }
+    *c.abort() = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // The five matrix shapes of a step (qkv, o, gate|up, down, head) and this CTA's slice of each: computed once
-  // (they involve integer divisions) and kept in shared memory for producer and consumers.
+  const int n_qkv = (p.n_q + 2 * p.n_kv) * p.D, n_att = p.n_q * p.D;
+  // This CTA's tiles of the five matrix shapes of a step (qkv, o, gate|up, down, head): computed once (they involve
+  // integer divisions) and kept in shared memory for producer and consumers.
   Slice* sl = reinterpret_cast<Slice*>(smem + 512);
   if (tid < 5) {
-    const int n_qkv_ = (p.n_q + 2 * p.n_kv) * p.D, n_att_ = p.n_q * p.D;
-    const Mat shapes[5] = {{nullptr, n_qkv_, p.H, 0}, {nullptr, p.H, n_att_, 0}, {nullptr, p.I, p.H, 1},
-                           {nullptr, p.H, p.I, 0}, {nullptr, p.V, p.H, 0}};
-    sl[tid] = slice_of(shapes[tid], p.log2G, p.stage_w, blockIdx.x, gridDim.x);
+    const int rows[5] = {n_qkv, p.H, p.I, p.H, p.V};
+    sl[tid] = slice_of(rows[tid], tid == 2, cta, ncta);
   }
   {
     const uint4* src = reinterpret_cast<const uint4*>(p.layers);
@@ -696,71 +692,59 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   c.tagw = ((epoch % 65535u) + 1u) << 16;
   const int pos = p.pos[0];
   const int hpg = p.n_q / p.n_kv;
-
-  const int n_qkv = (p.n_q + 2 * p.n_kv) * p.D, n_att = p.n_q * p.D;
   const int per_layer = n_qkv + n_att + p.H + p.I + p.H;   // exchange words per layer
 
   if (warp == kNCW) {
     // ================= producer =================
     RingPos rp = {0, 1u, 0};   // parity 1: the first pass over a fresh `empty` barrier does not wait
-    for (int l = 0; l < p.L && !*c.abort; ++l) {
+    for (int l = 0; l < p.L && !*c.abort(); ++l) {
       const StepLayer& ly = lys[l];
       const Mat mats[4] = {{(const uint8_t*)ly.w[0], n_qkv, p.H, 0},
                            {(const uint8_t*)ly.w[1], p.H, n_att, 0},
                            {(const uint8_t*)ly.w[2], p.I, p.H, 1},
                            {(const uint8_t*)ly.w[3], p.H, p.I, 0}};
       produce(c, mats[0], sl[0], rp, lane);
-      for (int h = cta; h < p.n_q && !*c.abort; h += ncta) produce_kv(c, p, ly, h / hpg, pos, rp, lane);
+      for (int h = cta; h < p.n_q && !*c.abort(); h += ncta) produce_kv(c, p, ly, h / hpg, pos, rp, lane);
 #pragma unroll
       for (int k = 1; k < 4; ++k)
-        if (!*c.abort) produce(c, mats[k], sl[k], rp, lane);
+        if (!*c.abort()) produce(c, mats[k], sl[k], rp, lane);
     }
-    if (!*c.abort) {
+    if (!*c.abort()) {
       const Mat head = {(const uint8_t*)p.w_head, p.V, p.H, 0};
       produce(c, head, sl[4], rp, lane);
     }
     // Leave only when every copy issued has landed. On the normal path the consumers have waited on every full
     // barrier already; on abort, wait (bounded) for the full barriers of the stages still in the ring.
-    if (*c.abort) {
+    if (*c.abort()) {
       const int it = rp.count;
-      for (int k = max(0, it - c.ns); k < it; ++k) {
-        const int slot = k % c.ns;
+      for (int k = max(0, it - c.p->ns); k < it; ++k) {
+        const int slot = k % c.p->ns;
         for (int i = 0; i < kSpinLimit; ++i)
-          if (mbar_try_wait(&c.full[slot], (k / c.ns) & 1)) break;
+          if (mbar_try_wait(c.full(slot), (k / c.p->ns) & 1)) break;
       }
     }
     return;
   }
 
   // ================= consumers =================
-  long long* tr = p.trace ? p.trace + (size_t)cta * (16 + 16 * p.L) : nullptr;
-  int tri = 0;
-#define TRACE()                                              \
-  do {                                                       \
-    if (tr && tid == 0) {                                    \
-      long long t_;                                          \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
-      tr[tri++] = t_;                                        \
-    }                                                        \
-  } while (0)
-  TRACE();
+#ifdef B200_STEP_TRACE
+  // trace row of a CTA: kTraceHead slots (0 = start, 1 = keys exchanged, 2 = token written), then per layer
+  // kTracePerLayer: per phase {staged, first weights there, GEMV done, barrier passed, emitted}, then attention done;
+  // the LM head uses the slots of a layer L
+  c.tr = p.trace ? p.trace + (size_t)cta * (kTraceHead + kTracePerLayer * (p.L + 1)) : nullptr;
+#endif
+  stamp(c, 0);
   RingPos rp = {0, 0u, 0};
-  // per-warp work split for the three row lengths (hidden, heads x head_dim, intermediate), in shared memory so
-  // that picking one by phase does not cost registers
-  WarpMap* wmaps = reinterpret_cast<WarpMap*>(smem + 640) + 3 * warp;
-  if (lane < 3) wmaps[lane] = warp_map(lane == 0 ? p.H : (lane == 1 ? n_att : p.I), sl[lane == 0 ? 0 : (lane == 1 ? 1 : 3)].ups, warp);
-  __syncwarp();
   unsigned long long best = 0ull;
-  const half* emb_row = p.emb + (size_t)p.tok[0] * p.H;
-  // RoPE factors and the page of this step's token depend only on pos: fetch them now, off the critical path
-  float rope_c = 0.f, rope_s = 0.f;
-  int page_new = 0;
+  // RoPE factors and the page of this step's token depend only on pos: the attention CTAs fetch them now, off the
+  // critical path, into the attention scratch (first read two barriers into the first attention phase)
   if (cta < p.n_q) {
-    page_new = p.bt[pos >> p.log2P];
-    if (tid < p.D) {
-      rope_c = p.cos_t[(size_t)pos * (p.D >> 1) + tid % (p.D >> 1)];
-      rope_s = p.sin_t[(size_t)pos * (p.D >> 1) + tid % (p.D >> 1)];
+    float* rope = c.att() + 4 * p.D + kNCW * p.D + 2 * kNCW;
+    if (tid < (p.D >> 1)) {
+      rope[tid] = p.cos_t[(size_t)pos * (p.D >> 1) + tid];
+      rope[(p.D >> 1) + tid] = p.sin_t[(size_t)pos * (p.D >> 1) + tid];
     }
+    if (tid == 0) reinterpret_cast<int*>(rope)[p.D] = p.bt[pos >> p.log2P];
   }
   // One loop body serves every GEMV of the step (4 per layer, then the LM head as "phase 0 of layer L"): the kernel
   // keeps a single copy of the staging, GEMV and attention code, which keeps the loop inside the instruction cache.
@@ -796,23 +780,45 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
       m = Mat{(const uint8_t*)ly.w[3], p.H, p.I, 0};
       Eout = Edown;
     }
-    const float resc = stage_x(c, Ein, emb_row, nw, n_in, p.eps, tid);
-    TRACE();
-    consume(c, m, sl[is_head ? 4 : ph], wmaps[ph == 1 ? 1 : (ph == 3 ? 2 : 0)], p.log2G, resc, rp, out, Eout, p.logits,
-            best, tid);
+    const Slice s = sl[is_head ? 4 : ph];
+    // the layers alternate between two partial-sum buffers (a slow thread may still add up phase n while a fast warp
+    // writes phase n + 1); the head, last and largest, takes the whole area
+    const int pstride = is_head ? p.part_stride_head : p.part_stride;
+    float* part = c.part() + ((step & 1) && !is_head ? kNCW * p.part_stride : 0);
+    if (nw) {
+      const half* emb_row = nullptr;
+      if (step == 0) {
+        // A token id outside the embedding table (a caller's mistake) must not become an address: row 0 is read
+        // instead and the step reports it.
+        long long tok_in = p.tok[0];
+        if (tok_in < 0 || tok_in >= p.V) {
+          if (cta == 0 && tid == 0) atomicCAS(&p.ctrl->error, 0, ERR_TOKEN);
+          tok_in = 0;
+        }
+        emb_row = p.emb + (size_t)tok_in * p.H;
+      }
+      stage_norm(c, Ein, emb_row, nw, n_in, p.eps, warp, lane);
+    }
+    else if (s.nt > 0) stage_plain(c, Ein, n_in, warp, lane);
+    const int tr_at = kTraceHead + kTracePerLayer * l + kTracePerPhase * ph;
+    stamp(c, tr_at);
+    gemv(c, m, s, part, pstride, rp, warp, lane, tr_at + 1);
+    stamp(c, tr_at + 2);
+    if (consumer_sync_or(*c.abort())) return;
+    stamp(c, tr_at + 3);
+    reduce_emit(c, m, s, part, pstride, out, Eout, p.logits, best, tid);
+    stamp(c, tr_at + 4);
     if (is_head) break;
-    if (consumer_sync_or(*c.abort)) return;
-    TRACE();
     if (ph == 0) {
       for (int h = cta; h < p.n_q; h += ncta) {
-        attention_head<D>(c, p, ly, Eqkv, Eatt, h, pos, rope_c, rope_s, page_new, rp, tid);
-        if (consumer_sync_or(*c.abort)) return;
+        attention_head<D>(c, p, ly, Eqkv, Eatt, h, pos, rp, tid);
+        if (consumer_sync_or(*c.abort())) return;
       }
-      TRACE();
+      stamp(c, kTraceHead + kTracePerLayer * l + 4 * kTracePerPhase);
     }
   }
   // this CTA's candidate: max over its threads' keys
-  unsigned long long* keys = reinterpret_cast<unsigned long long*>(c.att);
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(c.att());
   {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -821,8 +827,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     }
   }
   if (lane == 0) keys[warp] = best;
-  if (consumer_sync_or(*c.abort)) return;
-  TRACE();
+  if (consumer_sync_or(*c.abort())) return;
+  stamp(c, 1);
   uint32_t* Earg = p.xchg + (size_t)p.L * per_layer;   // [ncta][4] words: idx low 16, idx high 16, value key, valid
   if (tid == 0) {
     unsigned long long b = 0ull;
@@ -850,36 +856,48 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     }
     if (lane == 0) keys[kNCW + warp] = b;
     consumer_sync();
-    if (tid == 0 && !*c.abort) {
+    if (tid == 0 && !*c.abort()) {
       for (int k = 0; k < kNCW; ++k) b = keys[kNCW + k] > b ? keys[kNCW + k] : b;
-      const long long t = (long long)(0x7FFFFFFF - (int)(b & 0xFFFFFFFFu));
+      // b == 0: no logit was comparable (all NaN). torch.argmax, which the reference uses, answers with a valid
+      // index in that case; token 0 is this kernel's answer.
+      const long long t = b ? (long long)(0x7FFFFFFF - (int)(b & 0xFFFFFFFFu)) : 0ll;
       p.tok[0] = t;
       if (p.history) p.history[pos] = t;
       p.pos[0] = pos + 1;
       p.ctrl->epoch = epoch;
-      TRACE();
+      stamp(c, 2);
     }
   }
-#undef TRACE
 }
 
-size_t decode_step_smem_fixed(const StepParams& p) {
-  return (size_t)kHeaderBytes + p.resid_bytes + p.xin_bytes + p.xsum_bytes + p.att_bytes + p.part_bytes + p.table_bytes;
+// Lays the fixed areas out behind the header (sizes in, offsets out); returns where the ring starts.
+size_t decode_step_plan_smem(StepParams& p, int resid_bytes, int xin_bytes, int xsum_bytes, int att_bytes,
+                             int part_bytes, int table_bytes) {
+  p.off_xin = kHeaderBytes + resid_bytes;
+  p.off_xsum = p.off_xin + xin_bytes;
+  p.off_att = p.off_xsum + xsum_bytes;
+  p.off_part = p.off_att + att_bytes;
+  p.off_table = p.off_part + part_bytes;
+  p.off_ring = p.off_table + table_bytes;
+  return (size_t)p.off_ring;
 }
 int decode_step_threads() { return kThreads; }
 int decode_step_max_stages() { return kMaxStages; }
 int decode_step_consumer_warps() { return kNCW; }
+int decode_step_max_kv_tokens() { return kMaxKvTokens; }
 
 cudaError_t decode_step_launch(const StepParams& p, int grid, size_t smem, cudaStream_t st) {
-  static int configured_for = -1;
+  // the shared-memory limit of a kernel is a per-device attribute
+  static bool configured[64] = {};
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (configured_for != dev) {
-    cudaError_t e = cudaFuncSetAttribute(decode_step_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    e = cudaFuncSetAttribute(decode_step_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(decode_step_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
-    configured_for = dev;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -893,45 +911,6 @@ cudaError_t decode_step_launch(const StepParams& p, int grid, size_t smem, cudaS
   cfg.numAttrs = 1;
   return p.D == 64 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<64>, p)
                    : cudaLaunchKernelEx(&cfg, decode_step_kernel<128>, p);
-}
-
-// ---- stream layout ----------------------------------------------------------------------------------------------------
-// Rearranges one matrix (packed rows + scale/zero rows, the format of the quantizer) into the order the step kernel's
-// producers read it: the slice of CTA 0 first, then CTA 1, ...; inside a slice one block per ring stage, made of the
-// stage's packed rows followed by the same rows' (scale, zero) entries (gate|up: gate rows, up rows, gate sz, up sz).
-// Every row contributes K/2 + 4 K/G bytes wherever it lands, so a stage's block starts at
-// (index of its first row in slice order) * (K/2 + 4 K/G). One block per source row, one thread per 16-byte piece.
-__global__ void repack_stream_kernel(const uint8_t* __restrict__ W, const uint8_t* __restrict__ SZ,
-                                     uint8_t* __restrict__ out, int N, int K, int log2G, int gu, int ncta, int stage_w) {
-  const int rb = K >> 1, sb = (K >> log2G) << 2, pieces = (rb + sb) >> 4;
-  const int r = blockIdx.x;   // source row
-  const Mat m = {nullptr, gu ? N / 2 : N, K, gu};
-  const int units = gu ? m.N : (m.N + 1) >> 1;
-  const int u = gu ? (r < m.N ? r : r - m.N) : r >> 1;
-  const int base = units / ncta, rem = units % ncta, bnd = rem * (base + 1);
-  const int cta = u < bnd ? u / (base + 1) : rem + (u - bnd) / max(base, 1);
-  const Slice s = slice_of(m, log2G, stage_w, cta, ncta);
-  const int st = (u - s.ub) / s.ups, u0 = s.ub + st * s.ups, u1 = min(s.ue, u0 + s.ups);
-  const size_t rowall = (size_t)rb + sb;
-  int slot, nrows;
-  if (gu) { nrows = 2 * (u1 - u0); slot = (r < m.N ? 0 : u1 - u0) + (u - u0); }
-  else { nrows = min(m.N, 2 * u1) - 2 * u0; slot = r - 2 * u0; }
-  uint8_t* blk = out + (size_t)(2 * u0) * rowall;
-  for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
-    const int off = i << 4;
-    if (off < rb)
-      *reinterpret_cast<uint4*>(blk + (size_t)slot * rb + off) = *reinterpret_cast<const uint4*>(W + (size_t)r * rb + off);
-    else
-      *reinterpret_cast<uint4*>(blk + (size_t)nrows * rb + (size_t)slot * sb + (off - rb)) =
-          *reinterpret_cast<const uint4*>(SZ + (size_t)r * sb + (off - rb));
-  }
-}
-
-cudaError_t repack_stream_dispatch(const void* W, const void* SZ, void* out, int N, int K, int log2G, int gu, int ncta,
-                                   int stage_w, cudaStream_t st) {
-  repack_stream_kernel<<<N, 128, 0, st>>>((const uint8_t*)W, (const uint8_t*)SZ, (uint8_t*)out, N, K, log2G, gu, ncta,
-                                          stage_w);
-  return cudaPeekAtLastError();
 }
 
 }  // namespace b200

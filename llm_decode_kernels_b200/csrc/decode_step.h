@@ -9,8 +9,8 @@ namespace b200 {
 // One decoder layer; an array of these lives in DEVICE memory. Matrix order: 0 qkv, 1 o, 2 gate|up, 3 down.
 // Bit-compatible with b200_step_layer of include/b200decode.h.
 struct StepLayer {
-  const void* w[4];    // packed int4 [N, K/8] int32
-  const void* sz[4];   // (scale, zero) half2 [N, K/G]
+  const void* w[4];    // the matrix in tile layout (gemv_tile_repack_kernel); gate|up in its paired form
+  const void* sz[4];   // unused: the tile layout carries (scale, zero)
   const half* ln1;
   const half* ln2;
   half* kc;            // [pages, n_kv, P, D]
@@ -42,16 +42,22 @@ struct StepParams {
   half* logits;
   uint32_t* xchg;
   StepCtrl* ctrl;
-  long long* trace;   // optional [grid][16 + 16 L] phase timestamps (ns)
-  int debug;          // bit 0: do not wait for exchange tags (results are garbage; for timing experiments)
-  // shared-memory plan, computed on the host
-  int resid_bytes, xin_bytes, xsum_bytes, att_bytes, part_bytes, table_bytes, stage_w, stage_bytes, ns;
+  long long* trace;   // [grid][8 + 21 (L + 1)] phase timestamps (ns); read only by builds with -DB200_STEP_TRACE
+  // shared-memory plan, computed on the host: byte offsets of the areas behind the header and the residual stream
+  int off_xin, off_xsum, off_att, off_part, off_table, off_ring;
+  int ups;               // tile-unit blocks (kTileUnitBytes each) per ring stage
+  int stage_w;           // bytes of a stage that carry data (= ups * kTileUnitBytes)
+  int stage_bytes, ns;   // stage pitch and number of stages of the ring
+  int part_stride;       // row slots per warp in a partial-sum buffer of the layer phases (two buffers)
+  int part_stride_head;  // the same for the LM head (one buffer over the same area)
 };
 
-size_t decode_step_smem_fixed(const StepParams& p);
+size_t decode_step_plan_smem(StepParams& p, int resid_bytes, int xin_bytes, int xsum_bytes, int att_bytes,
+                             int part_bytes, int table_bytes);
 int decode_step_threads();
 int decode_step_max_stages();
 int decode_step_consumer_warps();
+int decode_step_max_kv_tokens();
 cudaError_t decode_step_launch(const StepParams& p, int grid, size_t smem, cudaStream_t st);
 
 }  // namespace b200

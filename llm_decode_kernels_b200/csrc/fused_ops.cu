@@ -4,17 +4,8 @@
 // data held in registers between its phases.
 #include "common.cuh"
 #include <math_constants.h>
-#include <stdlib.h>
 
 namespace b200 {
-
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("B200_PDL");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
 
 // ---- residual add + RMSNorm -----------------------------------------------------------------------------
 // Replaces add_rmsnorm_launch (reference kernels/fused_norm.cu:56-58). Rounding as in HF LlamaRMSNorm
@@ -152,18 +143,22 @@ cudaError_t rope_append_dispatch(void* qkv, const float* cos_t, const float* sin
 
 // ---- embedding row fetch: x[H] = emb[tok[0], :] (tok is int64 on the device) ------------------------------
 // Stands in for the torch.index_select of the reference's step (runtime/model.py:218).
+// A token id outside [0, V) must not become an address (the id comes from device memory: a caller's mistake or a
+// corrupted step would otherwise read far outside the table); row 0 is copied instead.
 __global__ void embed_row_kernel(const uint4* __restrict__ emb, const long long* __restrict__ tok,
-                                 uint4* __restrict__ x, int nchunk) {
+                                 uint4* __restrict__ x, int nchunk, int V) {
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < nchunk) x[i] = emb[(size_t)tok[0] * nchunk + i];
+  long long t = tok[0];
+  if (t < 0 || t >= V) t = 0;
+  if (i < nchunk) x[i] = emb[(size_t)t * nchunk + i];
 }
 
-cudaError_t embed_row_dispatch(const void* emb, const long long* tok, void* x, int H, cudaStream_t st) {
+cudaError_t embed_row_dispatch(const void* emb, const long long* tok, void* x, int H, int V, cudaStream_t st) {
   const int nchunk = H >> 3;
   B200_LAUNCH(embed_row_kernel, dim3((nchunk + 255) / 256), dim3(256), 0, st, (const uint4*)emb, tok, (uint4*)x,
-              nchunk);
+              nchunk, V);
   return cudaPeekAtLastError();
 }
 
@@ -216,7 +211,9 @@ argmax_kernel(const half* __restrict__ logits, int V, long long* __restrict__ to
       best = other > best ? other : best;
     }
     if (threadIdx.x == 0) {
-      const long long t = (long long)(0x7FFFFFFF - (int)(best & 0xFFFFFFFFu));
+      // best == 0: no comparable logit (all NaN). torch.argmax, which the reference uses, still answers with a valid
+      // index; token 0 is this kernel's answer, so the next step's embedding read stays inside the table.
+      const long long t = best ? (long long)(0x7FFFFFFF - (int)(best & 0xFFFFFFFFu)) : 0ll;
       tok[0] = t;
       if (pos) {
         const int p = pos[0];

@@ -23,7 +23,6 @@
 // not to each weight; `dequant_w4a16` below materialises the per-element weights for the bit-exact
 // check of the format.
 #include "common.cuh"
-#include <stdlib.h>
 
 namespace b200 {
 
@@ -315,12 +314,9 @@ static cudaError_t launch_seg(const void* Wp, const void* SZ, const void* x, voi
   tile = tile < 8 ? 8 : (tile > 512 ? 512 : tile);          // ... but at least 16 rows
   const int blocks = (units + tile - 1) / tile;
   const size_t smem = (size_t)K * 2 + (size_t)U * 4 + (size_t)tile * 2 * segs * 4;
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_seg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = smem;
-  }
+  static size_t allowed[kMaxDevices] = {};
+  const cudaError_t e = allow_dynamic_smem(gemv_w4a16_seg_kernel, smem, allowed);
+  if (e != cudaSuccess) return e;
   return launch_pdl(gemv_w4a16_seg_kernel, dim3(blocks), dim3(kSegThreads), smem, st, (const uint4*)Wp, (const half2*)SZ,
                     (const uint2*)x, (half*)y, N, K, log2G, tile);
 }
@@ -345,19 +341,6 @@ static cudaError_t launch_seg(const void* Wp, const void* SZ, const void* x, voi
 // barrier in the loop. Needs K % 128 == 0 and a group size that is a multiple of 128.
 constexpr int kMmaGemvWarps = 8, kMmaGemvThreads = kMmaGemvWarps * 32;
 
-DEVI void mma16816_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// D = A * B (no accumulator input: the first MMA of a unit starts from zero without clearing registers)
-DEVI void mma16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-               : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-}
-
 // A batch = 4 consecutive 128-weight units of two rows and their (scale, zero). A lane's four 16-byte loads per row
 // are 64 bytes apart, so the warp's loads of a batch cover 256 contiguous bytes of each of its 16 rows, issued back to
 // back (row-buffer locality in DRAM), and 8 loads per lane are in flight per batch.
@@ -372,7 +355,6 @@ struct MmaBatchRegs { uint4 wa[kMmaBatch], wb[kMmaBatch]; half2 sa[kMmaBatch], s
 // the order the warp consumes them: per 128-weight unit 512 bytes for rows g (lane l at 16 l), 512 bytes for rows
 // g + 8, then the 16 rows' (scale, zero) - 1088 bytes, units and tiles back to back - so every warp load is one
 // contiguous 512-byte read and a warp streams through memory in address order.
-constexpr int kTileUnitBytes = 1088;
 
 //
 // SWIGLU = true (tile layout only): the matrix is [gate; up] and the repack has put gate row i and up row i into the
@@ -609,6 +591,28 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
   }
 }
 
+// Launch shapes found by measurement (llm_decode_kernels_b200/autotune.py) override the heuristic of launch_mma for
+// the matrix shapes they name. A small host-side table, filled at set-up time (not thread-safe against launches).
+struct MmaTune { int mode, N, K, ksplit, blocks; };
+constexpr int kMaxTunes = 128;
+static MmaTune g_tunes[kMaxTunes];
+static int g_ntunes = 0;
+
+// ksplit in {1, 2, 4, 8}; blocks > 0. ksplit == 0 removes the entry. Returns false when the table is full.
+bool gemv_mma_tune(int mode, int N, int K, int ksplit, int blocks) {
+  for (int i = 0; i < g_ntunes; ++i) {
+    if (g_tunes[i].mode == mode && g_tunes[i].N == N && g_tunes[i].K == K) {
+      if (ksplit == 0) g_tunes[i] = g_tunes[--g_ntunes];
+      else { g_tunes[i].ksplit = ksplit; g_tunes[i].blocks = blocks; }
+      return true;
+    }
+  }
+  if (ksplit == 0) return true;
+  if (g_ntunes == kMaxTunes) return false;
+  g_tunes[g_ntunes++] = MmaTune{mode, N, K, ksplit, blocks};
+  return true;
+}
+
 // mode 0: row-major tensors; 1: tile layout; 2: tile layout of a [gate; up] matrix with the SwiGLU epilogue (N outputs)
 static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const void* x, void* y, int N, int K,
                               int log2G, cudaStream_t st, const NormArgs* norm = nullptr) {
@@ -620,36 +624,43 @@ static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const vo
   const int max_blocks = 2 * kNumSMs, want_warps = (kNumSMs * 16 * 4) / 5;
   int ksplit = 1;
   while (ksplit < kMmaGemvWarps && ntiles * ksplit < want_warps && nunit / (2 * ksplit) >= 2) ksplit *= 2;
+  int want_blocks = max_blocks;
+  for (int i = 0; i < g_ntunes; ++i) {
+    if (g_tunes[i].mode == mode && g_tunes[i].N == N && g_tunes[i].K == K && g_tunes[i].ksplit <= nunit) {
+      ksplit = g_tunes[i].ksplit;
+      want_blocks = g_tunes[i].blocks;
+      break;
+    }
+  }
   const int tpr = kMmaGemvWarps / ksplit;
   const int groups = (ntiles + tpr - 1) / tpr;
-  const int blocks = groups < max_blocks ? groups : max_blocks;
+  const int blocks = groups < want_blocks ? groups : want_blocks;
   const int rounds = (groups + blocks - 1) / blocks;
   const size_t smem = (size_t)K * 2 + (size_t)nunit * 4 + kMmaGemvWarps * 16 * 4 + 64;
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t e = cudaSuccess;
-    void (*all[])(const uint4*, const half2*, const uint2*, half*, int, int, int, int, int, const NormArgs) = {
-        gemv_w4a16_mma_kernel<false, false, false>, gemv_w4a16_mma_kernel<true, false, false>,
-        gemv_w4a16_mma_kernel<true, true, false>, gemv_w4a16_mma_kernel<true, false, true>,
-        gemv_w4a16_mma_kernel<true, true, true>};
-    for (auto k : all)
-      if (e == cudaSuccess) e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    static size_t allowed[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    configured = smem;
+    const bool tracked = dev >= 0 && dev < kMaxDevices;
+    if (smem > 48 * 1024 && !(tracked && smem <= allowed[dev])) {   // all variants share one per-device record
+      void (*all[])(const uint4*, const half2*, const uint2*, half*, int, int, int, int, int, const NormArgs) = {
+          gemv_w4a16_mma_kernel<false, false, false>, gemv_w4a16_mma_kernel<true, false, false>,
+          gemv_w4a16_mma_kernel<true, true, false>, gemv_w4a16_mma_kernel<true, false, true>,
+          gemv_w4a16_mma_kernel<true, true, true>};
+      for (auto k : all)
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (tracked) allowed[dev] = smem;
+    }
   }
   const NormArgs na = norm ? *norm : NormArgs{nullptr, nullptr, nullptr, 0.f};
   auto kern = mode == 0 ? gemv_w4a16_mma_kernel<false, false, false>
               : norm    ? (mode == 2 ? gemv_w4a16_mma_kernel<true, true, true> : gemv_w4a16_mma_kernel<true, false, true>)
                         : (mode == 2 ? gemv_w4a16_mma_kernel<true, true, false> : gemv_w4a16_mma_kernel<true, false, false>);
-  // Dependent launch pays for the small matrices of a step (TinyLlama shape, all GEMVs: 764 instead of 846 us per
-  // token) and costs on large ones. 70B shape cut to 16 layers on one GPU (matrices of 33, 44, 125 and 250 MB), us per
-  // token with dependent launch up to 24 / 40 / 64 / 140 MB / always: 2158 / 2130 / 2129 / 2220 / 2556; the full
-  // shape on two GPUs, 24 against 64 MB on the same machine, twice: 7.83, 7.96 against 7.74, 7.73 ms per token. The
-  // cut-off is 64 MB; the environment variable B200_PDL_MAX_MB moves it for A/B runs.
-  static const size_t pdl_max_mb = [] {
-    const char* e = getenv("B200_PDL_MAX_MB");
-    return e ? (size_t)atoi(e) : (size_t)64;
-  }();
+  // Dependent launch pays for the small matrices of a step and costs on large ones (the kernel then runs slower than
+  // with an ordinary launch): matrices beyond 64 MB are launched the ordinary way.
+  constexpr size_t pdl_max_mb = 64;
   const size_t weight_bytes = (size_t)(mode == 2 ? 2 * N : N) * K / 2;
   if (weight_bytes > (pdl_max_mb << 20)) {
     kern<<<blocks, kMmaGemvThreads, smem, st>>>((const uint4*)Wp, (const half2*)SZ, (const uint2*)x, (half*)y, N, K,

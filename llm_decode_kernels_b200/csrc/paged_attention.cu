@@ -1011,6 +1011,10 @@ constexpr int kMaxDevices = 64;
 float* g_attn_scratch_ptr[kMaxDevices] = {};   // device address of the array, per device, filled on first use
 }  // namespace
 
+namespace b200 {
+void record_cuda_error(cudaError_t e);   // c_api.cu: what b200_last_cuda_error() reports
+}
+
 extern "C" int b200_paged_attention_noalloc(const void* q, const void* kc, const void* vc, const int* bt, const int* pos,
                                             int n_q, int n_kv, int D, int log2P, int PS, int max_splits, void* out,
                                             void* stream) {
@@ -1023,19 +1027,29 @@ extern "C" int b200_paged_attention_noalloc(const void* q, const void* kc, const
   if (n_q > kNoAllocMaxHeads || max_splits > kNoAllocMaxSplits || D > kNoAllocMaxD) return B200_ERR_LIMIT;
   if ((reinterpret_cast<uintptr_t>(kc) & 15u) || (reinterpret_cast<uintptr_t>(vc) & 15u)) return B200_ERR_ALIGN;
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_ERR_LAUNCH;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    b200::record_cuda_error(e);
+    return B200_ERR_LAUNCH;
+  }
+  if (dev < 0 || dev >= kMaxDevices) return B200_ERR_LIMIT;
   if (!g_attn_scratch_ptr[dev]) {
     // In host code `g_attn_scratch` is only a handle for the symbol, not a device address: ask the runtime for the
     // address on the current device, once per device.
     float* p = nullptr;
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_scratch) != cudaSuccess || !p) return B200_ERR_LAUNCH;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_scratch);
+    if (e != cudaSuccess || !p) {
+      b200::record_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+      return B200_ERR_LAUNCH;
+    }
     g_attn_scratch_ptr[dev] = p;
   }
   float* o_part = g_attn_scratch_ptr[dev];
   float* m_part = o_part + (size_t)n_q * max_splits * D;
   float* l_part = m_part + (size_t)n_q * max_splits;
-  const cudaError_t e = b200::paged_attention_dispatch(0, q, kc, vc, bt, 1 << 30, pos, 1, n_q, n_kv, D, log2P, PS,
-                                                       max_splits, o_part, m_part, l_part, out,
-                                                       reinterpret_cast<cudaStream_t>(stream));
-  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+  e = b200::paged_attention_dispatch(0, q, kc, vc, bt, 1 << 30, pos, 1, n_q, n_kv, D, log2P, PS, max_splits, o_part,
+                                     m_part, l_part, out, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) return B200_OK;
+  b200::record_cuda_error(e);
+  return B200_ERR_LAUNCH;
 }

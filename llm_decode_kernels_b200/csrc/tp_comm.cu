@@ -18,8 +18,9 @@
 // two buffers alternate (o_proj partials use one slot, down_proj partials another), so when a rank overwrites a slot
 // every peer has signalled a later step and is therefore done with the slot's previous contents.
 //
-// Every wait is bounded (about four seconds, enough for ranks that drift apart between host-driven steps). A wait
-// that runs out stores a code in the block's error word, and the kernel returns without touching the outputs.
+// Every wait is bounded (about four seconds by default, enough for ranks that drift apart between host-driven
+// steps; a caller may store a shorter bound in the block's header). A wait that runs out stores a code in the
+// block's error word, and the kernel returns without touching the outputs.
 #include "common.cuh"
 
 namespace b200 {
@@ -31,6 +32,7 @@ constexpr int kCommMaxRanks = 16;
 constexpr int kCommFlagsOff = 0;      // uint32 flags[16]: flags[j] = latest step rank j has announced to this rank
 constexpr int kCommCounterOff = 64;   // uint32: steps this rank has taken
 constexpr int kCommErrorOff = 68;     // uint32: 0, or the code of a wait that ran out
+constexpr int kCommLimitOff = 72;     // uint32: polls before a wait for a peer gives up; 0 = kCommSpinLimit
 constexpr int kCommThreads = 1024;
 constexpr int kCommSpinLimit = 1 << 22;
 
@@ -71,6 +73,8 @@ DEVI bool exchange_flags(const CommPeers& P, int rank, int W) {
   }
   __syncthreads();
   const uint32_t step = step_s;
+  const uint32_t set_limit = *reinterpret_cast<const uint32_t*>(base + kCommLimitOff);
+  const int limit = set_limit ? (int)set_limit : kCommSpinLimit;
   int failed = 0;
   if (tid < W && tid != rank) {
     __threadfence_system();   // the partial was written by the previous kernel of this stream; order it before the flag
@@ -78,7 +82,7 @@ DEVI bool exchange_flags(const CommPeers& P, int rank, int W) {
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(base + kCommFlagsOff) + tid;
     int i = 0;
     while ((int32_t)(ld_acquire_sys(mine) - step) < 0) {
-      if (++i > kCommSpinLimit) { failed = 1; break; }
+      if (++i > limit) { failed = 1; break; }
       if (i > 256) __nanosleep(500);   // peers normally answer within microseconds: poll hard first, then back off
     }
     if (failed) atomicExch(reinterpret_cast<uint32_t*>(base + kCommErrorOff), COMM_ERR_PEER_WAIT);
@@ -208,5 +212,6 @@ cudaError_t tp_allgather_dispatch(const void* const* peers, int rank, int W, siz
 int comm_header_bytes() { return kCommHeaderBytes; }
 int comm_max_ranks() { return kCommMaxRanks; }
 int comm_error_offset() { return kCommErrorOff; }
+int comm_limit_offset() { return kCommLimitOff; }
 
 }  // namespace b200

@@ -118,50 +118,63 @@ def run_ctx(a):
         Path(a.out).write_text(txt)
 
 
+def tp_record(rank, world, local, dist, layers=80, ctx=4096, tokens=128, tp_comm="p2p", gemv="tiled"):
+    """Build this rank's shard of the 70B-shape model, decode `tokens` tokens from a pre-filled context `ctx` and
+    return the record (a dict; identical on every rank up to the rank-local fields). `dist` is the initialised
+    torch.distributed module, or None for one GPU."""
+    dev = f"cuda:{local}"
+    c = config(LLAMA3_70B, num_hidden_layers=layers)
+    t0 = time.time()
+    cfg = DecodeConfig(group=128, max_ctx=ctx + tokens + 16, page=16, device=dev, seed=0, tp_rank=rank,
+                       tp_world=world, tp_comm=tp_comm, step_kernel="multi", tile_weights=gemv == "tiled",
+                       keep_packed=False, gemv_stage=(2, 16, 0, 0) if gemv == "segmented" else None)
+    m = Model(LazyRandomState(c, dev, 0), c, cfg)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    build_s = time.time() - t0
+    m.kv.normal_()
+    m.prepare(ctx + tokens + 8)
+    if dist is not None:
+        dist.barrier()
+    us = time_decode(m, ctx, tokens, dist=dist)
+    err = m.step_error()
+    nbytes = m.bytes_per_token(ctx + tokens // 2)      # what THIS rank streams per token
+    peak, kind = peak_hbm_gbs()
+    rec = {"metric": "batch-1 decode tok/s (W4A16), tensor-parallel", "value": round(1e6 / us, 2), "unit": "tok/s",
+           "n_gpus": world, "us_per_token": round(us, 1), "ms_per_token": round(us / 1e3, 3),
+           "us_per_layer": round(us / layers, 2),
+           "config": {"workload": f"llama-3-70b-shape W4A16 g128 RTN, {layers} layers, batch 1, context {ctx}, "
+                                  f"{tokens} greedy tokens", "tp": world, "comm": tp_comm if world > 1 else None,
+                      "gemv": gemv, "graph": m.graph is not None},
+           "bytes_per_token_per_gpu": nbytes, "floor_us_at_peak": round(nbytes / peak / 1e3, 1),
+           "frac_of_hbm_per_gpu": round(nbytes / us / 1e3 / peak, 4), "peak_hbm_gbs": peak, "peak_source": kind,
+           "exchanges_per_token": 2 * layers + 1 if world > 1 else 0, "build_s": round(build_s, 1),
+           "step_error": err, "scaling": "strong", "data": "synthetic"}
+    if m.comm is not None:
+        dist.barrier()
+        m.comm.close()
+    del m
+    torch.cuda.empty_cache()
+    return rec
+
+
 def run_tp(a):
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
-    dev = f"cuda:{local}"
     dist = None
     if world > 1:
         import datetime
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device(dev), timeout=datetime.timedelta(seconds=600))
-    c = config(LLAMA3_70B, num_hidden_layers=a.layers)
-    t0 = time.time()
-    cfg = DecodeConfig(group=128, max_ctx=a.ctx + a.tokens + 16, page=16, device=dev, seed=0, tp_rank=rank,
-                       tp_world=world, tp_comm=a.tp_comm, step_kernel="multi", tile_weights=a.gemv == "tiled",
-                       gemv_stage=(2, 16, 0, 0) if a.gemv == "segmented" else None)
-    m = Model(LazyRandomState(c, dev, 0), c, cfg)
-    torch.cuda.empty_cache()
-    build_s = time.time() - t0
-    m.kv.normal_()
-    m.prepare(a.ctx + a.tokens + 8)
-    if dist is not None:
-        dist.barrier()
-    us = time_decode(m, a.ctx, a.tokens, dist=dist)
-    err = m.step_error()
-    nbytes = m.bytes_per_token(a.ctx + a.tokens // 2)      # what THIS rank streams per token
-    peak, kind = peak_hbm_gbs()
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"),
+                                timeout=datetime.timedelta(seconds=600))
+    line = tp_record(rank, world, local, dist, a.layers, a.ctx, a.tokens, a.tp_comm, a.gemv)
     if rank == 0:
-        line = {"metric": "batch-1 decode tok/s (W4A16), tensor-parallel", "value": round(1e6 / us, 2), "unit": "tok/s",
-                "n_gpus": world, "us_per_token": round(us, 1),
-                "config": {"workload": f"llama-3-70b-shape W4A16 g128 RTN, {a.layers} layers, batch 1, context "
-                                       f"{a.ctx}, {a.tokens} greedy tokens", "tp": world, "tp_comm": a.tp_comm,
-                           "gemv": a.gemv,
-                           "graph": m.graph is not None},
-                "bytes_per_token_per_gpu": nbytes, "floor_us_at_peak": round(nbytes / peak / 1e3, 1),
-                "frac_of_hbm_per_gpu": round(nbytes / us / 1e3 / peak, 4), "peak_hbm_gbs": peak, "peak_source": kind,
-                "exchanges_per_token": 2 * a.layers + 1 if world > 1 else 0, "build_s": round(build_s, 1),
-                "step_error": err, "data": "synthetic"}
         print(json.dumps(line), flush=True)
         if a.out:
             Path(a.out).write_text(json.dumps(line))
     if dist is not None:
         dist.barrier()
-        if m.comm is not None:
-            m.comm.close()
         dist.destroy_process_group()
 
 

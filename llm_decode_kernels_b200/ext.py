@@ -30,6 +30,7 @@ SIGNATURES = {
     "b200_gemv_w4a16_tiled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_gemv_w4a16_tiled_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_void_p],
+    "b200_gemv_w4a16_tune": [c_int, c_int, c_int, c_int, c_int],
     "b200_bw_read": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_bw_read_bulk": [c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_void_p],
     "b200_paged_attention": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -54,6 +55,7 @@ SIGNATURES = {
     "b200_comm_unimport": [c_void_p],
     "b200_comm_reset": [c_void_p],
     "b200_comm_error": [c_void_p, c_void_p],
+    "b200_comm_set_wait_limit": [c_void_p, ctypes.c_uint],
     "b200_tp_allreduce_add_rmsnorm": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_float,
                                       c_void_p],
     "b200_tp_allgather": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_int, c_void_p],
@@ -62,7 +64,7 @@ SIGNATURES = {
     "b200_rope_append_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_void_p],
     "b200_dequant_w4a16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "b200_embed_row": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "b200_embed_row": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "b200_argmax": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
@@ -82,26 +84,26 @@ class StepDesc(ctypes.Structure):
                 ("logits", c_void_p), ("xchg", c_void_p), ("ctrl", c_void_p), ("ctx_cap", c_int), ("grid", c_int), ("trace", c_void_p)]
 
 
-def load_library(build_if_missing=True):
-    """dlopen libb200decode.so (building it with nvcc first if it is absent) and declare its symbols."""
+def load_library(build_if_missing=True, path=None):
+    """dlopen libb200decode.so (building it with nvcc first if it is absent) and declare its symbols. `path` names
+    another build of the same library (step_trace.py's instrumented one); it must be given on the first call."""
     global _LIB
     if _LIB is not None:
+        if path is not None and Path(path).resolve() != Path(_LIB._name).resolve():
+            raise RuntimeError(f"{_LIB._name} is already loaded")
         return _LIB
-    if not LIB_PATH.exists():
+    if path is None and not LIB_PATH.exists():
         if not build_if_missing:
             raise RuntimeError(f"{LIB_PATH} is missing; run `python -m llm_decode_kernels_b200.build`")
         from . import build as _build
         _build.build()
-    lib = ctypes.CDLL(str(LIB_PATH))
+    lib = ctypes.CDLL(str(path or LIB_PATH))
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)          # AttributeError here = the library does not export a declared symbol
         fn.argtypes = argtypes
         fn.restype = c_int
     lib.b200_decode_step.argtypes = [ctypes.POINTER(StepDesc), c_void_p]
     lib.b200_decode_step.restype = c_int
-    lib.b200_decode_step_repack.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                            c_void_p]
-    lib.b200_decode_step_repack.restype = c_int
     lib.b200_gemv_w4a16_tiled_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemv_w4a16_tiled_bytes.restype = c_size_t
     lib.b200_decode_step_xchg_bytes.argtypes = [c_int] * 7
@@ -182,6 +184,21 @@ class Ops:
                                                          _ilog2_exact(int(group), "group"), int(gate_up), _stream()),
                     "gemv_tile_repack")
         return out
+
+    def gemv_tune(self, layout, N, K, ksplit, blocks):
+        """Launch shape of the tensor-core GEMV for matrices of N x K (b200_gemv_w4a16_tune); ksplit=0 forgets it."""
+        self._check(self.lib.b200_gemv_w4a16_tune(int(layout), int(N), int(K), int(ksplit), int(blocks)), "gemv_tune")
+
+    def load_gemv_tunes(self, path):
+        """Register every entry of an autotune file (written by llm_decode_kernels_b200.autotune). Returns how many."""
+        import json
+        from pathlib import Path as _P
+        if not _P(path).is_file():
+            return 0
+        rows = json.load(open(path)).get("gemv", [])
+        for r in rows:
+            self.gemv_tune(r["layout"], r["N"], r["K"], r["ksplit"], r["blocks"])
+        return len(rows)
 
     def gemv_w4a16_tiled(self, tiled, x, y, N, K, swiglu=False):
         """y[N] = W x from the tile-layout copy. swiglu: the copy is a paired [gate; up] and y[N] = silu(gate) * up."""
@@ -352,6 +369,10 @@ class Ops:
     def comm_reset(self, base):
         self._check(self.lib.b200_comm_reset(base), "comm_reset")
 
+    def comm_set_wait_limit(self, base, polls):
+        """Bound of the exchange kernels' waits for a peer, in polls (0 = default, about four seconds)."""
+        self._check(self.lib.b200_comm_set_wait_limit(base, int(polls)), "comm_set_wait_limit")
+
     def comm_error(self, base):
         code = ctypes.c_int(-1)
         self._check(self.lib.b200_comm_error(base, ctypes.byref(code)), "comm_error")
@@ -378,7 +399,19 @@ class Ops:
         for t, n in ((q, "q"), (kc, "kc"), (vc, "vc"), (out, "out")):
             _cuda(t, n, torch.float16)
         _cuda(bt, "bt", torch.int32), _cuda(pos, "pos", torch.int32)
-        D = kc.shape[3]
+        if kc.dim() != 4 or vc.shape != kc.shape:
+            raise RuntimeError("cache must be [pages, n_kv, P, D]")
+        D, n_kv = kc.shape[3], kc.shape[1]
+        if q.numel() % D or out.shape != q.shape:
+            raise RuntimeError("q must hold n_q * D values and out have q's shape")
+        n_q = q.numel() // D
+        if n_q % n_kv or n_q // n_kv not in (1, 2, 4, 8):
+            raise RuntimeError("heads-per-group must be 1/2/4/8")
+        if part_size <= 0 or max_splits <= 0 or pos.numel() != 1:
+            raise RuntimeError("part_size and max_splits must be > 0 and pos hold one position")
+        if bt.numel() * kc.shape[2] < min(part_size * max_splits, kc.shape[0] * kc.shape[2]):
+            raise RuntimeError("bt does not cover the pages of max_splits * part_size tokens")
+        _aligned16(kc, "kc"), _aligned16(vc, "vc")
         self._check(self.lib.b200_paged_attention_noalloc(
             q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), pos.data_ptr(), q.numel() // D, kc.shape[1], D,
             _ilog2_exact(kc.shape[2], "page size"), int(part_size), int(max_splits), out.data_ptr(), _stream()),
@@ -407,8 +440,10 @@ class Ops:
 
     def embed_row(self, emb, tok, x):
         _cuda(emb, "emb", torch.float16), _cuda(tok, "tok", torch.int64), _cuda(x, "x", torch.float16)
-        self._check(self.lib.b200_embed_row(emb.data_ptr(), tok.data_ptr(), x.data_ptr(), x.numel(), _stream()),
-                    "embed_row")
+        if emb.dim() != 2 or emb.shape[1] != x.numel():
+            raise RuntimeError("embed_row: emb must be [V, H] and x [H]")
+        self._check(self.lib.b200_embed_row(emb.data_ptr(), tok.data_ptr(), x.data_ptr(), x.numel(), emb.shape[0],
+                                            _stream()), "embed_row")
 
     def argmax(self, logits, tok, pos=None, history=None):
         """tok <- argmax(logits), lowest index on ties; with pos: history[pos] <- tok (if given), pos += 1."""
@@ -421,16 +456,6 @@ class Ops:
 
     def decode_step_xchg_bytes(self, L, H, I, n_q, n_kv, D, grid):
         return int(self.lib.b200_decode_step_xchg_bytes(L, H, I, n_q, n_kv, D, grid))
-
-    def decode_step_repack(self, packed, sz, group, gate_up, kmax, grid):
-        """Stream-layout copy of one quantized matrix for decode_step (b200_decode_step_repack). Returns uint8."""
-        _cuda(packed, "packed", torch.int32), _cuda(sz, "sz", torch.float16)
-        N, K = packed.shape[0], packed.shape[1] * 8
-        out = torch.empty(N * (K // 2 + 4 * (K // group)), dtype=torch.uint8, device=packed.device)
-        self._check(self.lib.b200_decode_step_repack(packed.data_ptr(), sz.data_ptr(), out.data_ptr(), N, K,
-                                                     _ilog2_exact(int(group), "group"), int(bool(gate_up)), int(kmax),
-                                                     int(grid), _stream()), "decode_step_repack")
-        return out
 
     def decode_step(self, desc: "StepDesc"):
         """One whole decode step as one persistent kernel (b200_decode_step) on the current stream."""

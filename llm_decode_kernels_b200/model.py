@@ -44,12 +44,14 @@ class DecodeConfig:
     attn_version: int = 0        # accepted for compatibility; the library has one attention kernel
     gemv_stage: tuple = None     # (stage, R, warps, pf) forced everywhere; None -> the library's shape-based choice
     fuse_rope_attention: bool = True   # RoPE + KV-append inside the attention kernel (b200_rope_paged_attention): one
-                                       # launch less per layer (TinyLlama shape, context 2048: 714 against 724 us per
-                                       # token)
+                                       # launch less per layer
     fuse_norm_gemv: bool = True  # residual add + RMSNorm inside the GEMV that consumes them (b200_gemv_w4a16_tiled_norm):
                                  # two launches less per layer; needs tile_weights, one GPU, no ablation switch
-    tile_weights: bool = True    # keep a second copy of every matrix in the tile layout of the tensor-core GEMV
-                                 # (b200_gemv_w4a16_tile_repack) and multiply from it; costs the weights' size again
+    tile_weights: bool = True    # hold every matrix in the tile layout of the tensor-core GEMV and of the persistent
+                                 # step (b200_gemv_w4a16_tile_repack) and multiply from it
+    keep_packed: bool = True     # False: once a matrix has its tile-layout copy, drop the quantizer's row-major
+                                 # packed / scale-zero tensors, which no kernel reads any more (halves the weight
+                                 # memory; Linear.packed and Linear.sz are then None)
     autotune_path: str = str(ROOT / "configs" / "autotune.json")
     attn_policy_path: str = str(ROOT / "configs" / "attn_policy.json")
     shuffle_pages: bool = True
@@ -91,6 +93,11 @@ class Linear:
         self.tiled = None            # tile-layout copy, made by Model when DecodeConfig.tile_weights is set
         self.paired = False          # the copy pairs gate row i with up row i (GEMV with SwiGLU epilogue)
 
+    def drop_packed(self):
+        """Free the row-major tensors once the tile-layout copy exists (DecodeConfig.keep_packed=False)."""
+        if self.tiled is not None:
+            self.packed = self.sz = None
+
 
 def _rope_theta(c):
     if getattr(c, "rope_theta", None) is not None:
@@ -130,9 +137,27 @@ class Model:
                                  if cfg.quant == "pre" else None)
         dev = cfg.device
         self.K = ext.load()
+        self.K.load_gemv_tunes(cfg.autotune_path)   # measured launch shapes of the GEMVs, if the table exists
         sd = hf_state
         g = lambda k: sd[k].to(dev).half()
         self.emb = g("model.embed_tokens.weight").contiguous()
+        if not cfg.keep_packed and "dequant" in cfg.ablate:
+            raise ValueError("the 'dequant' ablation reads the row-major tensors: keep_packed must stay True")
+        tile = cfg.tile_weights and cfg.gemv_stage is None
+        # gate|up is stored with gate row i next to up row i, so its GEMV can finish with SwiGLU (one launch less per
+        # layer) - unless that fusion, or the fused dequantization, is switched off for an ablation run
+        pair_gu = cfg.fused and not ({"swiglu", "dequant"} & set(cfg.ablate))
+
+        def finish(lin, gate_up=False):
+            """Tile-layout copy of a freshly quantized matrix (made layer by layer, so that with keep_packed=False
+            the row-major tensors of only one layer are alive at a time)."""
+            if tile:
+                lin.tiled = self.K.gemv_tile_repack(lin.packed, lin.sz, cfg.group, gate_up=gate_up and pair_gu)
+                lin.paired = gate_up and pair_gu and lin.tiled is not None
+                if not cfg.keep_packed:
+                    lin.drop_packed()
+            return lin
+
         self.layers = []
         for i in range(self.L):
             p = f"model.layers.{i}."
@@ -142,26 +167,16 @@ class Model:
             self.layers.append({
                 "ln1": g(p + "input_layernorm.weight").contiguous(),
                 "ln2": g(p + "post_attention_layernorm.weight").contiguous(),
-                "qkv": Linear(shard("qkv", wqkv), cfg, f"layers.{i}.qkv", pre=pre("qkv", f"layers.{i}.qkv")),
-                "o": Linear(shard("o", g(p + "self_attn.o_proj.weight")), cfg, f"layers.{i}.o",
-                            pre=pre("o", f"layers.{i}.o")),
-                "gu": Linear(shard("gu", wgu), cfg, f"layers.{i}.gu", pre=pre("gu", f"layers.{i}.gu")),
-                "down": Linear(shard("down", g(p + "mlp.down_proj.weight")), cfg, f"layers.{i}.down",
-                               pre=pre("down", f"layers.{i}.down"))})
+                "qkv": finish(Linear(shard("qkv", wqkv), cfg, f"layers.{i}.qkv", pre=pre("qkv", f"layers.{i}.qkv"))),
+                "o": finish(Linear(shard("o", g(p + "self_attn.o_proj.weight")), cfg, f"layers.{i}.o",
+                                   pre=pre("o", f"layers.{i}.o"))),
+                "gu": finish(Linear(shard("gu", wgu), cfg, f"layers.{i}.gu", pre=pre("gu", f"layers.{i}.gu")), True),
+                "down": finish(Linear(shard("down", g(p + "mlp.down_proj.weight")), cfg, f"layers.{i}.down",
+                                      pre=pre("down", f"layers.{i}.down")))})
             del wqkv, wgu
         self.norm_f = g("model.norm.weight").contiguous()
         lm = sd["lm_head.weight"] if "lm_head.weight" in sd else sd["model.embed_tokens.weight"]
-        self.lm_head = Linear(shard("lm_head", lm.to(dev).half()), cfg, "lm_head", pre=pre("lm_head", "lm_head"))
-
-        if cfg.tile_weights and cfg.gemv_stage is None:
-            # gate|up is stored with gate row i next to up row i, so its GEMV can finish with SwiGLU (one launch less
-            # per layer) - unless that fusion, or the fused dequantization, is switched off for an ablation run
-            pair = cfg.fused and not ({"swiglu", "dequant"} & set(cfg.ablate))
-            for lw in self.layers:
-                for n in ("qkv", "o", "gu", "down"):
-                    lw[n].tiled = self.K.gemv_tile_repack(lw[n].packed, lw[n].sz, cfg.group, gate_up=pair and n == "gu")
-                    lw[n].paired = pair and n == "gu" and lw[n].tiled is not None
-            self.lm_head.tiled = self.K.gemv_tile_repack(self.lm_head.packed, self.lm_head.sz, cfg.group)
+        self.lm_head = finish(Linear(shard("lm_head", lm.to(dev).half()), cfg, "lm_head", pre=pre("lm_head", "lm_head")))
 
         # paged KV cache [L, 2, pages, n_kv, P, D]; one block table shared by all layers (one sequence)
         self.n_pages = (cfg.max_ctx + cfg.page - 1) // cfg.page + 1
@@ -218,83 +233,87 @@ class Model:
         self.set_attention_partition(cfg.max_ctx)
 
     # ------------------------------------------------------------------ attention partitioning
-    def _policy(self):
-        p = Path(self.cfg.attn_policy_path)
-        return json.load(open(p)) if p.exists() else {}
+    def _policy_table(self):
+        """Rows of the attention policy file (DecodeConfig.attn_policy_path): [{"max_ctx": c, "part_size": p}, ...]
+        sorted by context, as kernel_bench writes them; empty when there is no file."""
+        path = Path(self.cfg.attn_policy_path)
+        if not path.is_file():
+            return []
+        with open(path) as f:
+            rows = json.load(f).get("policy", [])
+        return sorted((r for r in rows if r["max_ctx"] < (1 << 30)), key=lambda r: r["max_ctx"])
 
     def _policy_part_size(self, ctx_cap):
-        """Policy-table entry tuned at the largest context <= ctx_cap (reference runtime/model.py:164-172); with no
-        table, the smallest multiple of 32 tokens for which n_kv x splits still covers every SM about once."""
-        ents = [e for e in self._policy().get("policy", []) if e["max_ctx"] < (1 << 30)]
-        if ents:
-            below = [e for e in ents if e["max_ctx"] <= ctx_cap]
-            return (below[-1] if below else ents[0])["part_size"]
+        """Split size for contexts up to ctx_cap: the row of the policy table tuned at the largest context that does
+        not exceed ctx_cap (the first row for shorter contexts), which is how the reference picks it
+        (runtime/model.py:164-172). Without a table: the smallest multiple of 32 tokens, at least 64, for which
+        n_kv x splits still covers every SM about twice."""
+        rows = self._policy_table()
+        if rows:
+            fitting = [r for r in rows if r["max_ctx"] <= ctx_cap]
+            return int((fitting[-1] if fitting else rows[0])["part_size"])
         sms = torch.cuda.get_device_properties(self.cfg.device).multi_processor_count
-        want_splits = max(1, (2 * sms) // self.n_kv)
-        ps = 32 * max(1, math.ceil(ctx_cap / want_splits / 32))
-        return max(64, ps)
+        splits_wanted = max(1, (2 * sms) // self.n_kv)
+        return max(64, 32 * math.ceil(ctx_cap / splits_wanted / 32))
 
     def set_attention_partition(self, ctx_cap, part_size=None):
-        """Choose the split size for contexts up to ctx_cap and size the split scratch; the attention grid is fixed at
-        ceil(ctx_cap / part_size) splits and surplus ones exit (reference runtime/model.py:140-151)."""
-        ps = part_size or self.cfg.part_size or self._policy_part_size(ctx_cap)
-        self.part_size = ps
-        self.max_splits = max(1, math.ceil(ctx_cap / ps))
-        self.ctx_cap = self.max_splits * ps   # attention ignores tokens past this; run_step enforces it
-        f32 = dict(dtype=torch.float32, device=self.cfg.device)
-        self.o_part = torch.empty(self.n_q, self.max_splits, self.D, **f32)
-        self.m_part = torch.empty(self.n_q, self.max_splits, **f32)
-        self.l_part = torch.empty(self.n_q, self.max_splits, **f32)
-        self.graph = None
+        """Fix the split-K geometry of attention for contexts up to ctx_cap. The launch grid always has
+        ceil(ctx_cap / part_size) splits (a captured graph cannot change it; splits beyond the live context exit at
+        once), so the split scratch is sized for that many and the usable context is rounded up to whole splits."""
+        size = part_size or self.cfg.part_size or self._policy_part_size(ctx_cap)
+        n_splits = max(1, -(-ctx_cap // size))
+        self.part_size, self.max_splits, self.ctx_cap = size, n_splits, n_splits * size
+        dev = self.cfg.device
+        self.o_part = torch.empty(self.n_q, n_splits, self.D, dtype=torch.float32, device=dev)
+        self.m_part = torch.empty(self.n_q, n_splits, dtype=torch.float32, device=dev)
+        self.l_part = torch.empty_like(self.m_part)
+        self.graph = None               # a captured graph holds the old geometry
         self._setup_persistent_step()
 
     def _setup_persistent_step(self):
-        """Describe the step for b200_decode_step: device array of per-layer pointers, exchange and control memory."""
-        import ctypes
+        """Describe the step for b200_decode_step: device array of per-layer pointers, exchange and control memory.
+        The kernel streams the tile-layout copies of the matrices (gate|up in its paired form), the same copies the
+        per-operator GEMVs read."""
         mode = self.cfg.step_kernel
         G = self.cfg.group
-        fits = all(k % 128 == 0 and k % G == 0 and (k // G) % 4 == 0 for k in (self.H, self.n_q * self.D, self.I))
+        mats = [lw[n] for lw in self.layers for n in ("qkv", "o", "gu", "down")] + [self.lm_head]
+        fits = (all(k % 128 == 0 and k % G == 0 for k in (self.H, self.n_q * self.D, self.I)) and G % 128 == 0
+                and self.cfg.page <= 64 and all(m.tiled is not None for m in mats)
+                and all(lw["gu"].paired for lw in self.layers))
         if mode == "persistent" and self.tp > 1:
             raise ValueError("step_kernel='persistent' is single-GPU; tensor-parallel steps use one launch per operator")
-        self.persistent = mode == "persistent" or (mode == "auto" and not self.off and fits and self.tp == 1
-                                                   and self.ctx_cap <= PERSISTENT_MAX_CTX)
-        if mode == "persistent" and not fits:
-            raise ValueError("step_kernel='persistent' needs every K (hidden, heads*head_dim, intermediate) to hold a "
-                             "multiple of 4 quantization groups; use step_kernel='multi' for this shape")
         if mode == "persistent" and self.off:
             raise ValueError("step_kernel='persistent' computes the fused operators; it cannot run with fused=False or "
                              "an ablation switch")
+        if mode == "persistent" and not fits:
+            raise ValueError("step_kernel='persistent' needs tile_weights, hidden, heads*head_dim and intermediate sizes "
+                             "that are multiples of 128, a group size that is a multiple of 128 and pages of at most 64 "
+                             "tokens; use step_kernel='multi' for this model")
+        self.persistent = mode == "persistent" or (mode == "auto" and not self.off and fits and self.tp == 1
+                                                   and self.ctx_cap <= PERSISTENT_MAX_CTX)
         if not self.persistent:
             return
         dev = self.cfg.device
         if getattr(self, "_step_static", None) is None:
             grid = torch.cuda.get_device_properties(dev).multi_processor_count
-            kmax = max(self.H, self.n_q * self.D, self.I)
-            # a second copy of every matrix in the order the kernel's producers stream it (one bulk copy per stage)
-            streams = [{name: self.K.decode_step_repack(lw[name].packed, lw[name].sz, self.cfg.group, name == "gu", kmax,
-                                                        grid) for name in ("qkv", "o", "gu", "down")}
-                       for lw in self.layers]
-            head_stream = self.K.decode_step_repack(self.lm_head.packed, self.lm_head.sz, self.cfg.group, False, kmax,
-                                                    grid)
             arr = (ext.StepLayer * self.L)()
             for i, lw in enumerate(self.layers):
                 for k, name in enumerate(("qkv", "o", "gu", "down")):
-                    arr[i].w[k] = streams[i][name].data_ptr()
+                    arr[i].w[k] = lw[name].tiled.data_ptr()
                     arr[i].sz[k] = 0
                 arr[i].ln1, arr[i].ln2 = lw["ln1"].data_ptr(), lw["ln2"].data_ptr()
                 arr[i].kc, arr[i].vc = self.kv[i, 0].data_ptr(), self.kv[i, 1].data_ptr()
             host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
             nbytes = self.K.decode_step_xchg_bytes(self.L, self.H, self.I, self.n_q, self.n_kv, self.D, grid)
             self._step_static = {"layers": host.to(dev), "xchg": torch.zeros(nbytes, dtype=torch.uint8, device=dev),
-                                 "ctrl": torch.zeros(4, dtype=torch.int32, device=dev), "grid": grid,
-                                 "streams": streams, "head_stream": head_stream}
+                                 "ctrl": torch.zeros(4, dtype=torch.int32, device=dev), "grid": grid}
         st = self._step_static
         d = ext.StepDesc()
         d.layers = st["layers"].data_ptr()
         d.L, d.H, d.I, d.n_q, d.n_kv, d.D, d.V = self.L, self.H, self.I, self.n_q, self.n_kv, self.D, self.V
         d.log2G, d.log2P, d.eps = self.cfg.group.bit_length() - 1, self.cfg.page.bit_length() - 1, self.eps
         d.emb, d.norm_f = self.emb.data_ptr(), self.norm_f.data_ptr()
-        d.w_head, d.sz_head = st["head_stream"].data_ptr(), 0
+        d.w_head, d.sz_head = self.lm_head.tiled.data_ptr(), 0
         d.cos_t, d.sin_t, d.bt = self.cos.data_ptr(), self.sin.data_ptr(), self.bt.data_ptr()
         d.tok, d.pos, d.history = self.tok.data_ptr(), self.pos.data_ptr(), self.history.data_ptr()
         d.logits, d.xchg, d.ctrl = self.logits.data_ptr(), st["xchg"].data_ptr(), st["ctrl"].data_ptr()
@@ -302,16 +321,22 @@ class Model:
         self._step_desc = d
 
     def step_error(self):
-        """Code left by the persistent step kernel if one of its bounded waits gave up (0 = none). Synchronises."""
+        """Non-zero if a bounded wait inside a kernel of the step gave up (the step's outputs are then invalid): the
+        persistent kernel's code (4 = a token id outside the vocabulary was replaced by 0), the peer exchange's, or
+        the attention ring's. Synchronises."""
+        code = 0
         if getattr(self, "comm", None) is not None:
-            return self.comm.error()
-        if not getattr(self, "persistent", False):
-            return 0
-        return int(self._step_static["ctrl"][1])
+            code = self.comm.error()
+        if getattr(self, "persistent", False):
+            code = code or int(self._step_static["ctrl"][1])
+        else:
+            code = code or self.K.paged_attention_status()
+        return code
 
     def prepare(self, ctx_cap, use_graph=True, part_size=None):
-        """Configure attention for contexts <= ctx_cap and (re)capture the decode graph."""
-        assert ctx_cap <= self.cfg.max_ctx
+        """Get ready to decode up to context ctx_cap: attention geometry, then (optionally) the CUDA graph."""
+        if ctx_cap > self.cfg.max_ctx:
+            raise ValueError(f"ctx_cap {ctx_cap} exceeds max_ctx {self.cfg.max_ctx} the caches were sized for")
         self.set_attention_partition(ctx_cap, part_size)
         if use_graph:
             self.capture()
@@ -456,40 +481,43 @@ class Model:
         K.argmax(self.logits, self.tok, self.pos, self.history)
 
     def capture(self):
-        """Capture step() into a CUDA graph (two warm-up steps on a side stream first, as torch requires).
-        Warm-up runs at positions 0 and 1 (reference runtime/model.py:235-251); the token, position, history
-        entries and the KV page it touches are saved and put back, so capturing in mid-sequence loses nothing."""
+        """Record step() as one CUDA graph. torch wants the work run once or twice on a side stream before it
+        records, and a step has side effects (token, position, history, one KV row per layer), so everything the
+        warm-up and the recording touch is saved first and restored afterwards: capturing in mid-sequence loses
+        nothing. The warm-up runs at positions 0 and 1, the recording at 0, all inside the page bt[0]."""
         if self.tp > 1 and self.comm is None:
-            # Capturing a step that contains NCCL collectives did not complete on the B200 pool this was developed on
-            # (both ranks stalled inside the capture); with tp_comm="nccl" the steps are therefore launched eagerly.
-            # The peer-memory exchange is made of this library's own kernels and is captured like everything else.
+            # tp_comm="nccl": the step is launched eagerly (a capture that contains NCCL collectives is not attempted;
+            # the peer-memory exchange, made of this library's own kernels, is captured like everything else)
             self.graph = None
             return
-        saved_tok, saved_pos, saved_hist = self.tok.clone(), self.pos.clone(), self.history[:2].clone()
-        page0 = int(self.bt[0])
-        saved_kv = self.kv[:, :, page0].clone()
+        first_page = int(self.bt[0])
+        keep = {"tok": self.tok.clone(), "pos": self.pos.clone(), "hist": self.history[:2].clone(),
+                "kv": self.kv[:, :, first_page].clone()}
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
         self.pos.zero_()
-        s = torch.cuda.Stream()
-        s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):
-            for _ in range(2):
-                self.step()
-        torch.cuda.current_stream().wait_stream(s)
-        self.pos.zero_()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.stream(side):
             self.step()
-        self.tok.copy_(saved_tok)
-        self.pos.copy_(saved_pos)
-        self.history[:2].copy_(saved_hist)
-        self.kv[:, :, page0].copy_(saved_kv)
+            self.step()
+        torch.cuda.current_stream().wait_stream(side)
+        self.pos.zero_()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.step()
+        self.graph = graph
+        self.tok.copy_(keep["tok"])
+        self.pos.copy_(keep["pos"])
+        self.history[:2].copy_(keep["hist"])
+        self.kv[:, :, first_page].copy_(keep["kv"])
         torch.cuda.synchronize()
 
     def run_step(self, use_graph=True):
+        """One decode step at the next position (graph replay when a graph exists). The host mirrors the position
+        only to refuse a step the attention geometry or the caches cannot hold."""
+        limit = min(self.ctx_cap, self.cfg.max_ctx)
+        if self.host_pos + 1 > limit:
+            raise RuntimeError(f"context {self.host_pos + 1} exceeds the prepared attention cap {limit}; call prepare()")
         self.host_pos += 1
-        if self.host_pos > self.ctx_cap or self.host_pos > self.cfg.max_ctx:
-            raise RuntimeError(f"context {self.host_pos} exceeds the prepared attention cap "
-                               f"{min(self.ctx_cap, self.cfg.max_ctx)}; call prepare()")
         if use_graph and self.graph is not None:
             self.graph.replay()
         else:
@@ -497,32 +525,39 @@ class Model:
 
     # ------------------------------------------------------------------ high level
     def reset(self, pos=0):
-        self.pos.fill_(pos)
+        """Continue from position `pos` (0 = a new sequence; the cache rows below pos are kept)."""
         self.host_pos = pos
+        self.pos.fill_(pos)
 
     def teacher_force(self, tokens, use_graph=True, collect_logits=False):
-        """Feed tokens[i] at positions pos, pos+1, ...; returns logits [len, V] fp16 if requested."""
-        tokens = torch.as_tensor(tokens).long()
-        if tokens.device.type != "cuda":
-            tokens = (tokens.pin_memory() if tokens.numel() else tokens).to(self.tok.device, non_blocking=True)
-        out = torch.empty(len(tokens), self.V_full, dtype=torch.half, device=self.tok.device) if collect_logits else None
-        for i in range(len(tokens)):
-            self.tok.copy_(tokens[i:i + 1])
+        """Run one step per given token, feeding tokens[i] at the i-th next position (this is also how a prompt is
+        processed). Returns the logits of every step, fp16 [len, V], when collect_logits is set."""
+        ids = torch.as_tensor(tokens).long().reshape(-1)
+        n = ids.numel()
+        if n and (int(ids.min()) < 0 or int(ids.max()) >= self.V_full):
+            raise ValueError(f"token ids must lie in [0, {self.V_full})")
+        dev = self.tok.device
+        if ids.device.type != "cuda":
+            ids = (ids.pin_memory() if n else ids).to(dev, non_blocking=True)
+        logits = torch.empty(n, self.V_full, dtype=torch.half, device=dev) if collect_logits else None
+        for i in range(n):
+            self.tok.copy_(ids[i:i + 1])
             self.run_step(use_graph)
             if collect_logits:
-                out[i].copy_(self.logits)
-        return out
+                logits[i].copy_(self.logits)
+        return logits
 
     def generate(self, prompt, n_new, use_graph=True):
-        """Greedy: teacher-force the prompt, then free-run. Returns the n_new token ids as a list, reading each
-        one back from the device as it is produced (reference runtime/model.py:278-286)."""
+        """Greedy decoding of n_new tokens after `prompt`, each token read back to the host as soon as its step has
+        run (what the reference's generate does, runtime/model.py:278-286). Returns a list of ints."""
         self.reset(0)
         self.teacher_force(prompt, use_graph)
-        new = [int(self.tok)]
-        for _ in range(n_new - 1):
+        out = []
+        while True:
+            out.append(int(self.tok))      # device -> host read of the token the last step chose
+            if len(out) == n_new:
+                return out
             self.run_step(use_graph)
-            new.append(int(self.tok))
-        return new
 
     def generate_on_device(self, prompt, n_new, use_graph=True):
         """Same token stream as generate(), without a host read per token: the steps are queued back to back and
@@ -536,14 +571,19 @@ class Model:
 
     # ------------------------------------------------------------------ byte accounting (for the roofline)
     def weight_bytes(self):
-        b = sum(l[k].nbytes for l in self.layers for k in ("qkv", "o", "gu", "down"))
-        b += sum(l["ln1"].numel() * 2 + l["ln2"].numel() * 2 for l in self.layers)
-        return {"body": b, "lm_head": self.lm_head.nbytes, "embedding_row": self.H * 2}
+        """Bytes of weights one token reads, by part: the quantized matrices and norm vectors of the layers, the LM
+        head, and one embedding row (the accounting of the reference, runtime/model.py:289-293)."""
+        body = 0
+        for lw in self.layers:
+            body += sum(lw[name].nbytes for name in ("qkv", "o", "gu", "down"))
+            body += 2 * (lw["ln1"].numel() + lw["ln2"].numel())
+        return {"body": body, "lm_head": self.lm_head.nbytes, "embedding_row": 2 * self.H}
 
     def kv_bytes_per_token(self, ctx):
-        """KV bytes read by attention at context ctx plus the new K, V rows written, all layers."""
-        row = self.n_kv * self.D * 2
-        return self.L * (2 * row * ctx + 2 * row)
+        """Cache bytes one token moves at context ctx: K and V rows of ctx tokens read, one of each written, in every
+        layer (reference runtime/model.py:295-297)."""
+        kv_row = 2 * self.n_kv * self.D             # fp16 row of all kv heads
+        return self.L * 2 * kv_row * (ctx + 1)
 
     def bytes_per_token(self, ctx):
         wb = self.weight_bytes()

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_python_signatures_cover_the_header():
     names = set(declared_functions()) - {"b200_version", "b200_strerror", "b200_last_cuda_error", "b200_decode_step",
-                                         "b200_decode_step_xchg_bytes", "b200_decode_step_repack",
+                                         "b200_decode_step_xchg_bytes",
                                          "b200_gemv_w4a16_tiled_bytes"}   # declared on their own
     assert names == set(ext.SIGNATURES), names ^ set(ext.SIGNATURES)
     text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
@@ -62,6 +62,9 @@ def test_bad_arguments_are_refused_on_the_host():
     assert lib.b200_comm_header_bytes() == 256
     assert lib.b200_add_rmsnorm(p16, None, p16, p16, 65536, 1e-5, None) == -5                   # H over capacity
     assert lib.b200_swiglu(p16, p16, 0, None) == -1
+    assert lib.b200_embed_row(p16, p16, p16, 64, 0, None) == -1                                 # empty table
+    assert lib.b200_gemv_w4a16_tune(1, 5632, 2048, 3, 148) == -1                                # ksplit not 1/2/4/8
+    assert lib.b200_gemv_w4a16_tune(1, 5632, 2048, 4, 176) == 0 and lib.b200_gemv_w4a16_tune(1, 5632, 2048, 0, 0) == 0
     assert lib.b200_paged_attention(7, p16, p16, p16, p16, p16, 32, 4, 4, 64, 1, p16, p16, p16, p16, None) == -1
     assert lib.b200_paged_attention(2, p16, p16, p16, p16, p16, 12, 4, 4, 64, 1, p16, p16, p16, p16, None) == -3
     assert lib.b200_paged_attention_batched(p16, p16, p16, p16, 8, p16, 1, 32, 4, 96, 4, 64, 1, p16, p16, p16, p16,

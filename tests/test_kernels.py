@@ -484,6 +484,36 @@ def test_exchange_kernels_with_one_rank(K):
         K.comm_free(base)
 
 
+def test_exchange_wait_that_runs_out_is_reported(K):
+    """A peer that never signals: the exchange kernel gives up after its bound, reports it and leaves the outputs
+    alone. Made on one GPU without any fault: the "peer" is a second local block that no kernel ever writes, and the
+    bound is set to a few thousand polls (milliseconds) through the block header."""
+    import ctypes
+    H = 1024
+    hdr = K.comm_header_bytes()
+    mine, silent = K.comm_alloc(hdr + 2 * H + 256), K.comm_alloc(hdr + 2 * H + 256)
+    try:
+        peers = (ctypes.c_void_p * 2)(mine, silent)
+        K.comm_set_wait_limit(mine, 2000)
+        x0 = torch.randn(H, device=dev).half()
+        w = torch.ones(H, dtype=torch.half, device=dev)
+        x, out = x0.clone(), torch.full((H,), 7.0, dtype=torch.half, device=dev)
+        K.tp_allreduce_add_rmsnorm(peers, 0, hdr, x, w, out, 1e-5)
+        torch.cuda.synchronize()                                  # the call returns: the wait was bounded
+        assert K.comm_error(mine) == 1
+        assert torch.equal(x, x0) and bool((out == 7.0).all())    # nothing was computed from a partial that never came
+        dst = torch.full((2 * 8,), 3.0, dtype=torch.half, device=dev)
+        K.tp_allgather(peers, 0, hdr, dst, 8)
+        torch.cuda.synchronize()
+        assert bool((dst == 3.0).all())
+        K.comm_reset(mine)
+        K.comm_reset(silent)
+        assert K.comm_error(mine) == 0
+    finally:
+        K.comm_free(mine)
+        K.comm_free(silent)
+
+
 def test_embed_and_argmax(K):
     torch.manual_seed(0)
     emb = torch.randn(1000, 2048, device=dev).half()
@@ -504,6 +534,18 @@ def test_embed_and_argmax(K):
     lg = torch.randn(4099, device=dev).half()[3:]                  # not 16-byte aligned: the scalar scan
     K.argmax(lg, tok)
     assert int(tok) == R.argmax_ref(lg.cpu())
+    # no comparable logit at all: an index inside the vocabulary, never 2^31 - 1
+    K.argmax(torch.full((32000,), float("nan"), dtype=torch.half, device=dev), tok)
+    assert int(tok) == 0
+    lg = torch.full((1000,), float("nan"), dtype=torch.half, device=dev)
+    lg[617] = -3.0
+    K.argmax(lg, tok)
+    assert int(tok) == 617
+    # a token id outside the table reads row 0 instead of memory far outside it
+    for bad in (1000, -5, 1 << 40):
+        tok.fill_(bad)
+        K.embed_row(emb, tok, x)
+        assert torch.equal(x, emb[0])
 
 
 def test_bw_read_runs(K):

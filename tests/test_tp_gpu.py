@@ -1,4 +1,4 @@
-"""Tensor-parallel decode on 2 GPUs against the single-GPU runtime and the CPU oracle (needs >= 2 CUDA devices)."""
+"""Tensor-parallel decode on 2 GPUs against the CPU oracle and the single-GPU runtime (needs >= 2 CUDA devices)."""
 import os
 import types
 
@@ -45,7 +45,7 @@ def _rank_main(rank, world, port, out, modes, tp_comm):
         if len(modes) == 2:   # the captured graph replays exactly what the eager launches compute
             assert torch.equal(res[modes[0]], res[modes[1]])
         if rank == 0:
-            torch.save({"logits": res[modes[-1]], "tokens": toks, "prompt": prompt}, out)
+            torch.save({"logits": res[modes[-1]], "tokens": toks, "prompt": prompt, "bt": m.bt.cpu()}, out)
         dist.barrier()
         if m.comm is not None:
             m.comm.close()
@@ -88,3 +88,10 @@ def test_tp2_matches_single_gpu(tmp_path, tp_comm, modes):
     scale = ref.abs().max().item()
     assert (got["logits"] - ref).abs().max().item() <= 1e-2 * scale    # only the summation order differs
     assert got["tokens"][0] == int(got["logits"][-1].argmax())
+    # the CPU oracle on the unsharded model: RTN quantization works group by group along K and row by row, so
+    # quantizing a shard gives the bits of the same rows / column groups of the quantized whole matrix
+    from oracle import model_oracle as MO
+    ocfg = types.SimpleNamespace(group=128, quant="rtn", qparams=None, max_ctx=96, page=16, shuffle_pages=True)
+    o = MO.OracleModel(sd, c, ocfg, block_table=got["bt"])
+    want = o.teacher_force(got["prompt"], collect_logits=True).float()
+    assert (got["logits"] - want).abs().max().item() <= 1.5e-2 * want.abs().max().item()

@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from llm_decode_kernels_b200 import ext
+from oracle import ops_oracle as R
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-3
@@ -36,6 +37,10 @@ def _case(K, n_q, n_kv, D, ctx, PS, seed):
     torch.cuda.synchronize()
     err = (out.float() - ref.float()).abs().max().item() / ref.float().abs().max().item()
     assert err <= TOL, (n_q, n_kv, D, ctx, PS, err)
+    # and against the CPU oracle, so that the check does not rest on another kernel of the same library alone
+    want = R.paged_attention_ref(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), ctx, page).float()
+    err = (out.cpu().float() - want).abs().max().item() / want.abs().max().item()
+    assert err <= TOL, ("oracle", n_q, n_kv, D, ctx, PS, err)
 
 
 def test_two_calls_in_a_row_match_the_allocating_entry_point():
@@ -57,3 +62,8 @@ def test_sizes_beyond_the_fixed_array_are_refused():
     kc16 = torch.zeros(4, 16, 16, 64, dtype=torch.half, device="cuda")
     with pytest.raises(RuntimeError, match="capacity"):
         K.paged_attention_noalloc(q128, kc16, kc16, bt, pos, 16, 4, torch.empty_like(q128))  # 128 heads > 64
+    # the host face checks shapes before the pointer reaches the kernel
+    with pytest.raises(RuntimeError, match="shape"):
+        K.paged_attention_noalloc(q, kc, kc, bt, pos, 16, 4, torch.empty(16, 64, dtype=torch.half, device="cuda"))
+    with pytest.raises(RuntimeError, match="heads-per-group"):
+        K.paged_attention_noalloc(q[:12], kc, kc, bt, pos, 16, 4, torch.empty_like(q[:12]))   # 12 / 4 = 3
