@@ -9,11 +9,13 @@
 //     copies (cp.async.bulk + mbarrier transaction counts). Neither weights nor cached K/V depend on this step's
 //     activations, so the producer runs ahead of the computation by the depth of the ring and HBM never idles
 //     while CTAs wait for each other;
-//   * 16 consumer warps do the arithmetic out of the ring on the tensor cores (see "inner product" below), with the
-//     row length K split across the warps: warp w owns the 128-column units w, w + 16, ... of every row tile, so it
-//     needs only its own 128-element pieces of the activation vector, fetches exactly those, and keeps them in
-//     registers - no CTA-wide staging pass and no barrier in front of a GEMV. The warps' partial sums meet in shared
-//     memory once per matrix;
+//   * 8 consumer warps do the arithmetic out of the ring on the tensor cores (see "inner product" below), with the
+//     row length K split across the warps: warp w owns the 128-column units w, w + 8, ... of every row tile, so it
+//     needs only its own 128-element pieces of the activation vector and fetches exactly those - no CTA-wide staging
+//     pass and no barrier in front of a GEMV. The warps' partial sums meet in shared memory once per matrix.
+//     (Nine warps, not seventeen: a thread then has 168 registers instead of 96, and this kernel must not spill -
+//     with 227 KB of the SM's memory configured as shared there is next to no L1 left, so spilled registers would
+//     be fetched from the L2, a microsecond each time, in a kernel whose phases last a microsecond;)
 //   * CTAs exchange activation vectors through global memory WITHOUT grid barriers: every fp16 result is stored
 //     as a 32-bit word (tag << 16 | value) whose tag is this step's epoch; a consumer polls the words it needs until
 //     all carry the current tag. One store + one load crosses the chip instead of fence + atomic + poll + load.
@@ -60,14 +62,14 @@ namespace b200 {
 
 namespace {
 
-constexpr int kNCW = 16;                    // consumer warps
+constexpr int kNCW = 8;                     // consumer warps (with the producer: 9 warps, 168 registers a thread)
 constexpr int kNT = kNCW * 32;              // consumer threads
 constexpr int kThreads = kNT + 32;          // + producer warp
 constexpr int kMaxStages = 16;
 constexpr int kSpinLimit = 1 << 18;         // polls / try_waits before a wait gives up (tens of milliseconds)
 constexpr int kHeaderBytes = 2048;
-constexpr int kMaxKvTokens = 64;            // cached tokens per ring stage in attention (16 warps x 4 tokens)
-constexpr int kPollBatch = 4;               // exchange granules a lane keeps in flight while it polls (plain staging)
+constexpr int kMaxKvTokens = 64;            // cached tokens per ring stage in attention (2 rounds of 8 warps x 4 tokens)
+constexpr int kPollBatch = 6;               // exchange granules a lane keeps in flight while it polls (plain staging)
 constexpr int kNormBatch = 2;               // the same where a norm follows: units of the residual stream per pass
 
 enum : int { ERR_POLL = 1, ERR_FULL = 2, ERR_EMPTY = 3, ERR_TOKEN = 4 };
@@ -129,7 +131,7 @@ DEVI void st_tagged(uint32_t* p, uint32_t v) {
 // Shared memory: [0, 128) full barriers, [128, 256) empty barriers, 256 abort flag, 272 sum scratch, 512 slices;
 // from kHeaderBytes on: residual stream, then the areas whose offsets the host put into StepParams (off_*).
 // Pointers into it are formed where they are used (one add of a kernel parameter) instead of being carried in
-// registers through the whole step: with 17 warps a thread has 96 registers.
+// registers through the whole step.
 struct Cta {
   uint8_t* smem;
   const StepParams* p;   // the kernel's parameter block (constant bank)
@@ -167,7 +169,7 @@ DEVI void stamp(const Cta& c, int at) {
 #else
 DEVI void stamp(const Cta&, int) {}
 #endif
-constexpr int kTraceHead = 8, kTracePerPhase = 5, kTracePerLayer = 4 * kTracePerPhase + 1;
+constexpr int kTraceHead = 8, kTracePerPhase = 5, kTraceAttn = 4, kTracePerLayer = 4 * kTracePerPhase + kTraceAttn;
 
 DEVI void raise(const Cta& c, int code) {
   if (!*c.abort()) {
@@ -233,7 +235,7 @@ DEVI uint2 poll4(const Cta& c, const uint32_t* p) {
 }
 
 // ---- x staging, per warp ------------------------------------------------------------------------------------------
-// Warp w stages the units w, w + 16, ... of the activation vector: lane l holds granule l (4 values) of a unit.
+// Warp w stages the units w, w + 8, ... of the activation vector: lane l holds granule l (4 values) of a unit.
 DEVI void put_unit(const Cta& c, int u, uint2 v, int lane) {
   reinterpret_cast<uint2*>(c.xin())[32 * u + lane] = v;
   const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
@@ -397,70 +399,72 @@ DEVI void produce_kv(const Cta& c, const StepParams& p, const StepLayer& ly, int
   }
 }
 
+// One tile-unit block (at `tu` in the ring) against unit u of x: this lane's share of the two dot products, scaled
+// and with the zero-point term, for row slots g (ya) and g + 8 (yb); meaningful on lanes t == 0.
+// Lane (g, t) reads 16 bytes of row slot g and of row slot g + 8 (columns 32 t .. 32 t + 31 of the unit); lanes (0, t)
+// carry the matching 32 activations as the B operand, the other lanes zeros. Eight independent MMAs (each starts
+// from zero): a dependent mma.sync would wait for the whole latency of the one before it.
+DEVI void tile_unit(const Cta& c, const uint8_t* tu, int u, int lane, float& ya, float& yb) {
+  const int g = lane >> 2, t = lane & 3;
+  uint4 xv[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) xv[j] = make_uint4(0u, 0u, 0u, 0u);
+  if (g == 0) {
+    const uint4* xp = reinterpret_cast<const uint4*>(c.xin()) + 16 * u + 4 * t;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) xv[j] = xp[j];
+  }
+  const uint4 wa = *reinterpret_cast<const uint4*>(tu + 16 * lane);
+  const uint4 wb = *reinterpret_cast<const uint4*>(tu + 512 + 16 * lane);
+  const uint32_t A[4] = {wa.x, wa.y, wa.z, wa.w}, B[4] = {wb.x, wb.y, wb.z, wb.w};
+  float cl[4][4], ch[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t a8 = A[j] >> 8, b8 = B[j] >> 8;
+    // word j = columns 8 j .. 8 j + 7 of this lane's 32: (e0 e1) and (e4 e5) under the low mask, (e2 e3) and
+    // (e6 e7) under the high mask; xv[j] = (x0 x1, x2 x3, x4 x5, x6 x7)
+    mma16816_zero(cl[j], A[j] & 0x000F000Fu, B[j] & 0x000F000Fu, a8 & 0x000F000Fu, b8 & 0x000F000Fu, xv[j].x, xv[j].z);
+    mma16816_zero(ch[j], A[j] & 0x00F000F0u, B[j] & 0x00F000F0u, a8 & 0x00F000F0u, b8 & 0x00F000F0u, xv[j].y, xv[j].w);
+  }
+  // column 0 of the product: c[0] = row slot g, c[2] = row slot g + 8 (lanes t == 0)
+  const float2 sa = __half22float2(*reinterpret_cast<const half2*>(tu + 1024 + 4 * g));
+  const float2 sc = __half22float2(*reinterpret_cast<const half2*>(tu + 1024 + 4 * (g + 8)));
+  const float xs = c.xsum()[u];
+  const float la = (cl[0][0] + cl[1][0]) + (cl[2][0] + cl[3][0]), ha = (ch[0][0] + ch[1][0]) + (ch[2][0] + ch[3][0]);
+  const float lb = (cl[0][2] + cl[1][2]) + (cl[2][2] + cl[3][2]), hb = (ch[0][2] + ch[1][2]) + (ch[2][2] + ch[3][2]);
+  ya = fmaf(sa.x, fmaf(la, 16777216.f, fmaf(ha, 1048576.f, -sa.y * xs)), ya);
+  yb = fmaf(sc.x, fmaf(lb, 16777216.f, fmaf(hb, 1048576.f, -sc.y * xs)), yb);
+}
+
 // Consumer side of one matrix slice, one warp's share. The slice is the sequence of tile-unit blocks
 // (tile 0 unit 0, tile 0 unit 1, ..., tile 1 unit 0, ...), `ups` of them per ring stage; warp w takes the blocks of
-// units w, w + 16, ... of every tile. Lane (g, t) reads 16 bytes of row slot g and of row slot g + 8 (columns
-// 32 t .. 32 t + 31 of the unit), lanes (0, t) carry the matching 32 activations as the B operand, the other lanes
-// zeros; 8 MMAs per block. When the warp has passed its last unit of a tile, lanes t == 0 leave the two partial sums
-// of rows g and g + 8 in part[warp][16 * tile + row slot]. A warp whose units do not exist (K < 2048) only keeps the
-// ring's barriers moving.
+// units w, w + 8, ... of every tile, two at a time where the ring stage holds both (two independent instruction
+// streams for the scheduler to interleave). When the warp has passed its last unit of a tile, lanes t == 0 leave the
+// two partial sums of rows g and g + 8 in part[warp][16 * tile + row slot]. A warp whose units do not exist
+// (K < 1024) only keeps the ring's barriers moving.
 DEVI void gemv(const Cta& c, const Mat& m, const Slice& s, float* part, int pstride, RingPos& rp, int warp, int lane,
                int trace_at) {
   const int g = lane >> 2, t = lane & 3;
   const int nunit = m.K >> 7, NU = s.nt * nunit;
   const bool active = warp < nunit;
   int tl = 0, u = warp, idx = warp;   // the warp's next block: local tile, unit, place in the sequence
-  int cur_u = -1;
-  uint4 xv[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) xv[j] = make_uint4(0u, 0u, 0u, 0u);
-  float xs = 0.f, ya = 0.f, yb = 0.f;
+  float ya = 0.f, yb = 0.f;
   for (int i0 = 0; i0 < NU; i0 += c.p->ups, advance(rp, c.p->ns)) {
     const int slot = rp.slot;
     const bool ok = wait_bar(c, c.full(slot), rp.parity, ERR_FULL);
     if (i0 == 0) stamp(c, trace_at);   // the first stage of the matrix is in shared memory
     const int end = min(NU, i0 + c.p->ups);
-    const uint8_t* sb = c.stage(slot);
+    const uint8_t* sb = c.stage(slot) - (size_t)i0 * kTileUnitBytes;   // block idx of the sequence is at sb + idx * 1088
     if (ok && active) {
       while (idx < end) {
-        if (u != cur_u) {   // K > 2048: several units per warp, the activations of the next one come from xin
-          if (g == 0) {
-            const uint4* xp = reinterpret_cast<const uint4*>(c.xin()) + 16 * u + 4 * t;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) xv[j] = xp[j];
-          }
-          xs = c.xsum()[u];
-          cur_u = u;
-        }
-        const uint8_t* tu = sb + (size_t)(idx - i0) * kTileUnitBytes;
-        const uint4 wa = *reinterpret_cast<const uint4*>(tu + 16 * lane);
-        const uint4 wb = *reinterpret_cast<const uint4*>(tu + 512 + 16 * lane);
-        const uint32_t A[4] = {wa.x, wa.y, wa.z, wa.w}, B[4] = {wb.x, wb.y, wb.z, wb.w};
-        float cl[4], ch[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t a8 = A[j] >> 8, b8 = B[j] >> 8;
-          // word j = columns 8 j .. 8 j + 7 of this lane's 32: (e0 e1) and (e4 e5) under the low mask, (e2 e3) and
-          // (e6 e7) under the high mask; xv[j] = (x0 x1, x2 x3, x4 x5, x6 x7)
-          if (j == 0) {
-            mma16816_zero(cl, A[j] & 0x000F000Fu, B[j] & 0x000F000Fu, a8 & 0x000F000Fu, b8 & 0x000F000Fu, xv[j].x,
-                          xv[j].z);
-            mma16816_zero(ch, A[j] & 0x00F000F0u, B[j] & 0x00F000F0u, a8 & 0x00F000F0u, b8 & 0x00F000F0u, xv[j].y,
-                          xv[j].w);
-          } else {
-            mma16816_acc(cl, A[j] & 0x000F000Fu, B[j] & 0x000F000Fu, a8 & 0x000F000Fu, b8 & 0x000F000Fu, xv[j].x,
-                         xv[j].z);
-            mma16816_acc(ch, A[j] & 0x00F000F0u, B[j] & 0x00F000F0u, a8 & 0x00F000F0u, b8 & 0x00F000F0u, xv[j].y,
-                         xv[j].w);
-          }
-        }
-        if (t == 0) {   // column 0 of the product: c[0] = row slot g, c[2] = row slot g + 8
-          const float2 sa = __half22float2(*reinterpret_cast<const half2*>(tu + 1024 + 4 * g));
-          const float2 sc = __half22float2(*reinterpret_cast<const half2*>(tu + 1024 + 4 * (g + 8)));
-          ya = fmaf(sa.x, fmaf(cl[0], 16777216.f, fmaf(ch[0], 1048576.f, -sa.y * xs)), ya);
-          yb = fmaf(sc.x, fmaf(cl[2], 16777216.f, fmaf(ch[2], 1048576.f, -sc.y * xs)), yb);
-        }
-        u += kNCW;
+        const bool two = u + kNCW < nunit && idx + kNCW < end;   // the next unit of the same tile is in this stage too
+        float ya2 = 0.f, yb2 = 0.f;
+        tile_unit(c, sb + (size_t)idx * kTileUnitBytes, u, lane, ya, yb);
+        if (two) tile_unit(c, sb + (size_t)(idx + kNCW) * kTileUnitBytes, u + kNCW, lane, ya2, yb2);
+        ya += ya2;
+        yb += yb2;
+        const int step = two ? 2 * kNCW : kNCW;
+        u += step;
         if (u >= nunit) {
           if (t == 0) {
             part[warp * pstride + 16 * tl + g] = ya;
@@ -471,7 +475,7 @@ DEVI void gemv(const Cta& c, const Mat& m, const Slice& s, float* part, int pstr
           u = warp;
           idx = tl * nunit + warp;
         } else {
-          idx += kNCW;
+          idx += step;
         }
       }
     }
@@ -481,6 +485,25 @@ DEVI void gemv(const Cta& c, const Mat& m, const Slice& s, float* part, int pstr
 }
 
 enum : int { OUT_TAGGED = 0, OUT_SWIGLU = 1, OUT_LOGITS = 2 };
+
+// Sum of one row slot over the nwa warps that hold a share of it, always in the same order. With all warps (rows of
+// 1024 weights and more) the loads are issued together and added as a tree: the loop form would make every load
+// wait for the add before it.
+DEVI float sum_partials(const float* p, int pstride, int nwa) {
+  if (nwa == kNCW) {
+    float v[kNCW];
+#pragma unroll
+    for (int k = 0; k < kNCW; ++k) v[k] = p[k * pstride];
+#pragma unroll
+    for (int w = kNCW / 2; w > 0; w >>= 1)
+#pragma unroll
+      for (int k = 0; k < w; ++k) v[k] += v[k + w];
+    return v[0];
+  }
+  float y = 0.f;
+  for (int k = 0; k < nwa; ++k) y += p[k * pstride];
+  return y;
+}
 
 // After the barrier that follows gemv(): thread i adds the warps' partial sums of row slot i in a fixed order
 // (deterministic) and emits the output.
@@ -493,8 +516,7 @@ DEVI void reduce_emit(const Cta& c, const Mat& m, const Slice& s, const float* p
     for (int i = tid; i < 8 * s.nt; i += kNT) {
       const int slot = 16 * (i >> 3) + (i & 7), o = 8 * s.t0 + i;
       if (o >= m.N) continue;
-      float ga = 0.f, up = 0.f;
-      for (int k = 0; k < nwa; ++k) { ga += part[k * pstride + slot]; up += part[k * pstride + slot + 8]; }
+      const float ga = sum_partials(part + slot, pstride, nwa), up = sum_partials(part + slot + 8, pstride, nwa);
       const half h0 = __float2half(ga), h1 = __float2half(up);
       const float gf = __half2float(h0);
       const half sl = __float2half(__fdividef(gf, 1.f + __expf(-gf)));
@@ -505,9 +527,7 @@ DEVI void reduce_emit(const Cta& c, const Mat& m, const Slice& s, const float* p
   for (int i = tid; i < 16 * s.nt; i += kNT) {
     const int row = 16 * s.t0 + i;
     if (row >= m.N) continue;
-    float y = 0.f;
-    for (int k = 0; k < nwa; ++k) y += part[k * pstride + i];
-    const half h = __float2half(y);
+    const half h = __float2half(sum_partials(part + i, pstride, nwa));
     if (OUT == OUT_TAGGED) {
       st_tagged(E + row, c.tagw | (uint32_t)__half_as_ushort(h));
     } else {
@@ -523,7 +543,7 @@ DEVI void reduce_emit(const Cta& c, const Mat& m, const Slice& s, const float* p
 // dims [c D/8, (c+1) D/8) of it; each warp keeps a private online-softmax state, merged once at the end.
 template <int D>
 DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly, const uint32_t* Eqkv, uint32_t* Eattn,
-                         int h, int pos, RingPos& rp, int tid) {
+                         int h, int pos, RingPos& rp, int tid, int trace_at) {
   constexpr int D2 = D / 2, G4 = D / 4, DPL = D / 8;
   const int warp = tid >> 5, lane = tid & 31, ts = lane >> 3, ch = lane & 7;
   const int hpg = p.n_q / p.n_kv, kvh = h / hpg;
@@ -571,6 +591,7 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
   }
   consumer_sync();
 
+  stamp(c, trace_at);
   float qreg[DPL];
 #pragma unroll
   for (int d = 0; d < DPL; ++d) qreg[d] = qf[ch * DPL + d];
@@ -622,6 +643,7 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
     if (lane == 0) mbar_arrive(c.empty(slot));
   }
   if (warp == 0) fold(knew + ch * DPL, vnew + ch * DPL, ts == 0);   // the token of this step
+  stamp(c, trace_at + 1);
 
   // merge: token slots inside the warp, then the warps
   float lw = l;
@@ -651,6 +673,7 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
     }
     st_tagged(Eattn + (size_t)h * D + tid, c.tagw | (uint32_t)__half_as_ushort(__float2half(o / L)));
   }
+  stamp(c, trace_at + 2);
   consumer_sync();
 }
 
@@ -679,8 +702,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   // integer divisions) and kept in shared memory for producer and consumers.
   Slice* sl = reinterpret_cast<Slice*>(smem + 512);
   if (tid < 5) {
-    const int rows[5] = {n_qkv, p.H, p.I, p.H, p.V};
-    sl[tid] = slice_of(rows[tid], tid == 2, cta, ncta);
+    const int rows = tid == 0 ? n_qkv : (tid == 2 ? p.I : (tid == 4 ? p.V : p.H));
+    sl[tid] = slice_of(rows, tid == 2, cta, ncta);
   }
   {
     const uint4* src = reinterpret_cast<const uint4*>(p.layers);
@@ -729,7 +752,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   // ================= consumers =================
 #ifdef B200_STEP_TRACE
   // trace row of a CTA: kTraceHead slots (0 = start, 1 = keys exchanged, 2 = token written), then per layer
-  // kTracePerLayer: per phase {staged, first weights there, GEMV done, barrier passed, emitted}, then attention done;
+  // kTracePerLayer: per phase {staged, first weights there, GEMV done, barrier passed, emitted}, then attention
+  // {q k v polled and rotated, cached tokens folded, warps merged and output stored, done};
   // the LM head uses the slots of a layer L
   c.tr = p.trace ? p.trace + (size_t)cta * (kTraceHead + kTracePerLayer * (p.L + 1)) : nullptr;
 #endif
@@ -811,10 +835,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     if (is_head) break;
     if (ph == 0) {
       for (int h = cta; h < p.n_q; h += ncta) {
-        attention_head<D>(c, p, ly, Eqkv, Eatt, h, pos, rp, tid);
+        attention_head<D>(c, p, ly, Eqkv, Eatt, h, pos, rp, tid, kTraceHead + kTracePerLayer * l + 4 * kTracePerPhase);
         if (consumer_sync_or(*c.abort())) return;
       }
-      stamp(c, kTraceHead + kTracePerLayer * l + 4 * kTracePerPhase);
+      stamp(c, kTraceHead + kTracePerLayer * l + 4 * kTracePerPhase + 3);
     }
   }
   // this CTA's candidate: max over its threads' keys

@@ -25,8 +25,9 @@ import torch
 from . import build as B
 from . import ext
 
-HEAD, PER_PHASE, MATS = 8, 5, ("qkv", "o", "gate_up", "down")
-PER_LAYER = 4 * PER_PHASE + 1
+HEAD, PER_PHASE, N_ATT, MATS = 8, 5, 4, ("qkv", "o", "gate_up", "down")
+PER_LAYER = 4 * PER_PHASE + N_ATT
+ATT_STAMPS = ("q k v polled and rotated", "cached tokens folded", "merged and stored", "left")
 STAMPS = ("stage", "wait_weights", "mma", "barrier", "emit")     # what ends at each of a phase's five stamps
 
 
@@ -60,20 +61,21 @@ def main():
         torch.cuda.synchronize()
         t = trace.cpu().numpy().astype(np.float64)
         lay = t[:, HEAD:HEAD + PER_LAYER * L].reshape(grid, L, PER_LAYER)
-        start = np.concatenate([t[:, :1], lay[:, :-1, PER_LAYER - 2]], axis=1)   # previous stamp of a layer's first one:
-        # the kernel start, then the last emit of the layer before (the attention stamp exists on attention CTAs only)
+        G = 4 * PER_PHASE                            # first attention slot; the last one is "attention left"
         d = np.zeros((grid, L, PER_LAYER))
-        prev = start
-        for i in range(PER_LAYER):
-            cur = lay[:, :, i]
-            if i == PER_LAYER - 1:                  # attention: follows the qkv emit
-                d[:, :, i] = np.where(cur > 0, cur - lay[:, :, PER_PHASE - 1], 0.0)
-                continue
+        # a layer's first stamp follows the kernel start or the last emit of the layer before
+        prev = np.concatenate([t[:, :1], lay[:, :-1, G - 1]], axis=1)
+        for i in range(G):
             if i == PER_PHASE:                      # o.stage follows attention where there is one, else the qkv emit
-                att = lay[:, :, PER_LAYER - 1]
-                prev = np.where(att > 0, att, prev)
+                left = lay[:, :, PER_LAYER - 1]
+                prev = np.where(left > 0, left, prev)
+            cur = np.where(lay[:, :, i] > 0, lay[:, :, i], prev)   # a CTA without tiles of a matrix never waits for it
             d[:, :, i] = cur - prev
             prev = cur
+        prev = lay[:, :, PER_PHASE - 1]             # attention follows the qkv emit
+        for i in range(G, PER_LAYER):
+            d[:, :, i] = np.where(lay[:, :, i] > 0, lay[:, :, i] - prev, 0.0)
+            prev = lay[:, :, i]
         acc.append(d)
         totals.append((t[0, 2] - t[:, 0].min()) / 1e3)
     assert m.step_error() == 0, m.step_error()
@@ -84,10 +86,11 @@ def main():
             col = d[:, PER_PHASE * k + j]
             res["phases_us"][f"{name}.{what}"] = {"median_cta": round(float(np.median(col)), 3),
                                                   "slowest_cta": round(float(col.max()), 3)}
-    col = d[:n_att, PER_LAYER - 1]
-    res["phases_us"]["attention (its CTAs)"] = {"median_cta": round(float(np.median(col)), 3),
-                                                "slowest_cta": round(float(col.max()), 3)}
-    res["layer_us_median_cta"] = round(float(np.median(d[:, :PER_LAYER - 1].sum(axis=1))), 3)
+    for j, what in enumerate(ATT_STAMPS):
+        col = d[:n_att, 4 * PER_PHASE + j]
+        res["phases_us"][f"attention.{what}"] = {"median_cta": round(float(np.median(col)), 3),
+                                                 "slowest_cta": round(float(col.max()), 3)}
+    res["layer_us_median_cta"] = round(float(np.median(d[:, :4 * PER_PHASE].sum(axis=1))), 3)
     txt = json.dumps(res, indent=1)
     print(txt)
     if a.out:
