@@ -213,7 +213,7 @@ typedef struct b200_step_desc {
   int ctx_cap;         /* largest context (pos + 1) this launch may see */
   int grid;            /* CTAs = SMs of the device */
   long long* trace;    /* NULL. (A library built with -DB200_STEP_TRACE, which the normal build never is, fills an
-                        * int64 [grid, 8 + 24 (L + 1)] array here with per-CTA globaltimer values inside every phase.) */
+                        * int64 [grid, 8 + 25 (L + 1)] array here with per-CTA globaltimer values inside every phase.) */
 } b200_step_desc;
 
 /* Bytes of exchange memory a step of these dimensions needs. */

@@ -300,8 +300,8 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
   // shared-memory plan
   const int ncw = b200::decode_step_consumer_warps();
   const int resid_bytes = align_up(2 * d->H, 128);
-  const int xin_bytes = align_up(2 * kmax, 128);
-  const int xsum_bytes = align_up((kmax / 128) * 4, 128);
+  const int xin_bytes = align_up(2 * kmax, 128);             // two byte digits per activation, as B fragments
+  const int xsum_bytes = align_up((kmax / 128) * 8, 128);
   const int att_bytes = align_up((4 * d->D + ncw * d->D + 2 * ncw + d->D + 64) * 4, 128);
   int part_bytes;
   {

@@ -217,6 +217,17 @@ DEVI void mma16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, ui
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
+// mma.sync.m16n8k32, unsigned bytes x signed bytes, int32 accumulators (C += A B). Lane (g, t) holds
+//   A: a0 = A[g][4t .. 4t+3], a1 = A[g+8][4t .. 4t+3], a2 = A[g][16+4t ..], a3 = A[g+8][16+4t ..]   (one byte per k)
+//   B: b0 = B[4t .. 4t+3][g], b1 = B[16+4t ..][g]                       C as for m16n8k16.
+// Native on this part: it issues every 8 cycles per SM sub-core like the fp16 m16n8k16, for twice the k. (The e4m3
+// form of the same shape is emulated: measured with live operands it is slower than the fp16 one.)
+DEVI void mma16832_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // Bytes of one (16-row tile, 128-column unit) block of the tile layout (gemv_tile_repack_kernel): 512 B for row
 // slots 0-7 (lane l's 16 bytes at 16 l), 512 B for row slots 8-15, 16 x (scale, zero).
 constexpr int kTileUnitBytes = 1088;

@@ -9,11 +9,11 @@
 //     copies (cp.async.bulk + mbarrier transaction counts). Neither weights nor cached K/V depend on this step's
 //     activations, so the producer runs ahead of the computation by the depth of the ring and HBM never idles
 //     while CTAs wait for each other;
-//   * 8 consumer warps do the arithmetic out of the ring on the tensor cores (see "inner product" below), with the
-//     row length K split across the warps: warp w owns the 128-column units w, w + 8, ... of every row tile, so it
+//   * 12 consumer warps do the arithmetic out of the ring on the tensor cores (see "inner product" below), with the
+//     row length K split across the warps: warp w owns the 128-column units w, w + 12, ... of every row tile, so it
 //     needs only its own 128-element pieces of the activation vector and fetches exactly those - no CTA-wide staging
 //     pass and no barrier in front of a GEMV. The warps' partial sums meet in shared memory once per matrix.
-//     (Nine warps, not seventeen: a thread then has 168 registers instead of 96, and this kernel must not spill -
+//     (Thirteen warps, not seventeen: a thread then has 128 registers instead of 96, and this kernel must not spill -
 //     with 227 KB of the SM's memory configured as shared there is next to no L1 left, so spilled registers would
 //     be fetched from the L2, a microsecond each time, in a kernel whose phases last a microsecond;)
 //   * CTAs exchange activation vectors through global memory WITHOUT grid barriers: every fp16 result is stored
@@ -28,15 +28,25 @@
 // The gate|up matrix uses the paired form of the layout (gate row i and up row i in one tile), which puts both
 // halves of a SwiGLU output into the same thread.
 //
-// Inner product. A nibble masked in place is an fp16 SUBNORMAL: bits 0..3 of a half are q * 2^-24, bits 4..7 are
-// q * 2^-20. So (word & 0x000F000F) and (word & 0x00F000F0) are ready-made fp16 pairs, one shift by 8 exposes the
-// other four nibbles of a word, and a 16-row x 128-column block of W is 8 mma.m16n8k16 whose A registers are masked
-// words, with x in column 0 of B. The low-mask and the high-mask products go to two separate fp32 accumulators
-// (one MMA each per word), so x is used as it is - no scaling by max|x|, hence no reduction over the vector in
-// front of the GEMV:
-//     sum_k (q_k - z) * s * x_k  =  s * (2^24 * acc_lo + 2^20 * acc_hi - z * sum_k x_k)        per 128-column unit.
+// Inner product on the integer tensor cores. (word & 0x0F0F0F0F) and ((word >> 4) & 0x0F0F0F0F) are registers of four
+// unsigned-byte weights each - three integer instructions for 8 weights - so a 16-row x 128-column block of W is
+// four mma.m16n8k32 (u8 x s8 -> s32). The activations go in as 15-bit fixed point: staging scales a unit's x by
+// 2^s (s from the unit's max|x|; a unit belongs to one warp, so this costs five shuffles and no reduction over the
+// CTA), rounds to an integer X, |X| < 2^14, and splits it into two signed byte digits, X = 256 hi + lo. The digits
+// ride in columns 0 and 1 of the B operand, which a batch-1 GEMV leaves idle anyway, the accumulation is exact, and
+//     sum_k (q_k - z) * scale * x_k  =  scale * (2^-s * (256 C[.][0] + C[.][1]) - z * sum_k x_k)        per unit.
+// Rounding x to 2^-14 of its unit's maximum is finer than the fp16 rounding x already carries, except for elements
+// far below the maximum, whose absolute error it bounds by 2^-15 of the maximum (normwise ~1e-5 on the output).
+// A NaN or infinity in a unit of x - which an integer cannot carry - turns that unit's factor 2^-s into NaN, so
+// every row's output is NaN as in the reference.
+// Why this form: a GEMV phase of this kernel is bound by instruction issue, and most instructions around the
+// weights (LOP3, SHF, HFMA2) issue at half rate. Measured per tile-unit and warp, eight warps per SM: masked nibbles
+// as fp16 subnormals into mma.m16n8k16, 5 integer instructions + 1 MMA per 8 weights of a row pair: 320 cycles; the
+// same masks into half2 FMAs: 306; this form, 3 integer instructions per 8 weights and 4 MMAs per tile-unit: 195.
+// (The e4m3 MMA of the same shape would fit too - a nibble in the low half of an e4m3 byte is exactly q * 2^-9 -
+// but it is emulated on this part: 385.)
 // The per-element weight this stands for is the format's dequantized weight (dequant_w4a16 in gemv_w4a16.cu proves
-// the format bit-exactly); accumulation is fp32 throughout.
+// the format bit-exactly).
 //
 // Phases per layer (the reference's operator order, with the same rounding points as its fused kernels):
 //   A  resid += down[l-1] (layer 0: resid = embedding row);  x = RMSNorm(resid) * ln1;  qkv = Wqkv x
@@ -62,14 +72,15 @@ namespace b200 {
 
 namespace {
 
-constexpr int kNCW = 8;                     // consumer warps (with the producer: 9 warps, 168 registers a thread)
+constexpr int kNCW = 12;                    // consumer warps (with the producer: 13 warps, 128 registers a thread)
 constexpr int kNT = kNCW * 32;              // consumer threads
 constexpr int kThreads = kNT + 32;          // + producer warp
 constexpr int kMaxStages = 16;
 constexpr int kSpinLimit = 1 << 18;         // polls / try_waits before a wait gives up (tens of milliseconds)
 constexpr int kHeaderBytes = 2048;
-constexpr int kMaxKvTokens = 64;            // cached tokens per ring stage in attention (2 rounds of 8 warps x 4 tokens)
-constexpr int kPollBatch = 6;               // exchange granules a lane keeps in flight while it polls (plain staging)
+constexpr int kMaxKvTokens = 128;           // cached tokens per ring stage in attention (3 rounds of 12 warps x 4 tokens)
+constexpr int kKvRounds = (kMaxKvTokens + 4 * kNCW - 1) / (4 * kNCW);
+constexpr int kPollBatch = 4;               // exchange granules a lane keeps in flight while it polls (plain staging)
 constexpr int kNormBatch = 2;               // the same where a norm follows: units of the residual stream per pass
 
 enum : int { ERR_POLL = 1, ERR_FULL = 2, ERR_EMPTY = 3, ERR_TOKEN = 4 };
@@ -146,9 +157,9 @@ struct Cta {
   DEVI float* red() const { return reinterpret_cast<float*>(smem + 2 * kMaxStages * 8 + 16); }
   // [H] residual stream, private copy of the CTA; unit u belongs to warp u % kNCW
   DEVI half* resid() const { return reinterpret_cast<half*>(smem + kHeaderBytes); }
-  // [Kmax] activations of the running GEMV, natural order; unit u is written and read by one warp only
+  // activations of the running GEMV as byte-digit B fragments, 256 bytes per unit; unit u is written and read by one warp only
   DEVI half* xin() const { return reinterpret_cast<half*>(smem + p->off_xin); }
-  DEVI float* xsum() const { return reinterpret_cast<float*>(smem + p->off_xsum); }   // [Kmax / 128] unit sums
+  DEVI float* xsum() const { return reinterpret_cast<float*>(smem + p->off_xsum); }   // [Kmax / 128][2] sum, 2^-s
   DEVI float* att() const { return reinterpret_cast<float*>(smem + p->off_att); }     // attention scratch
   // partial dot products, [warp][row slot], two buffers used by alternate phases
   DEVI float* part() const { return reinterpret_cast<float*>(smem + p->off_part); }
@@ -169,7 +180,18 @@ DEVI void stamp(const Cta& c, int at) {
 #else
 DEVI void stamp(const Cta&, int) {}
 #endif
-constexpr int kTraceHead = 8, kTracePerPhase = 5, kTraceAttn = 4, kTracePerLayer = 4 * kTracePerPhase + kTraceAttn;
+#ifdef B200_STEP_TRACE
+DEVI long long now_ns() {
+  long long t_;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
+  return t_;
+}
+// slot `at` <- a duration (ns) instead of a time
+DEVI void stamp_value(const Cta& c, int at, long long v) {
+  if (c.tr && threadIdx.x == 0) c.tr[at] = v;
+}
+#endif
+constexpr int kTraceHead = 8, kTracePerPhase = 5, kTraceAttn = 5, kTracePerLayer = 4 * kTracePerPhase + kTraceAttn;
 
 DEVI void raise(const Cta& c, int code) {
   if (!*c.abort()) {
@@ -235,12 +257,45 @@ DEVI uint2 poll4(const Cta& c, const uint32_t* p) {
 }
 
 // ---- x staging, per warp ------------------------------------------------------------------------------------------
-// Warp w stages the units w, w + 8, ... of the activation vector: lane l holds granule l (4 values) of a unit.
+// Warp w stages the units w, w + kNCW, ... of the activation vector: lane l holds granule l (4 values) of a unit.
+// A unit's x goes to shared memory as the B fragments of the integer MMAs: X = round(x * 2^s), split into the signed
+// byte digits hi and lo (X = 256 hi + lo, both in [-128, 127]), laid out as
+//     xin words [unit][digit n = 0 (hi), 1 (lo)][t = 0..3][MMA m = 0..3][register r = 0..1]
+// where lane (n, t) of tile_unit() loads its eight registers with two 16-byte reads. Register r of MMA m pairs with
+// word 2 (m / 2) + r of the lane's four weight words, low nibbles (m even: elements e0 e4 e1 e5 of the word, in
+// byte order) or high nibbles (m odd: e2 e6 e3 e7). Granule l = 4 elements of word (l % 8) / 2: elements e0..e3 on
+// even lanes, e4..e7 on odd ones, so a lane pair swaps its packed bytes once and each lane permutes one register.
+// xsum[2 u] = 2^-s sum X (for the zero-point term), xsum[2 u + 1] = 2^-s (both NaN if the unit is not finite).
 DEVI void put_unit(const Cta& c, int u, uint2 v, int lane) {
-  reinterpret_cast<uint2*>(c.xin())[32 * u + lane] = v;
+  // max|x| of the unit from the bit patterns (the order of non-negative fp16 numbers is the order of their bits)
+  const uint32_t m2 = __vmaxu2(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu);
+  const uint32_t mx = __reduce_max_sync(0xffffffffu, max(m2 & 0xFFFFu, m2 >> 16));
+  const bool finite = mx < 0x7C00u;                       // no infinity, no NaN
+  const int sh = 28 - max((int)(mx >> 10), 1);            // exponent field e: max|x| in [2^(e-15), 2^(e-14)) -> 2^sh max|x| in [2^13, 2^14)
+  const float sc = __int_as_float((sh + 127) << 23);      // 2^sh, sh in [-2, 27]
+  // round(x * 2^sh) + 128 in the low bits of a float: adding 1.5 * 2^23 + 128 rounds to an integer (nearest even)
+  // and leaves it, in two's complement, in the mantissa. Byte 0 of that, with its top bit flipped, is the lo digit
+  // (X & 255 read as a signed byte), byte 1 is the hi digit ((X + 128) >> 8).
+  constexpr float kMagic = 12582912.f + 128.f;
   const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
-  const float s = warp_sum((a.x + a.y) + (b.x + b.y));
-  if (lane == 0) c.xsum()[u] = s;
+  const uint32_t w0 = __float_as_uint(fmaf(a.x, sc, kMagic)), w1 = __float_as_uint(fmaf(a.y, sc, kMagic));
+  const uint32_t w2 = __float_as_uint(fmaf(b.x, sc, kMagic)), w3 = __float_as_uint(fmaf(b.y, sc, kMagic));
+  const uint32_t kM = __float_as_uint(kMagic);            // w - kM = X
+  const int xsum_i = __reduce_add_sync(0xffffffffu, (int)(w0 - kM) + (int)(w1 - kM) + (int)(w2 - kM) + (int)(w3 - kM));
+  const float resc = finite ? __int_as_float((127 - sh) << 23) : __int_as_float(0x7fc00000);   // 2^-sh, or NaN
+  if (lane == 0) {
+    c.xsum()[2 * u] = (float)xsum_i * resc;               // the sum of what the MMAs multiply, rescaled
+    c.xsum()[2 * u + 1] = resc;
+  }
+  // bytes: this granule's 4 elements in order
+  const uint32_t lo = __byte_perm(__byte_perm(w0, w1, 0x0040), __byte_perm(w2, w3, 0x0040), 0x5410) ^ 0x80808080u;
+  const uint32_t hi = __byte_perm(__byte_perm(w0, w1, 0x0051), __byte_perm(w2, w3, 0x0051), 0x5410);
+  const int t = lane >> 3, wd = (lane & 7) >> 1, odd = lane & 1;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(c.xin()) + (size_t)u * 64 + t * 8 + ((wd >> 1) * 2 + odd) * 2 + (wd & 1);
+  const uint32_t hi_o = __shfl_xor_sync(0xffffffffu, hi, 1), lo_o = __shfl_xor_sync(0xffffffffu, lo, 1);
+  // even lane (e0..e3; partner e4..e7): low-nibble register (e0 e4 e1 e5); odd lane: high-nibble one (e2 e6 e3 e7)
+  dst[0] = odd ? __byte_perm(hi, hi_o, 0x3726) : __byte_perm(hi, hi_o, 0x5140);
+  dst[32] = odd ? __byte_perm(lo, lo_o, 0x3726) : __byte_perm(lo, lo_o, 0x5140);
 }
 
 // x <- E[0..K) (tagged).
@@ -390,56 +445,52 @@ DEVI void produce_kv(const Cta& c, const StepParams& p, const StepLayer& ly, int
     uint8_t* dst = c.stage(slot);
     if (lane == 0) mbar_expect_tx(c.full(slot), 2 * npg * page_bytes);
     __syncwarp();
-    if (lane < npg) {
-      const size_t off = ((size_t)p.bt[pg0 + lane] * p.n_kv + kvh) * page_bytes;
-      bulk_g2s(dst + lane * page_bytes, reinterpret_cast<const uint8_t*>(ly.kc) + off, page_bytes, c.full(slot));
-      bulk_g2s(dst + (size_t)tps * p.D * 2 + lane * page_bytes, reinterpret_cast<const uint8_t*>(ly.vc) + off,
+    for (int pg = lane; pg < npg; pg += 32) {
+      const size_t off = ((size_t)p.bt[pg0 + pg] * p.n_kv + kvh) * page_bytes;
+      bulk_g2s(dst + pg * page_bytes, reinterpret_cast<const uint8_t*>(ly.kc) + off, page_bytes, c.full(slot));
+      bulk_g2s(dst + (size_t)tps * p.D * 2 + pg * page_bytes, reinterpret_cast<const uint8_t*>(ly.vc) + off,
                page_bytes, c.full(slot));
     }
   }
 }
 
-// One tile-unit block (at `tu` in the ring) against unit u of x: this lane's share of the two dot products, scaled
-// and with the zero-point term, for row slots g (ya) and g + 8 (yb); meaningful on lanes t == 0.
-// Lane (g, t) reads 16 bytes of row slot g and of row slot g + 8 (columns 32 t .. 32 t + 31 of the unit); lanes (0, t)
-// carry the matching 32 activations as the B operand, the other lanes zeros. Eight independent MMAs (each starts
-// from zero): a dependent mma.sync would wait for the whole latency of the one before it.
+// One tile-unit block (at `tu` in the ring) against unit u of x: the dot products of row slots g (ya) and g + 8 (yb)
+// over the unit's 128 columns, scaled and with the zero-point term; meaningful on lanes t == 0.
+// Lane (g, t) reads 16 bytes of row slot g and of row slot g + 8 (columns 32 t .. 32 t + 31 of the unit); lanes
+// (0, t) carry the hi digits of the matching 32 activations as the B operand, lanes (1, t) the lo digits, the other
+// lanes zeros. Four MMAs in two independent chains.
 DEVI void tile_unit(const Cta& c, const uint8_t* tu, int u, int lane, float& ya, float& yb) {
   const int g = lane >> 2, t = lane & 3;
-  uint4 xv[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) xv[j] = make_uint4(0u, 0u, 0u, 0u);
-  if (g == 0) {
-    const uint4* xp = reinterpret_cast<const uint4*>(c.xin()) + 16 * u + 4 * t;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) xv[j] = xp[j];
+  uint4 x0 = make_uint4(0u, 0u, 0u, 0u), x1 = x0;
+  if (g < 2) {
+    const uint4* xp = reinterpret_cast<const uint4*>(c.xin()) + (size_t)u * 16 + (g * 4 + t) * 2;
+    x0 = xp[0];   // MMAs 0, 1: registers (m0 r0, m0 r1, m1 r0, m1 r1)
+    x1 = xp[1];   // MMAs 2, 3
   }
   const uint4 wa = *reinterpret_cast<const uint4*>(tu + 16 * lane);
   const uint4 wb = *reinterpret_cast<const uint4*>(tu + 512 + 16 * lane);
-  const uint32_t A[4] = {wa.x, wa.y, wa.z, wa.w}, B[4] = {wb.x, wb.y, wb.z, wb.w};
-  float cl[4][4], ch[4][4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t a8 = A[j] >> 8, b8 = B[j] >> 8;
-    // word j = columns 8 j .. 8 j + 7 of this lane's 32: (e0 e1) and (e4 e5) under the low mask, (e2 e3) and
-    // (e6 e7) under the high mask; xv[j] = (x0 x1, x2 x3, x4 x5, x6 x7)
-    mma16816_zero(cl[j], A[j] & 0x000F000Fu, B[j] & 0x000F000Fu, a8 & 0x000F000Fu, b8 & 0x000F000Fu, xv[j].x, xv[j].z);
-    mma16816_zero(ch[j], A[j] & 0x00F000F0u, B[j] & 0x00F000F0u, a8 & 0x00F000F0u, b8 & 0x00F000F0u, xv[j].y, xv[j].w);
-  }
-  // column 0 of the product: c[0] = row slot g, c[2] = row slot g + 8 (lanes t == 0)
+  constexpr uint32_t kNib = 0x0F0F0F0Fu;
+  int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+  mma16832_u8s8(c0, wa.x & kNib, wb.x & kNib, wa.y & kNib, wb.y & kNib, x0.x, x0.y);
+  mma16832_u8s8(c1, (wa.x >> 4) & kNib, (wb.x >> 4) & kNib, (wa.y >> 4) & kNib, (wb.y >> 4) & kNib, x0.z, x0.w);
+  mma16832_u8s8(c0, wa.z & kNib, wb.z & kNib, wa.w & kNib, wb.w & kNib, x1.x, x1.y);
+  mma16832_u8s8(c1, (wa.z >> 4) & kNib, (wb.z >> 4) & kNib, (wa.w >> 4) & kNib, (wb.w >> 4) & kNib, x1.z, x1.w);
+  // lanes t == 0: C columns 0 (hi digits) and 1 (lo digits) of rows g (c[0], c[1]) and g + 8 (c[2], c[3])
   const float2 sa = __half22float2(*reinterpret_cast<const half2*>(tu + 1024 + 4 * g));
   const float2 sc = __half22float2(*reinterpret_cast<const half2*>(tu + 1024 + 4 * (g + 8)));
-  const float xs = c.xsum()[u];
-  const float la = (cl[0][0] + cl[1][0]) + (cl[2][0] + cl[3][0]), ha = (ch[0][0] + ch[1][0]) + (ch[2][0] + ch[3][0]);
-  const float lb = (cl[0][2] + cl[1][2]) + (cl[2][2] + cl[3][2]), hb = (ch[0][2] + ch[1][2]) + (ch[2][2] + ch[3][2]);
-  ya = fmaf(sa.x, fmaf(la, 16777216.f, fmaf(ha, 1048576.f, -sa.y * xs)), ya);
-  yb = fmaf(sc.x, fmaf(lb, 16777216.f, fmaf(hb, 1048576.f, -sc.y * xs)), yb);
+  const float xs = c.xsum()[2 * u], resc = c.xsum()[2 * u + 1];
+  const float va = (float)(((c0[0] + c1[0]) << 8) + (c0[1] + c1[1]));
+  const float vb = (float)(((c0[2] + c1[2]) << 8) + (c0[3] + c1[3]));
+  ya = fmaf(sa.x, fmaf(va, resc, -sa.y * xs), ya);
+  yb = fmaf(sc.x, fmaf(vb, resc, -sc.y * xs), yb);
 }
 
 // Consumer side of one matrix slice, one warp's share. The slice is the sequence of tile-unit blocks
 // (tile 0 unit 0, tile 0 unit 1, ..., tile 1 unit 0, ...), `ups` of them per ring stage; warp w takes the blocks of
-// units w, w + 8, ... of every tile, two at a time where the ring stage holds both (two independent instruction
-// streams for the scheduler to interleave). When the warp has passed its last unit of a tile, lanes t == 0 leave the
+// units w, w + kNCW, ... of every tile, two at a time where the ring stage holds both (two independent instruction
+// streams for the scheduler to interleave). The activations are re-read from shared memory for every block: keeping
+// them in registers across tiles was measured and loses - it pushes the kernel over its 168 registers, and a
+// spilled register costs an L2 round trip here. When the warp has passed its last unit of a tile, lanes t == 0 leave the
 // two partial sums of rows g and g + 8 in part[warp][16 * tile + row slot]. A warp whose units do not exist
 // (K < 1024) only keeps the ring's barriers moving.
 DEVI void gemv(const Cta& c, const Mat& m, const Slice& s, float* part, int pstride, RingPos& rp, int warp, int lane,
@@ -449,10 +500,18 @@ DEVI void gemv(const Cta& c, const Mat& m, const Slice& s, float* part, int pstr
   const bool active = warp < nunit;
   int tl = 0, u = warp, idx = warp;   // the warp's next block: local tile, unit, place in the sequence
   float ya = 0.f, yb = 0.f;
+#ifdef B200_STEP_TRACE
+  long long waited = 0;
+#endif
   for (int i0 = 0; i0 < NU; i0 += c.p->ups, advance(rp, c.p->ns)) {
     const int slot = rp.slot;
+#ifdef B200_STEP_TRACE
+    const long long w0 = now_ns();
+#endif
     const bool ok = wait_bar(c, c.full(slot), rp.parity, ERR_FULL);
-    if (i0 == 0) stamp(c, trace_at);   // the first stage of the matrix is in shared memory
+#ifdef B200_STEP_TRACE
+    waited += now_ns() - w0;   // time this warp spent waiting for ring stages of the matrix
+#endif
     const int end = min(NU, i0 + c.p->ups);
     const uint8_t* sb = c.stage(slot) - (size_t)i0 * kTileUnitBytes;   // block idx of the sequence is at sb + idx * 1088
     if (ok && active) {
@@ -482,6 +541,9 @@ DEVI void gemv(const Cta& c, const Mat& m, const Slice& s, float* part, int pstr
     __syncwarp();
     if (lane == 0) mbar_arrive(c.empty(slot));
   }
+#ifdef B200_STEP_TRACE
+  stamp_value(c, trace_at, waited);
+#endif
 }
 
 enum : int { OUT_TAGGED = 0, OUT_SWIGLU = 1, OUT_LOGITS = 2 };
@@ -495,10 +557,11 @@ DEVI float sum_partials(const float* p, int pstride, int nwa) {
 #pragma unroll
     for (int k = 0; k < kNCW; ++k) v[k] = p[k * pstride];
 #pragma unroll
-    for (int w = kNCW / 2; w > 0; w >>= 1)
+    for (int k = 0; k + 1 < kNCW; k += 2) v[k] += v[k + 1];     // pairs, then the pair sums in order
+    float y = v[0];
 #pragma unroll
-      for (int k = 0; k < w; ++k) v[k] += v[k + w];
-    return v[0];
+    for (int k = 2; k < kNCW; k += 2) y += v[k];
+    return y;
   }
   float y = 0.f;
   for (int k = 0; k < nwa; ++k) y += p[k * pstride];
@@ -599,51 +662,99 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
 #pragma unroll
   for (int d = 0; d < DPL; ++d) acc[d] = 0.f;
 
-  // fold one token (K row kp, V row vp, both this lane's DPL dims) into the warp's state; `valid` per token slot
-  auto fold = [&](const half* kp, const half* vp, bool valid) {
-    float kf[DPL], s = 0.f;
+  // Fold R rounds of 4 tokens per warp (token slot ts of round r: row jrow[r] of kb / vb, counted if valid[r]) into the
+  // warp's online-softmax state. The R scores are computed independently and share ONE max / rescale step, so a ring
+  // stage costs one dependent chain (loads, dot product, shuffles, exponentials, accumulate) whatever its token
+  // count. A slot that is not valid repeats a real row (its score is masked): rows past the stage's tokens may hold
+  // stale bytes of the ring, NaN patterns among them, and 0 * NaN would poison the sum.
+  auto fold = [&](const half* kb, const half* vb, const int (&jrow)[kKvRounds], const bool (&valid)[kKvRounds],
+                  const int R) {
+    float s[kKvRounds];
 #pragma unroll
-    for (int d8 = 0; d8 < DPL; d8 += 8) unpack8(*reinterpret_cast<const uint4*>(kp + d8), kf + d8);
+    for (int r = 0; r < kKvRounds; ++r) {
+      s[r] = -CUDART_INF_F;
+      if (r < R) {
+        float kf[DPL], a = 0.f;
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) s = fmaf(kf[d], qreg[d], s);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    s = valid ? s : -CUDART_INF_F;
-    float mw = fmaxf(s, __shfl_xor_sync(0xffffffffu, s, 8));
+        for (int d8 = 0; d8 < DPL; d8 += 8)
+          unpack8(*reinterpret_cast<const uint4*>(kb + (size_t)jrow[r] * D + ch * DPL + d8), kf + d8);
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) a = fmaf(kf[d], qreg[d], a);
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        a += __shfl_xor_sync(0xffffffffu, a, 4);
+        s[r] = valid[r] ? a : -CUDART_INF_F;
+      }
+    }
+    float mw = s[0];
+#pragma unroll
+    for (int r = 1; r < kKvRounds; ++r) mw = fmaxf(mw, s[r]);
+    mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, 8));
     mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, 16));
     const float mn = fmaxf(m, mw);
     if (mn == -CUDART_INF_F) return;           // nothing valid yet in this warp (warp-uniform)
-    const float alpha = __expf(m - mn), pr = __expf(s - mn);
+    const float alpha = __expf(m - mn);
     m = mn;
-    l = l * alpha + pr;
-    float vf[DPL];
+    l *= alpha;
 #pragma unroll
-    for (int d8 = 0; d8 < DPL; d8 += 8) unpack8(*reinterpret_cast<const uint4*>(vp + d8), vf + d8);
+    for (int d = 0; d < DPL; ++d) acc[d] *= alpha;
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) acc[d] = fmaf(pr, vf[d], acc[d] * alpha);
+    for (int r = 0; r < kKvRounds; ++r) {
+      if (r < R) {
+        const float pr = __expf(s[r] - mn);    // a masked slot: e^(-inf) = 0
+        l += pr;
+        float vf[DPL];
+#pragma unroll
+        for (int d8 = 0; d8 < DPL; d8 += 8)
+          unpack8(*reinterpret_cast<const uint4*>(vb + (size_t)jrow[r] * D + ch * DPL + d8), vf + d8);
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[d] = fmaf(pr, vf[d], acc[d]);
+      }
+    }
   };
 
   const int tps = kv_tokens_per_stage(p);
   const int nst = (pos + tps - 1) / tps;
+#ifdef B200_STEP_TRACE
+  long long waited = 0;
+#endif
   for (int st = 0; st < nst; ++st, advance(rp, c.p->ns)) {
     const int slot = rp.slot;
+#ifdef B200_STEP_TRACE
+    const long long w0 = now_ns();
+#endif
     const bool ok = wait_bar(c, c.full(slot), rp.parity, ERR_FULL);
+#ifdef B200_STEP_TRACE
+    waited += now_ns() - w0;
+#endif
     const half* kbase = reinterpret_cast<const half*>(c.stage(slot));
     const half* vbase = kbase + (size_t)tps * D;
-    const int nt = min(tps, pos - st * tps);
+    const int nt = min(tps, pos - st * tps);   // >= 1
     if (ok) {
-      for (int j0 = 4 * warp; j0 < nt; j0 += 4 * kNCW) {
-        const int j = j0 + ts;
-        const int jj = min(j, nt - 1);
-        fold(kbase + (size_t)jj * D + ch * DPL, vbase + (size_t)jj * D + ch * DPL, j < nt);
+      int jrow[kKvRounds];
+      bool valid[kKvRounds];
+#pragma unroll
+      for (int r = 0; r < kKvRounds; ++r) {
+        const int j = 4 * warp + ts + 4 * kNCW * r;
+        valid[r] = j < nt;
+        jrow[r] = min(j, nt - 1);
       }
+      const int R = (nt + 4 * kNCW - 1) / (4 * kNCW);   // rounds that hold a token of this stage (block-uniform)
+      fold(kbase, vbase, jrow, valid, R);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(c.empty(slot));
   }
-  if (warp == 0) fold(knew + ch * DPL, vnew + ch * DPL, ts == 0);   // the token of this step
+  if (warp == 0) {   // the token of this step: one more round of one slot
+    const int jrow[kKvRounds] = {};
+    bool valid[kKvRounds] = {};
+    valid[0] = ts == 0;
+    fold(knew, vnew, jrow, valid, 1);
+  }
   stamp(c, trace_at + 1);
+#ifdef B200_STEP_TRACE
+  stamp_value(c, trace_at + 4, waited);   // a duration: what warp 0 waited for the K/V stages
+#endif
 
   // merge: token slots inside the warp, then the warps
   float lw = l;
@@ -753,7 +864,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
 #ifdef B200_STEP_TRACE
   // trace row of a CTA: kTraceHead slots (0 = start, 1 = keys exchanged, 2 = token written), then per layer
   // kTracePerLayer: per phase {staged, first weights there, GEMV done, barrier passed, emitted}, then attention
-  // {q k v polled and rotated, cached tokens folded, warps merged and output stored, done};
+  // {q k v polled and rotated, cached tokens folded, warps merged and output stored, done, wait for K/V stages};
   // the LM head uses the slots of a layer L
   c.tr = p.trace ? p.trace + (size_t)cta * (kTraceHead + kTracePerLayer * (p.L + 1)) : nullptr;
 #endif

@@ -42,7 +42,7 @@ struct StepParams {
   half* logits;
   uint32_t* xchg;
   StepCtrl* ctrl;
-  long long* trace;   // [grid][8 + 24 (L + 1)] phase timestamps (ns); read only by builds with -DB200_STEP_TRACE
+  long long* trace;   // [grid][8 + 25 (L + 1)] phase timestamps (ns); read only by builds with -DB200_STEP_TRACE
   // shared-memory plan, computed on the host: byte offsets of the areas behind the header and the residual stream
   int off_xin, off_xsum, off_att, off_part, off_table, off_ring;
   int ups;               // tile-unit blocks (kTileUnitBytes each) per ring stage

@@ -8,8 +8,8 @@ tokens of a TinyLlama-shape model to fill the cache, then traces `reps` steps. P
 of a layer, the time spent up to each stamp since the one before, averaged over layers and steps, as the median over
 the CTAs and the slowest CTA:
     stage         x of the phase is staged (this includes waiting for the CTAs that produce it)
-    wait_weights  the first ring stage of the matrix is in shared memory
-    mma           this warp's tile-units are multiplied
+    wait_weights  time warp 0 spent waiting for the matrix's ring stages to land in shared memory (all stages)
+    mma           this warp's tile-units are multiplied (the interval up to the stamp, without those waits)
     barrier       all warps of the CTA have left their partial sums
     emit          the partial sums are added and the outputs stored
 and the attention phase on the CTAs that own a head (the others go straight on and wait in the next staging).
@@ -25,9 +25,10 @@ import torch
 from . import build as B
 from . import ext
 
-HEAD, PER_PHASE, N_ATT, MATS = 8, 5, 4, ("qkv", "o", "gate_up", "down")
+HEAD, PER_PHASE, N_ATT, MATS = 8, 5, 5, ("qkv", "o", "gate_up", "down")
 PER_LAYER = 4 * PER_PHASE + N_ATT
-ATT_STAMPS = ("q k v polled and rotated", "cached tokens folded", "merged and stored", "left")
+ATT_STAMPS = ("q k v polled and rotated", "cached tokens folded", "merged and stored", "left",
+              "of which waiting for K/V stages")
 STAMPS = ("stage", "wait_weights", "mma", "barrier", "emit")     # what ends at each of a phase's five stamps
 
 
@@ -65,17 +66,25 @@ def main():
         d = np.zeros((grid, L, PER_LAYER))
         # a layer's first stamp follows the kernel start or the last emit of the layer before
         prev = np.concatenate([t[:, :1], lay[:, :-1, G - 1]], axis=1)
+        waits = {}
         for i in range(G):
+            if i % PER_PHASE == 1:                  # a duration, not a time: what warp 0 waited for ring stages
+                waits[i] = lay[:, :, i]
+                continue
             if i == PER_PHASE:                      # o.stage follows attention where there is one, else the qkv emit
-                left = lay[:, :, PER_LAYER - 1]
+                left = lay[:, :, PER_LAYER - 2]
                 prev = np.where(left > 0, left, prev)
             cur = np.where(lay[:, :, i] > 0, lay[:, :, i], prev)   # a CTA without tiles of a matrix never waits for it
             d[:, :, i] = cur - prev
             prev = cur
+        for i, w in waits.items():                  # the wait is part of the interval that ends at the "mma" stamp
+            d[:, :, i] = w
+            d[:, :, i + 1] -= w
         prev = lay[:, :, PER_PHASE - 1]             # attention follows the qkv emit
-        for i in range(G, PER_LAYER):
+        for i in range(G, PER_LAYER - 1):
             d[:, :, i] = np.where(lay[:, :, i] > 0, lay[:, :, i] - prev, 0.0)
             prev = lay[:, :, i]
+        d[:, :, PER_LAYER - 1] = lay[:, :, PER_LAYER - 1]   # a duration
         acc.append(d)
         totals.append((t[0, 2] - t[:, 0].min()) / 1e3)
     assert m.step_error() == 0, m.step_error()
