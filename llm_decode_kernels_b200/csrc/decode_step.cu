@@ -662,29 +662,27 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
 #pragma unroll
   for (int d = 0; d < DPL; ++d) acc[d] = 0.f;
 
-  // Fold R rounds of 4 tokens per warp (token slot ts of round r: row jrow[r] of kb / vb, counted if valid[r]) into the
-  // warp's online-softmax state. The R scores are computed independently and share ONE max / rescale step, so a ring
-  // stage costs one dependent chain (loads, dot product, shuffles, exponentials, accumulate) whatever its token
-  // count. A slot that is not valid repeats a real row (its score is masked): rows past the stage's tokens may hold
-  // stale bytes of the ring, NaN patterns among them, and 0 * NaN would poison the sum.
-  auto fold = [&](const half* kb, const half* vb, const int (&jrow)[kKvRounds], const bool (&valid)[kKvRounds],
-                  const int R) {
+  // Fold kKvRounds rounds of 4 tokens per warp into the warp's online-softmax state. Round r, token slot ts: the K row
+  // at byte koff[r] of shared memory, the V row at voff[r], counted if valid[r] (a slot that is not valid reads this
+  // step's own k, v - real data, masked by its score; stale bytes of the ring could be NaN patterns, and 0 * NaN
+  // would poison the sum). The scores of all rounds are computed independently and share ONE max / rescale step, so
+  // a ring stage costs one dependent chain (loads, dot product, shuffles, exponentials, accumulate) whatever its
+  // token count; the round count is fixed so that the chain carries no predicates.
+  auto fold = [&](const uint32_t (&koff)[kKvRounds], const uint32_t (&voff)[kKvRounds], const bool (&valid)[kKvRounds]) {
     float s[kKvRounds];
 #pragma unroll
     for (int r = 0; r < kKvRounds; ++r) {
-      s[r] = -CUDART_INF_F;
-      if (r < R) {
-        float kf[DPL], a = 0.f;
+      const half* kp = reinterpret_cast<const half*>(c.smem + koff[r]);
+      float kf[DPL], a0 = 0.f, a1 = 0.f;
 #pragma unroll
-        for (int d8 = 0; d8 < DPL; d8 += 8)
-          unpack8(*reinterpret_cast<const uint4*>(kb + (size_t)jrow[r] * D + ch * DPL + d8), kf + d8);
+      for (int d8 = 0; d8 < DPL; d8 += 8) unpack8(*reinterpret_cast<const uint4*>(kp + d8), kf + d8);
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) a = fmaf(kf[d], qreg[d], a);
-        a += __shfl_xor_sync(0xffffffffu, a, 1);
-        a += __shfl_xor_sync(0xffffffffu, a, 2);
-        a += __shfl_xor_sync(0xffffffffu, a, 4);
-        s[r] = valid[r] ? a : -CUDART_INF_F;
-      }
+      for (int d = 0; d < DPL; d += 2) { a0 = fmaf(kf[d], qreg[d], a0); a1 = fmaf(kf[d + 1], qreg[d + 1], a1); }
+      float a = a0 + a1;
+      a += __shfl_xor_sync(0xffffffffu, a, 1);
+      a += __shfl_xor_sync(0xffffffffu, a, 2);
+      a += __shfl_xor_sync(0xffffffffu, a, 4);
+      s[r] = valid[r] ? a : -CUDART_INF_F;
     }
     float mw = s[0];
 #pragma unroll
@@ -700,56 +698,58 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
     for (int d = 0; d < DPL; ++d) acc[d] *= alpha;
 #pragma unroll
     for (int r = 0; r < kKvRounds; ++r) {
-      if (r < R) {
-        const float pr = __expf(s[r] - mn);    // a masked slot: e^(-inf) = 0
-        l += pr;
-        float vf[DPL];
+      const half* vp = reinterpret_cast<const half*>(c.smem + voff[r]);
+      const float pr = __expf(s[r] - mn);      // a masked slot: e^(-inf) = 0
+      l += pr;
+      float vf[DPL];
 #pragma unroll
-        for (int d8 = 0; d8 < DPL; d8 += 8)
-          unpack8(*reinterpret_cast<const uint4*>(vb + (size_t)jrow[r] * D + ch * DPL + d8), vf + d8);
+      for (int d8 = 0; d8 < DPL; d8 += 8) unpack8(*reinterpret_cast<const uint4*>(vp + d8), vf + d8);
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[d] = fmaf(pr, vf[d], acc[d]);
-      }
+      for (int d = 0; d < DPL; ++d) acc[d] = fmaf(pr, vf[d], acc[d]);
     }
   };
 
+  // The cached tokens come stage by stage from the ring. The token of this step (rotated k, v in the attention
+  // scratch) rides along as token number nt of the last stage: a stage holds at most kMaxKvTokens tokens and the
+  // warps' slots cover 4 kNCW kKvRounds > kMaxKvTokens, so there is always a slot for it and it costs no chain of its own.
+  static_assert(4 * kNCW * kKvRounds > kMaxKvTokens, "the last stage needs a spare slot for the token of this step");
   const int tps = kv_tokens_per_stage(p);
   const int nst = (pos + tps - 1) / tps;
+  const uint32_t knew_off = (uint32_t)(reinterpret_cast<const uint8_t*>(knew) - c.smem) + ch * DPL * 2;
+  const uint32_t vnew_off = (uint32_t)(reinterpret_cast<const uint8_t*>(vnew) - c.smem) + ch * DPL * 2;
 #ifdef B200_STEP_TRACE
   long long waited = 0;
 #endif
-  for (int st = 0; st < nst; ++st, advance(rp, c.p->ns)) {
+  for (int st = 0; st < max(nst, 1); ++st) {
+    const bool have = st < nst, last = st >= nst - 1;   // nst == 0 (empty cache): one pass without a ring stage
     const int slot = rp.slot;
 #ifdef B200_STEP_TRACE
     const long long w0 = now_ns();
 #endif
-    const bool ok = wait_bar(c, c.full(slot), rp.parity, ERR_FULL);
+    const bool ok = have ? wait_bar(c, c.full(slot), rp.parity, ERR_FULL) : true;
 #ifdef B200_STEP_TRACE
     waited += now_ns() - w0;
 #endif
-    const half* kbase = reinterpret_cast<const half*>(c.stage(slot));
-    const half* vbase = kbase + (size_t)tps * D;
-    const int nt = min(tps, pos - st * tps);   // >= 1
+    const uint32_t kbase = c.p->off_ring + (uint32_t)slot * c.p->stage_bytes + ch * DPL * 2;
+    const uint32_t vbase = kbase + (uint32_t)tps * D * 2;
+    const int nt = have ? min(tps, pos - st * tps) : 0;
     if (ok) {
-      int jrow[kKvRounds];
+      uint32_t koff[kKvRounds], voff[kKvRounds];
       bool valid[kKvRounds];
 #pragma unroll
       for (int r = 0; r < kKvRounds; ++r) {
         const int j = 4 * warp + ts + 4 * kNCW * r;
-        valid[r] = j < nt;
-        jrow[r] = min(j, nt - 1);
+        valid[r] = j < nt || (last && j == nt);
+        koff[r] = j < nt ? kbase + (uint32_t)j * (D * 2) : knew_off;
+        voff[r] = j < nt ? vbase + (uint32_t)j * (D * 2) : vnew_off;
       }
-      const int R = (nt + 4 * kNCW - 1) / (4 * kNCW);   // rounds that hold a token of this stage (block-uniform)
-      fold(kbase, vbase, jrow, valid, R);
+      fold(koff, voff, valid);
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(c.empty(slot));
-  }
-  if (warp == 0) {   // the token of this step: one more round of one slot
-    const int jrow[kKvRounds] = {};
-    bool valid[kKvRounds] = {};
-    valid[0] = ts == 0;
-    fold(knew, vnew, jrow, valid, 1);
+    if (have) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(c.empty(slot));
+      advance(rp, c.p->ns);
+    }
   }
   stamp(c, trace_at + 1);
 #ifdef B200_STEP_TRACE
