@@ -122,3 +122,26 @@ def calibrate(hf, tok, group=128, clip=False, n=128, L=512, lm_head=True, log=pr
         m.weight.data.copy_(w.to(dev))
     log(f"gptq done: {time.time() - t0:.0f}s, {len(result)} matrices")
     return result
+
+
+def calibrate_cached(hf, tok, cache_dir, group=128, clip=False, n=128, L=512, lm_head=True, seed=0, log=print):
+    """calibrate() behind the on-disk cache of checkpoint.cached_qparams: the key names the model's shapes, the group
+    size, the clipping switch and the calibration set (windows, length, seed), so a second run with the same settings
+    loads the parameters instead of calibrating for minutes. The calibration windows are this module's
+    `calibration_windows` with the given seed."""
+    from . import checkpoint
+    c = hf.config
+    key = checkpoint.qparams_key(hidden=c.hidden_size, layers=c.num_hidden_layers, heads=c.num_attention_heads,
+                                 kv_heads=c.num_key_value_heads, inter=c.intermediate_size, vocab=c.vocab_size,
+                                 group=group, clip=clip, n=n, L=L, lm_head=lm_head, seed=seed,
+                                 weights=_fingerprint(hf))
+    return checkpoint.cached_qparams(cache_dir, key,
+                                     lambda: calibrate(hf, tok, group=group, clip=clip, n=n, L=L, lm_head=lm_head, log=log))
+
+
+def _fingerprint(hf):
+    """A cheap identity of the weights being calibrated: sums of a few tensors (the cache must not hand the
+    parameters of one checkpoint to another of the same shape)."""
+    sd = hf.state_dict()
+    keys = sorted(sd)[:: max(1, len(sd) // 8)]
+    return [round(float(sd[k].float().sum()), 4) for k in keys]

@@ -34,7 +34,9 @@ class DecodeConfig:
     weights: str = "int4"        # only "int4" (W4A16) exists in this runtime
     group: int = 128
     quant: str = "rtn"           # "rtn" | "clip" (RTN + per-group range clipping) | "pre" (use `qparams`, e.g. GPTQ)
-    qparams: dict = field(default=None, repr=False)  # "layers.{i}.{qkv,o,gu,down}" / "lm_head" -> (q, scale, zero)
+                                 # | "packed" (`qparams` holds matrices already in kernel format, see checkpoint.py)
+    qparams: dict = field(default=None, repr=False)  # "layers.{i}.{qkv,o,gu,down}" / "lm_head" -> (q, scale, zero);
+                                 # with quant="packed": -> (packed int32 [N, K/8], sz fp16 [N, K/group, 2])
     lm_head: str = "auto"        # "auto" / "int4": INT4 head (the only kind here)
     fused: bool = True           # False: residual add, RMSNorm and SwiGLU run as separate torch ops (ablation)
     backend: str = "cuda"        # only "cuda"
@@ -80,9 +82,23 @@ PERSISTENT_MAX_CTX = 2048   # beyond this the in-kernel attention (one CTA per q
 class Linear:
     """One W4A16 projection in kernel format (reference runtime/model.py:56-72)."""
 
-    def __init__(self, w, cfg: DecodeConfig, key: str = None, keep_ref: bool = False, pre=None):
-        self.N, self.K = w.shape
+    def __init__(self, w, cfg: DecodeConfig, key: str = None, keep_ref: bool = False, pre=None, packed=None):
         self.quant = True
+        self.tiled = None            # tile-layout copy, made by Model when DecodeConfig.tile_weights is set
+        self.paired = False          # the copy pairs gate row i with up row i (GEMV with SwiGLU epilogue)
+        if packed is not None:       # already in kernel format: nothing to quantize
+            pk, sz = packed
+            if pk.dtype != torch.int32 or sz.dtype != torch.float16 or sz.dim() != 3 or sz.shape[2] != 2:
+                raise ValueError(f"{key}: packed weights must be int32 [N, K/8] with fp16 (scale, zero) [N, K/group, 2]")
+            self.N, self.K = pk.shape[0], pk.shape[1] * 8
+            if sz.shape[0] != self.N or sz.shape[1] * cfg.group != self.K:
+                raise ValueError(f"{key}: scale/zero shape {tuple(sz.shape)} does not match {self.N} x {self.K}, "
+                                 f"group {cfg.group}")
+            self.packed, self.sz = pk.to(cfg.device).contiguous(), sz.to(cfg.device).contiguous()
+            self.w_ref = None
+            self.nbytes = self.packed.numel() * 4 + self.sz.numel() * 2
+            return
+        self.N, self.K = w.shape
         if cfg.quant == "pre" and pre is None:
             pre = (cfg.qparams or {}).get(key)
             assert pre is not None, f"no precomputed weights for {key}"
@@ -90,8 +106,6 @@ class Linear:
         self.packed, self.sz = ql.packed.to(cfg.device), ql.sz.to(cfg.device)
         self.w_ref = ql.w_ref
         self.nbytes = ql.nbytes()
-        self.tiled = None            # tile-layout copy, made by Model when DecodeConfig.tile_weights is set
-        self.paired = False          # the copy pairs gate row i with up row i (GEMV with SwiGLU epilogue)
 
     def drop_packed(self):
         """Free the row-major tensors once the tile-layout copy exists (DecodeConfig.keep_packed=False)."""
@@ -158,25 +172,34 @@ class Model:
                     lin.drop_packed()
             return lin
 
+        have_packed = cfg.quant == "packed"
+        if have_packed and not cfg.qparams:
+            raise ValueError("quant='packed' needs qparams = {name: (packed, sz)} (checkpoint.load_quantized)")
+
+        def lin(kind, key, weights, gate_up=False):
+            """One projection: from its kernel-format tensors when the configuration brings them (the fp16 weights
+            are then never asked for), else quantized from weights()."""
+            if have_packed:
+                return finish(Linear(None, cfg, key, packed=TP.shard_packed(kind, cfg.qparams[key], full, cfg.group,
+                                                                            self.tp_rank, self.tp)), gate_up)
+            return finish(Linear(shard(kind, weights()), cfg, key, pre=pre(kind, key)), gate_up)
+
         self.layers = []
         for i in range(self.L):
             p = f"model.layers.{i}."
-            wqkv = torch.cat([g(p + "self_attn.q_proj.weight"), g(p + "self_attn.k_proj.weight"),
-                              g(p + "self_attn.v_proj.weight")], 0)
-            wgu = torch.cat([g(p + "mlp.gate_proj.weight"), g(p + "mlp.up_proj.weight")], 0)
             self.layers.append({
                 "ln1": g(p + "input_layernorm.weight").contiguous(),
                 "ln2": g(p + "post_attention_layernorm.weight").contiguous(),
-                "qkv": finish(Linear(shard("qkv", wqkv), cfg, f"layers.{i}.qkv", pre=pre("qkv", f"layers.{i}.qkv"))),
-                "o": finish(Linear(shard("o", g(p + "self_attn.o_proj.weight")), cfg, f"layers.{i}.o",
-                                   pre=pre("o", f"layers.{i}.o"))),
-                "gu": finish(Linear(shard("gu", wgu), cfg, f"layers.{i}.gu", pre=pre("gu", f"layers.{i}.gu")), True),
-                "down": finish(Linear(shard("down", g(p + "mlp.down_proj.weight")), cfg, f"layers.{i}.down",
-                                      pre=pre("down", f"layers.{i}.down")))})
-            del wqkv, wgu
+                "qkv": lin("qkv", f"layers.{i}.qkv", lambda: torch.cat([g(p + "self_attn.q_proj.weight"),
+                                                                        g(p + "self_attn.k_proj.weight"),
+                                                                        g(p + "self_attn.v_proj.weight")], 0)),
+                "o": lin("o", f"layers.{i}.o", lambda: g(p + "self_attn.o_proj.weight")),
+                "gu": lin("gu", f"layers.{i}.gu", lambda: torch.cat([g(p + "mlp.gate_proj.weight"),
+                                                                     g(p + "mlp.up_proj.weight")], 0), True),
+                "down": lin("down", f"layers.{i}.down", lambda: g(p + "mlp.down_proj.weight"))})
         self.norm_f = g("model.norm.weight").contiguous()
-        lm = sd["lm_head.weight"] if "lm_head.weight" in sd else sd["model.embed_tokens.weight"]
-        self.lm_head = finish(Linear(shard("lm_head", lm.to(dev).half()), cfg, "lm_head", pre=pre("lm_head", "lm_head")))
+        head_key = "lm_head.weight" if "lm_head.weight" in sd else "model.embed_tokens.weight"
+        self.lm_head = lin("lm_head", "lm_head", lambda: sd[head_key].to(dev).half())
 
         # paged KV cache [L, 2, pages, n_kv, P, D]; one block table shared by all layers (one sequence)
         self.n_pages = (cfg.max_ctx + cfg.page - 1) // cfg.page + 1
@@ -186,7 +209,8 @@ class Model:
             self.bt = torch.randperm(self.n_pages, generator=gen).int().to(dev)
         else:
             self.bt = torch.arange(self.n_pages).int().to(dev)
-        self.cos, self.sin = (t.to(dev) for t in rope_tables(cfg.max_ctx + 1, self.D, _rope_theta(c)))
+        self.rope_theta = _rope_theta(c)
+        self.cos, self.sin = (t.to(dev) for t in rope_tables(cfg.max_ctx + 1, self.D, self.rope_theta))
 
         # device-resident decode state and static activation buffers
         h16 = dict(dtype=torch.half, device=dev)
@@ -231,6 +255,16 @@ class Model:
         self.norm_in_gemv = (cfg.fuse_norm_gemv and self.tp == 1 and not self.off
                              and all(lin.tiled is not None for lin in heads))
         self.set_attention_partition(cfg.max_ctx)
+
+    @classmethod
+    def from_quantized(cls, path, cfg: DecodeConfig = None, **overrides):
+        """Build the runtime from a directory written by checkpoint.save_quantized: no quantizer runs, the packed
+        tensors go to the device as they are (each rank of a tensor-parallel group cuts its own shard)."""
+        import dataclasses
+        from . import checkpoint
+        c, group, state, qparams = checkpoint.load_quantized(path)
+        cfg = dataclasses.replace(cfg or DecodeConfig(), group=group, quant="packed", qparams=qparams, **overrides)
+        return cls(state, c, cfg)
 
     # ------------------------------------------------------------------ attention partitioning
     def _policy_table(self):

@@ -102,6 +102,27 @@ def shard_qsz(kind, qsz, dims, group, rank, world):
     return q[:, a:b].contiguous(), s[:, a // group:b // group].contiguous(), z[:, a // group:b // group].contiguous()
 
 
+def shard_packed(kind, psz, dims, group, rank, world):
+    """The same slicing applied to a matrix in kernel format: (packed int32 [N, K/8], sz fp16 [N, K/G, 2]). Column
+    slices fall on group boundaries, which are word boundaries too (a group is a multiple of 8 weights)."""
+    if world == 1 or psz is None:
+        return psz
+    n_q, n_kv, D, I, V = dims
+    packed, sz = psz
+    if kind in ("qkv", "gu", "lm_head"):
+        if kind == "qkv":
+            rows = qkv_rows(n_q, n_kv, D, rank, world)
+        elif kind == "gu":
+            rows = gate_up_rows(I, rank, world)
+        else:
+            rows = torch.arange(*part(V, rank, world, "vocabulary"))
+        return shard_rows(packed, rows), shard_rows(sz, rows)
+    a, b = (x * D for x in part(n_q, rank, world)) if kind == "o" else part(I, rank, world)
+    if a % group or b % group:
+        raise ValueError("a column slice would cut a quantization group")
+    return packed[:, a // 8:b // 8].contiguous(), sz[:, a // group:b // group].contiguous()
+
+
 # ---- exchange over NVLink peer memory ------------------------------------------------------------------------------
 class _RawCuda:
     """Minimal __cuda_array_interface__ carrier, so torch can wrap memory the exchange block owns."""
