@@ -178,9 +178,10 @@ def peak_hbm_gbs():
 
 
 # Measured with ncu on the same kernel, TinyLlama shape cut to 6 layers (profiles/decode_step_kernel_tinyllama_6layers.md):
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch over the algorithmic bytes of that launch. Traffic grows
-# with the layers in proportion to the bytes, so the 22-layer figure is this ratio times the step's bytes.
-STEP_TRAFFIC_OVER_ALGORITHMIC = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch (175,900,160 + 4,468,992) over the algorithmic bytes of
+# that launch (6 layers + LM head + embedding row + KV at context 40: 175,499,264). Traffic grows with the layers in
+# proportion to the bytes, so the 22-layer figure is this ratio times the step's bytes.
+STEP_TRAFFIC_OVER_ALGORITHMIC = 180369152 / 175499264
 
 
 def parity_gate(dev, step_kernel, n_tokens=40):

@@ -18,6 +18,10 @@ cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, in
                                       cudaStream_t st);
 cudaError_t gemv_w4a16_tiled_norm_dispatch(const void* Wt, const void* x_in, const void* delta, const void* norm_w,
                                            float eps, void* x_out, void* y, int N, int K, int swiglu, cudaStream_t st);
+cudaError_t gemv_w4a16_tiled_allreduce_dispatch(const void* Wt, const void* x, void* y, int N, int K,
+                                                const void* const* peers, int rank, int W, size_t slot_off,
+                                                cudaStream_t st);
+size_t gemv_allreduce_slot_bytes(int N, int W);
 cudaError_t dequant_w4a16_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G,
                                    cudaStream_t st);
 cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int H, float eps,
@@ -415,6 +419,25 @@ int b200_tp_allreduce_add_rmsnorm(const void* const* peers, int rank, int W, siz
   REQUIRE(H <= 32768, B200_ERR_LIMIT);
   REQUIRE(aligned16(x) && aligned16(w) && aligned16(out), B200_ERR_ALIGN);
   return finish(b200::tp_allreduce_add_rmsnorm_dispatch(peers, rank, W, slot_off, x, w, out, H, eps, S(stream)));
+}
+
+size_t b200_tp_gemv_slot_bytes(int N, int W) {
+  if (N <= 0 || W < 1 || W > b200::comm_max_ranks()) return 0;
+  return b200::gemv_allreduce_slot_bytes(N, W);
+}
+
+int b200_gemv_w4a16_tiled_allreduce(const void* Wt, const void* x, void* y, int N, int K, const void* const* peers,
+                                    int rank, int W, size_t slot_off, void* stream) {
+  REQUIRE(Wt && x && y && N > 0 && K > 0, B200_ERR_ARG);
+  REQUIRE(K % 128 == 0 && N % 8 == 0, B200_ERR_SHAPE);
+  REQUIRE(K <= 65536, B200_ERR_LIMIT);
+  REQUIRE(peers && W >= 1 && W <= b200::comm_max_ranks() && rank >= 0 && rank < W, B200_ERR_ARG);
+  REQUIRE(slot_off >= (size_t)b200::comm_header_bytes() && slot_off % 256 == 0, B200_ERR_ALIGN);
+  for (int r = 0; r < W; ++r) REQUIRE(peers[r] && aligned16(peers[r]), B200_ERR_ARG);
+  REQUIRE(aligned16(Wt) && (reinterpret_cast<uintptr_t>(x) & 7u) == 0 && aligned16(y), B200_ERR_ALIGN);
+  const cudaError_t e = b200::gemv_w4a16_tiled_allreduce_dispatch(Wt, x, y, N, K, peers, rank, W, slot_off, S(stream));
+  if (e == cudaErrorInvalidValue) return B200_ERR_LIMIT;   // more tile groups than the slot has flag rows
+  return finish(e);
 }
 
 int b200_tp_allgather(const void* const* peers, int rank, int W, size_t slot_off, void* dst, int n, void* stream) {

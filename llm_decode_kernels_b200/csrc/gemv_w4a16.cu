@@ -23,6 +23,7 @@
 // not to each weight; `dequant_w4a16` below materialises the per-element weights for the bit-exact
 // check of the format.
 #include "common.cuh"
+#include "tp_comm.cuh"
 
 namespace b200 {
 
@@ -374,10 +375,26 @@ struct NormArgs {
   float eps;
 };
 
-template <bool TILED, bool SWIGLU, bool NORM>
+//
+// ALLRED = true (tile layout, tensor-parallel row-split projections o_proj / down_proj): the kernel's rows are this
+// rank's PARTIAL sums, and the all-reduce over the ranks happens here, tile group by tile group, instead of in a
+// kernel of its own. The block that has computed a tile group's rows
+//   1. rounds them to fp16 and pushes them, 16 bytes at a time, into slot data[rank] of EVERY rank's exchange block
+//      (its own included): plain peer stores over NVLink,
+//   2. tells every peer "my rows of group g, call number c, are with you" (release store into the peer's flag word
+//      flags[g][rank]) and waits until every peer has said the same (acquire loads of the local flag words, bounded),
+//   3. adds the W copies - all in LOCAL memory by now - in rank order with fp32 accumulation, rounds once, and stores
+//      the sum to y. Every rank adds the same numbers in the same order: the sums are bit-identical on all ranks.
+// The block of the same index on each peer does the same for the same rows, so nobody waits for anything that depends
+// on this GPU's scheduling; the wait is one NVLink round trip, overlapped over all blocks of the grid. Slot reuse:
+// a rank reaches call c + 1 on a slot only after another exchange has completed in between (the o_proj and down_proj
+// slots alternate, and the logits gather follows the last layer), which every peer can only have joined after it was
+// done reading this slot. N % 8 == 0. A wait that runs out sets the block's error word and leaves y's rows alone.
+template <bool TILED, bool SWIGLU, bool NORM, bool ALLRED>
 __global__ void __launch_bounds__(kMmaGemvThreads, 2)
 gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ, const uint2* __restrict__ X,
-                      half* __restrict__ y, int N, int K, int log2G, int ksplit, int rounds, const NormArgs na) {
+                      half* __restrict__ y, int N, int K, int log2G, int ksplit, int rounds, const NormArgs na,
+                      const AllReduceArgs ar) {
   extern __shared__ __align__(16) uint8_t mma_smem[];
   const int nunit = K >> 7;                                                // 128-weight units per row
   uint4* xin = reinterpret_cast<uint4*>(mma_smem);                         // [K/8] staged x, 16 bytes = one word's 8
@@ -560,10 +577,14 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
       const float gf = __half2float(hg);
       return __hmul(__float2half(gf / (1.f + expf(-gf))), hu);
     };
+    __shared__ __align__(16) half rowbuf[kMmaGemvWarps * 16];   // ALLRED: the round's rows, in row order
     if (ksplit == 1) {
       if (t == 0 && tile < ntiles) {
         if (SWIGLU) {
           if (8 * tile + g < N) y[8 * tile + g] = gated(ya, yb);
+        } else if (ALLRED) {
+          rowbuf[16 * warp + g] = __float2half(ya);
+          rowbuf[16 * warp + g + 8] = __float2half(yb);
         } else {
           const int ra = 16 * tile + g, rb = ra + 8;
           if (ra < N) y[ra] = __float2half(ya);
@@ -582,11 +603,85 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
         }
         if (SWIGLU) {
           if (row < 8 && tl < ntiles && 8 * tl + row < N) y[8 * tl + row] = gated(v, v8);
+        } else if (ALLRED) {
+          rowbuf[tid] = __float2half(v);
         } else if (tl < ntiles && 16 * tl + row < N) {
           y[16 * tl + row] = __float2half(v);
         }
       }
+      if (!ALLRED) __syncthreads();
+    }
+    if (ALLRED) {
+      // this round's tile group: tiles [gidx * tpr, (gidx + 1) * tpr), rows from row0 on, `nchunk` pieces of 8 rows
+      __shared__ uint32_t call_s;
+      __shared__ int failed_s;
+      const int gidx = r * gridDim.x + blockIdx.x, row0 = 16 * gidx * tiles_per_round;
+      const int nrows = max(0, min(N - row0, 16 * tiles_per_round)), nchunk = nrows >> 3;
+      uint8_t* mine = ar.P.p[ar.rank] + ar.off;
+      if (tid == 0) {
+        call_s = *reinterpret_cast<volatile uint32_t*>(mine) + 1u;   // read after the wait on the previous kernel
+        failed_s = 0;
+      }
+      __syncthreads();   // rowbuf complete, call number known
+      const uint32_t call = call_s;
+      const size_t data_off = ar.off + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + ((size_t)ar.rank * N + row0) * 2;
+      for (int i = tid; i < nchunk * ar.W; i += kMmaGemvThreads) {
+        const int p = i / nchunk, c = i - p * nchunk;
+        st_peer16(ar.P.p[p] + data_off + 16 * (size_t)c, reinterpret_cast<const uint4*>(rowbuf)[c]);
+      }
+      __syncthreads();   // every push of this block is issued before any of its flags
+      if (tid < ar.W && tid != ar.rank && nchunk > 0) {
+        __threadfence_system();
+        const size_t flag_off = ar.off + kGemvSlotCtrlBytes + ((size_t)gidx * kCommMaxRanks) * 4;
+        st_release_sys(reinterpret_cast<uint32_t*>(ar.P.p[tid] + flag_off) + ar.rank, call);
+        const uint32_t* here = reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + flag_off) + tid;
+        const uint32_t set_limit = *reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + kCommLimitOff);
+        const int limit = set_limit ? (int)set_limit : kCommSpinLimit;
+        int spins = 0;
+        while ((int32_t)(ld_acquire_sys(here) - call) < 0) {
+          if (++spins > limit) {
+            failed_s = 1;
+            atomicExch(reinterpret_cast<uint32_t*>(ar.P.p[ar.rank] + kCommErrorOff), COMM_ERR_PEER_WAIT);
+            break;
+          }
+          if (spins > 256) __nanosleep(200);
+        }
+      }
       __syncthreads();
+      if (!failed_s) {
+        const uint8_t* base = mine + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + (size_t)row0 * 2;
+        for (int c = tid; c < nchunk; c += kMmaGemvThreads) {
+          float acc[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+          for (int q = 0; q < ar.W; ++q) {
+            float f[8];
+            unpack8(ld_peer16(base + (size_t)q * N * 2 + 16 * (size_t)c), f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += f[k];
+          }
+          uint4 o;
+          o.x = as_u32(__floats2half2_rn(acc[0], acc[1]));
+          o.y = as_u32(__floats2half2_rn(acc[2], acc[3]));
+          o.z = as_u32(__floats2half2_rn(acc[4], acc[5]));
+          o.w = as_u32(__floats2half2_rn(acc[6], acc[7]));
+          reinterpret_cast<uint4*>(y + row0)[c] = o;
+        }
+      }
+      __syncthreads();   // rowbuf, part and the shared words are free for the next round
+    }
+  }
+  if (ALLRED) {
+    // the last block to finish closes the call: the slot's call counter moves on, the ticket goes back to zero
+    uint32_t* ctrl = reinterpret_cast<uint32_t*>(ar.P.p[ar.rank] + ar.off);
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(ctrl + 1, 1u) == gridDim.x - 1) {
+        ctrl[1] = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(ctrl) = *reinterpret_cast<volatile uint32_t*>(ctrl) + 1u;
+      }
     }
   }
 }
@@ -615,7 +710,8 @@ bool gemv_mma_tune(int mode, int N, int K, int ksplit, int blocks) {
 
 // mode 0: row-major tensors; 1: tile layout; 2: tile layout of a [gate; up] matrix with the SwiGLU epilogue (N outputs)
 static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const void* x, void* y, int N, int K,
-                              int log2G, cudaStream_t st, const NormArgs* norm = nullptr) {
+                              int log2G, cudaStream_t st, const NormArgs* norm = nullptr,
+                              const AllReduceArgs* allred = nullptr) {
   const int ntiles = mode == 2 ? (N + 7) / 8 : (N + 15) / 16, nunit = K / 128;
   // ksplit warps share a row tile: the smallest split that gives the chip enough warps (measured: with enough tiles
   // a warp per tile, no barrier, is as fast as any split; short of tiles, splitting K wins), as long as a warp keeps
@@ -644,10 +740,11 @@ static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const vo
     if (e != cudaSuccess) return e;
     const bool tracked = dev >= 0 && dev < kMaxDevices;
     if (smem > 48 * 1024 && !(tracked && smem <= allowed[dev])) {   // all variants share one per-device record
-      void (*all[])(const uint4*, const half2*, const uint2*, half*, int, int, int, int, int, const NormArgs) = {
-          gemv_w4a16_mma_kernel<false, false, false>, gemv_w4a16_mma_kernel<true, false, false>,
-          gemv_w4a16_mma_kernel<true, true, false>, gemv_w4a16_mma_kernel<true, false, true>,
-          gemv_w4a16_mma_kernel<true, true, true>};
+      void (*all[])(const uint4*, const half2*, const uint2*, half*, int, int, int, int, int, const NormArgs,
+                    const AllReduceArgs) = {
+          gemv_w4a16_mma_kernel<false, false, false, false>, gemv_w4a16_mma_kernel<true, false, false, false>,
+          gemv_w4a16_mma_kernel<true, true, false, false>,   gemv_w4a16_mma_kernel<true, false, true, false>,
+          gemv_w4a16_mma_kernel<true, true, true, false>,    gemv_w4a16_mma_kernel<true, false, false, true>};
       for (auto k : all)
         if (e == cudaSuccess) e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
@@ -655,20 +752,25 @@ static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const vo
     }
   }
   const NormArgs na = norm ? *norm : NormArgs{nullptr, nullptr, nullptr, 0.f};
-  auto kern = mode == 0 ? gemv_w4a16_mma_kernel<false, false, false>
-              : norm    ? (mode == 2 ? gemv_w4a16_mma_kernel<true, true, true> : gemv_w4a16_mma_kernel<true, false, true>)
-                        : (mode == 2 ? gemv_w4a16_mma_kernel<true, true, false> : gemv_w4a16_mma_kernel<true, false, false>);
+  const AllReduceArgs ar = allred ? *allred : AllReduceArgs{};
+  if (allred && (mode != 1 || norm || rounds * blocks > kCommMaxGroups || N % 8)) return cudaErrorInvalidValue;
+  auto kern = mode == 0 ? gemv_w4a16_mma_kernel<false, false, false, false>
+              : allred  ? gemv_w4a16_mma_kernel<true, false, false, true>
+              : norm    ? (mode == 2 ? gemv_w4a16_mma_kernel<true, true, true, false>
+                                     : gemv_w4a16_mma_kernel<true, false, true, false>)
+                        : (mode == 2 ? gemv_w4a16_mma_kernel<true, true, false, false>
+                                     : gemv_w4a16_mma_kernel<true, false, false, false>);
   // Dependent launch pays for the small matrices of a step and costs on large ones (the kernel then runs slower than
   // with an ordinary launch): matrices beyond 64 MB are launched the ordinary way.
   constexpr size_t pdl_max_mb = 64;
   const size_t weight_bytes = (size_t)(mode == 2 ? 2 * N : N) * K / 2;
   if (weight_bytes > (pdl_max_mb << 20)) {
     kern<<<blocks, kMmaGemvThreads, smem, st>>>((const uint4*)Wp, (const half2*)SZ, (const uint2*)x, (half*)y, N, K,
-                                                log2G, ksplit, rounds, na);
+                                                log2G, ksplit, rounds, na, ar);
     return cudaPeekAtLastError();
   }
   return launch_pdl(kern, dim3(blocks), dim3(kMmaGemvThreads), smem, st, (const uint4*)Wp, (const half2*)SZ,
-                    (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds, na);
+                    (const uint2*)x, (half*)y, N, K, log2G, ksplit, rounds, na, ar);
 }
 
 // ---- tile layout -------------------------------------------------------------------------------------------------------
@@ -719,6 +821,20 @@ cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, in
                                       cudaStream_t st) {
   return launch_mma(swiglu ? 2 : 1, Wt, nullptr, x, y, N, K, 7, st);
 }
+
+// y = all-reduce over the W ranks of (this rank's W x): the ALLRED form of the kernel. peers[r] = rank r's exchange
+// block as this process sees it, slot_off = offset of a GEMV slot (gemv_slot_bytes) inside every block.
+cudaError_t gemv_w4a16_tiled_allreduce_dispatch(const void* Wt, const void* x, void* y, int N, int K,
+                                                const void* const* peers, int rank, int W, size_t slot_off,
+                                                cudaStream_t st) {
+  AllReduceArgs ar = {};
+  for (int r = 0; r < W; ++r) ar.P.p[r] = (uint8_t*)peers[r];
+  ar.rank = rank;
+  ar.W = W;
+  ar.off = slot_off;
+  return launch_mma(1, Wt, nullptr, x, y, N, K, 7, st, nullptr, &ar);
+}
+size_t gemv_allreduce_slot_bytes(int N, int W) { return gemv_slot_bytes(N, W); }
 
 // residual add + RMSNorm + GEMV (+ SwiGLU) in one launch: see NormArgs
 cudaError_t gemv_w4a16_tiled_norm_dispatch(const void* Wt, const void* x_in, const void* delta, const void* norm_w,

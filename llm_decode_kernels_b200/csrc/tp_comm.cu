@@ -21,45 +21,11 @@
 // Every wait is bounded (about four seconds by default, enough for ranks that drift apart between host-driven
 // steps; a caller may store a shorter bound in the block's header). A wait that runs out stores a code in the
 // block's error word, and the kernel returns without touching the outputs.
-#include "common.cuh"
+#include "tp_comm.cuh"
 
 namespace b200 {
 
-// Layout of one rank's exchange block (allocated by comm_alloc, zeroed): a 256-byte header, then the data slots at
-// offsets the caller chooses (multiples of 16 bytes).
-constexpr int kCommHeaderBytes = 256;
-constexpr int kCommMaxRanks = 16;
-constexpr int kCommFlagsOff = 0;      // uint32 flags[16]: flags[j] = latest step rank j has announced to this rank
-constexpr int kCommCounterOff = 64;   // uint32: steps this rank has taken
-constexpr int kCommErrorOff = 68;     // uint32: 0, or the code of a wait that ran out
-constexpr int kCommLimitOff = 72;     // uint32: polls before a wait for a peer gives up; 0 = kCommSpinLimit
-constexpr int kCommThreads = 1024;
-constexpr int kCommSpinLimit = 1 << 22;
-
-enum : uint32_t { COMM_ERR_PEER_WAIT = 1 };
-
-struct CommPeers {
-  uint8_t* p[kCommMaxRanks];   // base of every rank's exchange block as mapped into this process; p[rank] is local
-};
-
 namespace {
-
-DEVI void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-DEVI uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-DEVI uint4 ld_peer16(const void* p) {
-  uint4 r;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-               : "l"(p)
-               : "memory");
-  return r;
-}
 
 // Steps 1 and 2 of the header comment, by all threads of the (single) block. Returns false if a wait ran out.
 DEVI bool exchange_flags(const CommPeers& P, int rank, int W) {

@@ -59,6 +59,8 @@ SIGNATURES = {
     "b200_tp_allreduce_add_rmsnorm": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_float,
                                       c_void_p],
     "b200_tp_allgather": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_int, c_void_p],
+    "b200_gemv_w4a16_tiled_allreduce": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_size_t,
+                                        c_void_p],
     "b200_paged_attention_noalloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_void_p, c_void_p],
     "b200_rope_append_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
@@ -106,6 +108,8 @@ def load_library(build_if_missing=True, path=None):
     lib.b200_decode_step.restype = c_int
     lib.b200_gemv_w4a16_tiled_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemv_w4a16_tiled_bytes.restype = c_size_t
+    lib.b200_tp_gemv_slot_bytes.argtypes = [c_int, c_int]
+    lib.b200_tp_gemv_slot_bytes.restype = c_size_t
     lib.b200_decode_step_xchg_bytes.argtypes = [c_int] * 7
     lib.b200_decode_step_xchg_bytes.restype = c_size_t
     lib.b200_version.restype = c_int
@@ -384,6 +388,21 @@ class Ops:
         self._check(self.lib.b200_tp_allreduce_add_rmsnorm(peers, int(rank), len(peers), int(slot_off), x.data_ptr(),
                                                            w.data_ptr(), out.data_ptr(), x.numel(), float(eps),
                                                            _stream()), "tp_allreduce_add_rmsnorm")
+
+    def tp_gemv_slot_bytes(self, N, W):
+        """Bytes of the exchange-block region gemv_tiled_allreduce needs for outputs of N rows over W ranks."""
+        return int(self.lib.b200_tp_gemv_slot_bytes(int(N), int(W)))
+
+    def gemv_tiled_allreduce(self, tiled, x, y, N, K, peers, rank, slot_off):
+        """y[N] = sum over the ranks of (rank's W_r x_r): the row-split GEMV with its all-reduce inside
+        (b200_gemv_w4a16_tiled_allreduce). tiled: this rank's column shard in tile layout; y a local fp16 tensor."""
+        _cuda(tiled, "tiled", torch.uint8), _cuda(x, "x", torch.float16), _cuda(y, "y", torch.float16)
+        if x.numel() != K or y.numel() != N:
+            raise RuntimeError("gemv_tiled_allreduce: x must hold K and y N values")
+        _aligned16(y, "y")
+        self._check(self.lib.b200_gemv_w4a16_tiled_allreduce(tiled.data_ptr(), x.data_ptr(), y.data_ptr(), int(N),
+                                                             int(K), peers, int(rank), len(peers), int(slot_off),
+                                                             _stream()), "gemv_tiled_allreduce")
 
     def tp_allgather(self, peers, rank, slot_off, dst, n):
         _cuda(dst, "dst", torch.float16)

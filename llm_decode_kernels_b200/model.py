@@ -247,13 +247,18 @@ class Model:
                 if self.off & {"norm"}:
                     raise ValueError("tp_comm='p2p' fuses the all-reduce with residual add + RMSNorm; it cannot run "
                                      "with that fusion switched off (use tp_comm='nccl')")
-                # the row-split projections and the LM head write straight into slots of the exchange block
-                self.comm = TP.PeerComm(self.K, self.tp_rank, self.tp, [2 * self.H, 2 * self.H, 2 * self.V], dev,
-                                        cfg.tp_group)
-                self.o, self.down, self.logits_local = self.comm.slot(0), self.comm.slot(1), self.comm.slot(2)
-        heads = [lw[n] for lw in self.layers for n in ("qkv", "gu")] + [self.lm_head]
-        self.norm_in_gemv = (cfg.fuse_norm_gemv and self.tp == 1 and not self.off
-                             and all(lin.tiled is not None for lin in heads))
+                # exchange block: two regions for the all-reduce inside the o_proj / down_proj GEMVs (they alternate),
+                # the logit shard, and - for fuse_norm_gemv=False, where the exchange is a kernel of its own fused with
+                # add + RMSNorm - two plain slots the row-split projections write their partials into
+                gslot = self.K.tp_gemv_slot_bytes(self.H, self.tp)
+                self.comm = TP.PeerComm(self.K, self.tp_rank, self.tp, [gslot, gslot, 2 * self.V, 2 * self.H, 2 * self.H],
+                                        dev, cfg.tp_group)
+                self.logits_local = self.comm.slot(2)
+        every = [lw[n] for lw in self.layers for n in ("qkv", "o", "gu", "down")] + [self.lm_head]
+        self.norm_in_gemv = (cfg.fuse_norm_gemv and not self.off and all(lin.tiled is not None for lin in every)
+                             and (self.tp == 1 or self.comm is not None))
+        if self.comm is not None and not self.norm_in_gemv:
+            self.o, self.down = self.comm.slot(3), self.comm.slot(4)
         self.set_attention_partition(cfg.max_ctx)
 
     @classmethod
@@ -402,7 +407,7 @@ class Model:
         kernel (tp_comm='p2p') or by an NCCL all-reduce in front of it."""
         if self.tp > 1 and delta is not None:
             if self.comm is not None:
-                self.K.tp_allreduce_add_rmsnorm(self.comm.peers, self.tp_rank, self.comm.offsets[slot], self.x, w,
+                self.K.tp_allreduce_add_rmsnorm(self.comm.peers, self.tp_rank, self.comm.offsets[3 + slot], self.x, w,
                                                 self.normed, self.eps)
                 return
             self.all_reduce(delta)
@@ -490,16 +495,17 @@ class Model:
         self.K.argmax(self.logits, self.tok, self.pos, self.history)
 
     def step_norm_in_gemv(self):
-        """The layers with residual add + RMSNorm done inside the qkv / gate|up / LM-head GEMVs: 7 launches per layer
-        (qkv, rope+append, attention, combine, o, gate|up+SwiGLU, down) instead of 10. The residual stream alternates
-        between self.x and self.x_alt: a fused GEMV reads one and writes the other."""
+        """The layers with residual add + RMSNorm done inside the qkv / gate|up / LM-head GEMVs: 6 launches per layer
+        (qkv, rope + attention, combine, o, gate|up + SwiGLU, down) instead of 10. The residual stream alternates
+        between self.x and self.x_alt: a fused GEMV reads one and writes the other. Tensor parallel (tp_comm="p2p"):
+        the same launches - the all-reduce of o_proj and down_proj happens inside those two GEMVs."""
         K, cur, nxt, delta = self.K, self.x, self.x_alt, None
         for li, lw in enumerate(self.layers):
             K.gemv_w4a16_tiled_norm(lw["qkv"].tiled, cur, delta, lw["ln1"], self.eps, nxt, self.qkv, lw["qkv"].N,
                                     lw["qkv"].K)
             cur, nxt = nxt, cur
             self.attention(li)
-            self.linear(lw["o"], self.attn.view(-1), self.o)
+            self.row_split_linear(lw["o"], self.attn.view(-1), self.o, 0)
             gu = lw["gu"]
             if gu.paired:
                 K.gemv_w4a16_tiled_norm(gu.tiled, cur, self.o, lw["ln2"], self.eps, nxt, self.act, self.I, gu.K,
@@ -508,11 +514,22 @@ class Model:
                 K.gemv_w4a16_tiled_norm(gu.tiled, cur, self.o, lw["ln2"], self.eps, nxt, self.gu, gu.N, gu.K)
                 self.swiglu()
             cur, nxt = nxt, cur
-            self.linear(lw["down"], self.act, self.down)
+            self.row_split_linear(lw["down"], self.act, self.down, 1)
             delta = self.down
         K.gemv_w4a16_tiled_norm(self.lm_head.tiled, cur, delta, self.norm_f, self.eps, nxt, self.logits_local,
                                 self.lm_head.N, self.lm_head.K)
+        if self.comm is not None:   # every rank gathers the whole vocabulary and takes the same argmax: no broadcast
+            K.tp_allgather(self.comm.peers, self.tp_rank, self.comm.offsets[2], self.logits, self.V)
         K.argmax(self.logits, self.tok, self.pos, self.history)
+
+    def row_split_linear(self, lin, x, y, slot):
+        """o_proj / down_proj. Tensor parallel: this rank's column shard times its x, summed over the ranks inside the
+        same kernel (b200_gemv_w4a16_tiled_allreduce through exchange region `slot`); y is the sum on every rank."""
+        if self.comm is None:
+            self.linear(lin, x, y)
+        else:
+            self.K.gemv_tiled_allreduce(lin.tiled, x, y, lin.N, lin.K, self.comm.peers, self.tp_rank,
+                                        self.comm.offsets[slot])
 
     def capture(self):
         """Record step() as one CUDA graph. torch wants the work run once or twice on a side stream before it

@@ -120,6 +120,8 @@ def test_gemv_tile_layout(K, name):
     torch.manual_seed(1)
     w = (torch.randn(N, Kd) * 0.02).half().to(dev)
     x = torch.randn(Kd, device=dev).half()
+    for layout in (0, 1):     # "same order" needs the same launch shape: forget a measured one an earlier test's Model
+        K.gemv_tune(layout, N, Kd, 0, 0)   # may have registered for this matrix shape (the table is per process)
     for G in (128, 256) if Kd % 256 == 0 else (128,):
         ql = PQ.QuantLinear(w, G)
         tiled = K.gemv_tile_repack(ql.packed, ql.sz, G)
@@ -482,6 +484,44 @@ def test_exchange_kernels_with_one_rank(K):
         K.comm_reset(base)
     finally:
         K.comm_free(base)
+
+
+def test_gemv_with_allreduce_inside(K):
+    """b200_gemv_w4a16_tiled_allreduce on one GPU. W = 1: no peer, the kernel's push / sum path must give the bits of
+    the plain tile-layout GEMV, call after call (the slot's call counter moves on). W = 2 with a second local block
+    standing in for a peer that never pushes: the bounded wait runs out, the error word is set, y is left alone."""
+    import ctypes
+    torch.manual_seed(7)
+    hdr = K.comm_header_bytes()
+    for N, Kd in ((8192, 1024), (2048, 5632), (1000, 512)):     # 70B TP8 o_proj shard, TinyLlama down, ragged tiles
+        ql = PQ.QuantLinear((torch.randn(N, Kd) * 0.05).half(), 128, keep_ref=False)
+        tiled = K.gemv_tile_repack(ql.packed.to(dev), ql.sz.to(dev), 128)
+        x = torch.randn(Kd, device=dev).half()
+        want = torch.empty(N, dtype=torch.half, device=dev)
+        K.gemv_w4a16_tiled(tiled, x, want, N, Kd)
+        nbytes = hdr + 2 * ((K.tp_gemv_slot_bytes(N, 2) + 255) // 256 * 256)
+        mine, silent = K.comm_alloc(nbytes), K.comm_alloc(nbytes)
+        try:
+            one = (ctypes.c_void_p * 1)(mine)
+            for _ in range(3):
+                y = torch.zeros(N, dtype=torch.half, device=dev)
+                K.gemv_tiled_allreduce(tiled, x, y, N, Kd, one, 0, hdr)
+                assert torch.equal(y, want)
+            assert K.comm_error(mine) == 0
+            two = (ctypes.c_void_p * 2)(mine, silent)
+            K.comm_set_wait_limit(mine, 2000)
+            y = torch.full((N,), 7.0, dtype=torch.half, device=dev)
+            K.gemv_tiled_allreduce(tiled, x, y, N, Kd, two, 0, hdr)
+            torch.cuda.synchronize()                              # returns: every wait is bounded
+            assert K.comm_error(mine) == 1 and bool((y == 7.0).all())
+            K.comm_reset(mine)
+            assert K.comm_error(mine) == 0
+        finally:
+            K.comm_free(mine)
+            K.comm_free(silent)
+    with pytest.raises(RuntimeError):
+        K.gemv_tiled_allreduce(tiled, x, torch.empty(1001, dtype=torch.half, device=dev), 1001, 512,
+                               (ctypes.c_void_p * 1)(0), 0, hdr)
 
 
 def test_exchange_wait_that_runs_out_is_reported(K):

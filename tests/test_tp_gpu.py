@@ -15,7 +15,7 @@ def _cfg():
                                  head_dim=128)
 
 
-def _rank_main(rank, world, port, out, modes, tp_comm):
+def _rank_main(rank, world, port, out, modes, tp_comm, fuse):
     import datetime
     import torch.distributed as dist
     from llm_decode_kernels_b200.model import DecodeConfig, Model
@@ -28,7 +28,8 @@ def _rank_main(rank, world, port, out, modes, tp_comm):
         c = _cfg()
         sd = {k: (v * 3 if v.dim() == 2 else v) for k, v in random_llama_state(c, "cpu", 3).items()}
         m = Model(sd, c, DecodeConfig(max_ctx=96, seed=4, device=f"cuda:{rank}", tp_rank=rank, tp_world=world,
-                                      tp_comm=tp_comm))
+                                      tp_comm=tp_comm, fuse_norm_gemv=fuse))
+        assert m.norm_in_gemv == (fuse and tp_comm == "p2p")
         assert not m.persistent and m.n_q == 8 // world and m.V == 3000 // world
         assert (m.comm is not None) == (tp_comm == "p2p")
         g = torch.Generator().manual_seed(1)
@@ -53,11 +54,11 @@ def _rank_main(rank, world, port, out, modes, tp_comm):
         dist.destroy_process_group()
 
 
-def _spawn(world, out, modes, tp_comm, limit_s=150):
+def _spawn(world, out, modes, tp_comm, fuse, limit_s=150):
     """Child processes with a deadline: a rank that never returns is killed and the test fails, it does not hang."""
     ctx = mp.get_context("spawn")
     port = 29900 + (os.getpid() + len(modes) + len(tp_comm)) % 1000
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, out, modes, tp_comm)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, out, modes, tp_comm, fuse)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -69,15 +70,17 @@ def _spawn(world, out, modes, tp_comm, limit_s=150):
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
 
 
-@pytest.mark.parametrize("tp_comm,modes", [("nccl", (False,)),          # NCCL collectives: launched eagerly
-                                           ("p2p", (False, True))])     # peer-memory exchange: eager, then one graph
-def test_tp2_matches_single_gpu(tmp_path, tp_comm, modes):
+@pytest.mark.parametrize("tp_comm,modes,fuse", [
+    ("nccl", (False,), True),          # NCCL collectives: launched eagerly
+    ("p2p", (False, True), True),      # all-reduce inside the row-split GEMVs: eager, then one graph
+    ("p2p", (False, True), False)])    # exchange kernels of their own, fused with add + RMSNorm
+def test_tp2_matches_single_gpu(tmp_path, tp_comm, modes, fuse):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from llm_decode_kernels_b200.model import DecodeConfig, Model
     from llm_decode_kernels_b200.shapes import random_llama_state
     out = str(tmp_path / "tp2.pt")
-    _spawn(2, out, modes, tp_comm)
+    _spawn(2, out, modes, tp_comm, fuse)
     got = torch.load(out)
     c = _cfg()
     sd = {k: (v * 3 if v.dim() == 2 else v) for k, v in random_llama_state(c, "cpu", 3).items()}
