@@ -160,6 +160,25 @@ int b200_rope_append_batched(void* qkv, const float* cos_t, const float* sin_t, 
                              int bt_stride, void* kc, void* vc, int B, int n_q, int n_kv, int D, int log2P,
                              void* stream);
 
+/* Batched forms for the prompt: rows of x / delta / out are H apart, the norm weight is shared; gu [rows, 2I],
+ * out [rows, I]. Same arithmetic per row as b200_add_rmsnorm / b200_swiglu. rows <= 65535 for the SwiGLU. */
+int b200_add_rmsnorm_batched(void* x, const void* delta, const void* w, void* out, int rows, int H, float eps,
+                             void* stream);
+int b200_swiglu_batched(const void* gu, void* out, int rows, int I, void* stream);
+
+/* Y[T, N] = X[T, K] . dequant(W)[N, K]^T for the T tokens of a prompt, fp32 accumulation on the tcgen05 tensor cores
+ * (accumulator in tensor memory), fp16 out. The reference has no counterpart: it feeds a prompt through its decode
+ * step one token at a time (runtime/model.py:267-276) and lists the batched GEMM as cut (RESULTS.md:385-387).
+ * Wp int32 [N, K/8] and SZ half2 [N, K >> log2G] are the quantizer's row-major tensors (runtime/quant.py:61-90),
+ * X fp16 [T, K] (16B), Y fp16 [T, N]. K % 64 == 0, group = 2^log2G >= 64, T <= b200_gemm_w4a16_max_tokens().
+ * The dequantized fp16 weights are those of b200_dequant_w4a16, bit for bit. Waits on the tensor core are bounded:
+ * if one runs out the CTA frees its tensor memory and returns, and b200_gemm_w4a16_status reports 1 (sticky). */
+int b200_gemm_w4a16(const void* Wp, const void* SZ, const void* X, void* Y, int T, int N, int K, int log2G,
+                    void* stream);
+int b200_gemm_w4a16_max_tokens(void);
+/* Synchronous read of the status word: 0, or 1 once a bounded wait ran out. */
+int b200_gemm_w4a16_status(int* code);
+
 /* out fp16 [N, K] (16B) = per-element dequantized weight, bit-identical to the quantizer's dequantize
  * (reference runtime/quant.py:93-97). Used to prove the kernels read the packed format correctly. */
 int b200_dequant_w4a16(const void* Wp, const void* SZ, void* out, int N, int K, int log2G, void* stream);

@@ -24,9 +24,13 @@ cudaError_t gemv_w4a16_tiled_allreduce_dispatch(const void* Wt, const void* x, v
 size_t gemv_allreduce_slot_bytes(int N, int W);
 cudaError_t dequant_w4a16_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G,
                                    cudaStream_t st);
-cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int H, float eps,
+cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int rows, int H, float eps,
                                  cudaStream_t st);
-cudaError_t swiglu_dispatch(const void* gu, void* out, int I, cudaStream_t st);
+cudaError_t swiglu_dispatch(const void* gu, void* out, int rows, int I, cudaStream_t st);
+cudaError_t prefill_gemm_dispatch(const void* Wp, const void* SZ, const void* X, void* Y, int T, int N, int K, int log2G,
+                                  cudaStream_t st);
+int prefill_gemm_max_tokens();
+cudaError_t prefill_gemm_status(int* code);
 cudaError_t rope_append_dispatch(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt,
                                  int bt_stride, void* kc, void* vc, int B, int n_q, int n_kv, int D, int log2P,
                                  cudaStream_t st);
@@ -220,19 +224,43 @@ int b200_paged_attention_status(int* code) {
   return finish(b200::paged_attention_status(code));
 }
 
-int b200_add_rmsnorm(void* x, const void* delta, const void* w, void* out, int H, float eps, void* stream) {
-  REQUIRE(x && w && out && H > 0, B200_ERR_ARG);
+int b200_add_rmsnorm_batched(void* x, const void* delta, const void* w, void* out, int rows, int H, float eps,
+                             void* stream) {
+  REQUIRE(x && w && out && H > 0 && rows > 0, B200_ERR_ARG);
   REQUIRE(H % 8 == 0, B200_ERR_SHAPE);
   REQUIRE(H <= 32768, B200_ERR_LIMIT);
   REQUIRE(aligned16(x) && aligned16(w) && aligned16(out) && aligned16(delta), B200_ERR_ALIGN);
-  return finish(b200::add_rmsnorm_dispatch(x, delta, w, out, H, eps, S(stream)));
+  return finish(b200::add_rmsnorm_dispatch(x, delta, w, out, rows, H, eps, S(stream)));
 }
 
-int b200_swiglu(const void* gu, void* out, int I, void* stream) {
-  REQUIRE(gu && out && I > 0, B200_ERR_ARG);
+int b200_add_rmsnorm(void* x, const void* delta, const void* w, void* out, int H, float eps, void* stream) {
+  return b200_add_rmsnorm_batched(x, delta, w, out, 1, H, eps, stream);
+}
+
+int b200_swiglu_batched(const void* gu, void* out, int rows, int I, void* stream) {
+  REQUIRE(gu && out && I > 0 && rows > 0, B200_ERR_ARG);
   REQUIRE(I % 8 == 0, B200_ERR_SHAPE);
+  REQUIRE(rows <= 65535, B200_ERR_LIMIT);
   REQUIRE(aligned16(gu) && aligned16(out), B200_ERR_ALIGN);
-  return finish(b200::swiglu_dispatch(gu, out, I, S(stream)));
+  return finish(b200::swiglu_dispatch(gu, out, rows, I, S(stream)));
+}
+
+int b200_swiglu(const void* gu, void* out, int I, void* stream) { return b200_swiglu_batched(gu, out, 1, I, stream); }
+
+int b200_gemm_w4a16(const void* Wp, const void* SZ, const void* X, void* Y, int T, int N, int K, int log2G,
+                    void* stream) {
+  REQUIRE(Wp && SZ && X && Y && T > 0 && N > 0 && K > 0, B200_ERR_ARG);
+  REQUIRE(log2G >= 6 && log2G < 31 && K % 64 == 0 && K % (1 << log2G) == 0, B200_ERR_SHAPE);
+  REQUIRE(T <= b200::prefill_gemm_max_tokens(), B200_ERR_LIMIT);
+  REQUIRE(aligned16(X), B200_ERR_ALIGN);
+  return finish(b200::prefill_gemm_dispatch(Wp, SZ, X, Y, T, N, K, log2G, S(stream)));
+}
+
+int b200_gemm_w4a16_max_tokens(void) { return b200::prefill_gemm_max_tokens(); }
+
+int b200_gemm_w4a16_status(int* code) {
+  REQUIRE(code, B200_ERR_ARG);
+  return finish(b200::prefill_gemm_status(code));
 }
 
 int b200_rope_append_batched(void* qkv, const float* cos_t, const float* sin_t, const int* pos, const int* bt,

@@ -11,7 +11,7 @@ namespace b200 {
 // Replaces add_rmsnorm_launch (reference kernels/fused_norm.cu:56-58). Rounding as in HF LlamaRMSNorm
 // (reference reference/ref_ops.py:15-20): x <- x +_fp16 delta (written back); h = half(float(x) * rsqrt(
 // mean(float(x)^2) + eps)); out = w *_fp16 h. One block; each thread keeps its 8-element chunks in
-// registers across the reduction, so x is read once.
+// registers across the reduction, so x is read once. With a batch (the prompt's tokens) block b takes row b.
 constexpr int kNormThreads = 512;
 constexpr int kNormMaxChunks = 8;  // H <= 512 * 8 * 8 = 32768
 
@@ -20,6 +20,9 @@ add_rmsnorm_kernel(half* __restrict__ x, const half* __restrict__ delta, const h
                    half* __restrict__ out, int H, float eps) {
   pdl_launch_dependents();
   pdl_wait();
+  x += (size_t)blockIdx.x * H;
+  out += (size_t)blockIdx.x * H;
+  if (delta) delta += (size_t)blockIdx.x * H;
   __shared__ float part[kNormThreads / 32];
   const int tid = threadIdx.x, nchunk = H >> 3;
   uint4 xv[kNormMaxChunks];
@@ -68,22 +71,26 @@ add_rmsnorm_kernel(half* __restrict__ x, const half* __restrict__ delta, const h
   }
 }
 
-cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int H, float eps,
+cudaError_t add_rmsnorm_dispatch(void* x, const void* delta, const void* w, void* out, int rows, int H, float eps,
                                  cudaStream_t st) {
-  B200_LAUNCH(add_rmsnorm_kernel, dim3(1), dim3(kNormThreads), 0, st, (half*)x, (const half*)delta, (const half*)w,
+  B200_LAUNCH(add_rmsnorm_kernel, dim3(rows), dim3(kNormThreads), 0, st, (half*)x, (const half*)delta, (const half*)w,
               (half*)out, H, eps);
   return cudaPeekAtLastError();
 }
 
 // ---- SwiGLU ---------------------------------------------------------------------------------------------
 // Replaces swiglu_launch (reference kernels/fused_swiglu.cu:23-26). gu = gate followed by up, [2I];
-// out[i] = half(silu_fp32(gate_i)) *_fp16 up_i (reference reference/ref_ops.py:23-27).
+// out[i] = half(silu_fp32(gate_i)) *_fp16 up_i (reference reference/ref_ops.py:23-27). blockIdx.y = row of a batch
+// (gu [rows, 2I], out [rows, I]).
 __global__ void swiglu_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out,
                               int nchunk) {
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= nchunk) return;
+  gate += (size_t)blockIdx.y * 2 * nchunk;
+  up += (size_t)blockIdx.y * 2 * nchunk;
+  out += (size_t)blockIdx.y * nchunk;
   const uint4 gv = gate[i], uv = up[i];
   const uint32_t g[4] = {gv.x, gv.y, gv.z, gv.w}, u[4] = {uv.x, uv.y, uv.z, uv.w};
   uint32_t o[4];
@@ -96,9 +103,9 @@ __global__ void swiglu_kernel(const uint4* __restrict__ gate, const uint4* __res
   out[i] = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-cudaError_t swiglu_dispatch(const void* gu, void* out, int I, cudaStream_t st) {
+cudaError_t swiglu_dispatch(const void* gu, void* out, int rows, int I, cudaStream_t st) {
   const int nchunk = I >> 3, threads = 128;
-  B200_LAUNCH(swiglu_kernel, dim3((nchunk + threads - 1) / threads), dim3(threads), 0, st, (const uint4*)gu, (const
+  B200_LAUNCH(swiglu_kernel, dim3((nchunk + threads - 1) / threads, rows), dim3(threads), 0, st, (const uint4*)gu, (const
               uint4*)((const half*)gu + I), (uint4*)out, nchunk);
   return cudaPeekAtLastError();
 }

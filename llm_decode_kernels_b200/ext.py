@@ -9,7 +9,8 @@ Errors surface as RuntimeError before anything is launched. There is no fallback
 cannot be built, or a tensor is not on a CUDA device, the call raises.
 
 Additional operators (no counterpart in the reference): dequant_w4a16, paged_attention_batched,
-rope_append_batched, embed_row, argmax.
+rope_append_batched, embed_row, argmax, and the prompt's batched forms gemm_w4a16, add_rmsnorm_batched,
+swiglu_batched.
 """
 import ctypes
 import math
@@ -66,6 +67,11 @@ SIGNATURES = {
     "b200_rope_append_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_void_p],
     "b200_dequant_w4a16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_add_rmsnorm_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "b200_swiglu_batched": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "b200_gemm_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "b200_gemm_w4a16_max_tokens": [],
+    "b200_gemm_w4a16_status": [c_void_p],
     "b200_embed_row": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "b200_argmax": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
@@ -456,6 +462,49 @@ class Ops:
             raise RuntimeError("dequant_w4a16: inconsistent shapes")
         self._check(self.lib.b200_dequant_w4a16(packed.data_ptr(), sz.data_ptr(), out.data_ptr(), N, K,
                                                 _ilog2_exact(int(group), "group"), _stream()), "dequant_w4a16")
+
+    # ---- the prompt: T tokens at once --------------------------------------------------------------------
+    def gemm_w4a16(self, packed, sz, x, y, group):
+        """y[T, N] = x[T, K] @ dequant(packed, sz)^T on the tcgen05 tensor cores. packed int32 [N, K/8], sz fp16
+        [N, K/group, 2], x fp16 [T, K], y fp16 [T, N]; K % 64 == 0, group >= 64, T <= gemm_max_tokens()."""
+        _cuda(packed, "packed", torch.int32), _cuda(sz, "sz", torch.float16)
+        _cuda(x, "x", torch.float16), _cuda(y, "y", torch.float16)
+        N, K = packed.shape[0], packed.shape[1] * 8
+        if x.dim() != 2 or x.shape[1] != K or tuple(y.shape) != (x.shape[0], N) or K % group:
+            raise RuntimeError("gemm_w4a16: inconsistent shapes")
+        if tuple(sz.shape) != (N, K // group, 2):
+            raise RuntimeError("gemm_w4a16: sz must be [N, K/group, 2]")
+        self._check(self.lib.b200_gemm_w4a16(packed.data_ptr(), sz.data_ptr(), x.data_ptr(), y.data_ptr(), x.shape[0],
+                                             N, K, _ilog2_exact(int(group), "group"), _stream()), "gemm_w4a16")
+
+    def gemm_max_tokens(self):
+        return int(self.lib.b200_gemm_w4a16_max_tokens())
+
+    def gemm_status(self):
+        """0, or 1 once a bounded wait inside the GEMM kernel ran out (synchronizes the device)."""
+        code = c_int(-1)
+        self._check(self.lib.b200_gemm_w4a16_status(ctypes.byref(code)), "gemm_w4a16_status")
+        return code.value
+
+    def add_rmsnorm_batched(self, x, delta, w, out, eps):
+        """Row-wise add_rmsnorm over x [T, H] (delta [T, H] or None, w [H], out [T, H])."""
+        _cuda(x, "x", torch.float16), _cuda(w, "w", torch.float16), _cuda(out, "out", torch.float16)
+        if delta is not None:
+            _cuda(delta, "delta", torch.float16)
+        T, H = x.shape
+        if w.numel() != H or tuple(out.shape) != (T, H) or (delta is not None and tuple(delta.shape) != (T, H)):
+            raise RuntimeError("add_rmsnorm_batched: inconsistent shapes")
+        self._check(self.lib.b200_add_rmsnorm_batched(x.data_ptr(), None if delta is None else delta.data_ptr(),
+                                                      w.data_ptr(), out.data_ptr(), T, H, float(eps), _stream()),
+                    "add_rmsnorm_batched")
+
+    def swiglu_batched(self, gu, out):
+        """out[t] = silu(gu[t, :I]) * gu[t, I:] for gu [T, 2I], out [T, I]."""
+        _cuda(gu, "gu", torch.float16), _cuda(out, "out", torch.float16)
+        T, I = out.shape
+        if tuple(gu.shape) != (T, 2 * I):
+            raise RuntimeError("swiglu_batched: gu must be [T, 2I] and out [T, I]")
+        self._check(self.lib.b200_swiglu_batched(gu.data_ptr(), out.data_ptr(), T, I, _stream()), "swiglu_batched")
 
     def embed_row(self, emb, tok, x):
         _cuda(emb, "emb", torch.float16), _cuda(tok, "tok", torch.int64), _cuda(x, "x", torch.float16)

@@ -598,11 +598,88 @@ class Model:
                 logits[i].copy_(self.logits)
         return logits
 
-    def generate(self, prompt, n_new, use_graph=True):
+    def prefill(self, tokens, collect_logits=False):
+        """Process a prompt T tokens at a time instead of one step per token: every weight matrix is read once per
+        chunk of up to gemm_max_tokens() tokens (b200_gemm_w4a16, tcgen05 tensor cores), the small operators run in
+        their batched forms, and attention runs as a batch of T queries over the same block table, query t seeing
+        the cache up to its own position. The reference has no such path (it steps through the prompt,
+        runtime/model.py:267-276). Leaves the runtime exactly where teacher_force(tokens) would: K/V rows of the
+        prompt in the cache, self.logits / self.tok from the last prompt token, the position behind the prompt.
+        The history entries of the prompt positions before the last are not written. Returns the logits of every
+        prompt position, fp16 [len, V], when collect_logits is set. One GPU, row-major packed weights kept
+        (keep_packed=True)."""
+        if self.tp != 1:
+            raise ValueError("prefill() is single-GPU; tensor-parallel ranks step through the prompt")
+        if self.off:
+            raise ValueError("prefill() computes the fused operators; it cannot run with an ablation switch")
+        mats = [lw[n] for lw in self.layers for n in ("qkv", "o", "gu", "down")] + [self.lm_head]
+        if any(mt.packed is None for mt in mats):
+            raise ValueError("prefill() reads the row-major packed tensors: build the model with keep_packed=True")
+        if self.cfg.group % 64 or any(mt.K % 64 for mt in mats):
+            raise ValueError("prefill() needs a group size and row lengths that are multiples of 64")
+        ids = torch.as_tensor(tokens).long().reshape(-1)
+        n = ids.numel()
+        if n == 0:
+            return torch.empty(0, self.V_full, dtype=torch.half, device=self.tok.device) if collect_logits else None
+        if int(ids.min()) < 0 or int(ids.max()) >= self.V_full:
+            raise ValueError(f"token ids must lie in [0, {self.V_full})")
+        limit = min(self.ctx_cap, self.cfg.max_ctx)
+        if self.host_pos + n > limit:
+            raise RuntimeError(f"context {self.host_pos + n} exceeds the prepared attention cap {limit}; call prepare()")
+        dev, K, G = self.tok.device, self.K, self.cfg.group
+        if ids.device.type != "cuda":
+            ids = ids.pin_memory().to(dev, non_blocking=True)
+        h16 = dict(dtype=torch.half, device=dev)
+        nq, nkv, D, S = self.n_q, self.n_kv, self.D, self.max_splits
+        # tokens per chunk: the GEMM's limit, and split scratch of at most 256 MB
+        chunk = max(1, min(K.gemm_max_tokens(), (256 << 20) // (nq * S * D * 4)))
+        all_logits = torch.empty(n, self.V_full, **h16) if collect_logits else None
+        for c0 in range(0, n, chunk):
+            T = min(chunk, n - c0)
+            x = self.emb.index_select(0, ids[c0:c0 + T])
+            pos = torch.arange(self.host_pos + c0, self.host_pos + c0 + T, dtype=torch.int32, device=dev)
+            bt = self.bt.view(1, -1).expand(T, -1).contiguous()
+            normed, qkv = torch.empty(T, self.H, **h16), torch.empty(T, (nq + 2 * nkv) * D, **h16)
+            q, attn = torch.empty(T, nq, D, **h16), torch.empty(T, nq, D, **h16)
+            o, act, down = torch.empty(T, self.H, **h16), torch.empty(T, self.I, **h16), torch.empty(T, self.H, **h16)
+            gu = torch.empty(T, 2 * self.I, **h16)
+            o_part = torch.empty(T, nq, S, D, dtype=torch.float32, device=dev)
+            m_part, l_part = (torch.empty(T, nq, S, dtype=torch.float32, device=dev) for _ in range(2))
+            delta = None
+            for li, lw in enumerate(self.layers):
+                K.add_rmsnorm_batched(x, delta, lw["ln1"], normed, self.eps)
+                K.gemm_w4a16(lw["qkv"].packed, lw["qkv"].sz, normed, qkv, G)
+                K.rope_append_batched(qkv, self.cos, self.sin, pos, bt, self.kv[li, 0], self.kv[li, 1], nq, nkv)
+                q.copy_(qkv[:, : nq * D].view(T, nq, D))
+                K.paged_attention_batched(q, self.kv[li, 0], self.kv[li, 1], bt, pos, self.part_size, o_part, m_part,
+                                          l_part, attn)
+                K.gemm_w4a16(lw["o"].packed, lw["o"].sz, attn.view(T, nq * D), o, G)
+                K.add_rmsnorm_batched(x, o, lw["ln2"], normed, self.eps)
+                K.gemm_w4a16(lw["gu"].packed, lw["gu"].sz, normed, gu, G)
+                K.swiglu_batched(gu, act)
+                K.gemm_w4a16(lw["down"].packed, lw["down"].sz, act, down, G)
+                delta = down
+            K.add_rmsnorm_batched(x, delta, self.norm_f, normed, self.eps)
+            if collect_logits:
+                K.gemm_w4a16(self.lm_head.packed, self.lm_head.sz, normed, all_logits[c0:c0 + T], G)
+        if collect_logits:
+            self.logits.copy_(all_logits[n - 1])
+        else:   # only the last position's logits are needed to go on: one GEMV
+            self.linear(self.lm_head, normed[T - 1], self.logits)
+        self.host_pos += n
+        self.pos.fill_(self.host_pos - 1)
+        K.argmax(self.logits, self.tok, self.pos, self.history)   # token after the prompt; pos -> host_pos
+        return all_logits
+
+    def generate(self, prompt, n_new, use_graph=True, prefill=False):
         """Greedy decoding of n_new tokens after `prompt`, each token read back to the host as soon as its step has
-        run (what the reference's generate does, runtime/model.py:278-286). Returns a list of ints."""
+        run (what the reference's generate does, runtime/model.py:278-286). prefill=True processes the prompt with
+        prefill() instead of one step per token. Returns a list of ints."""
         self.reset(0)
-        self.teacher_force(prompt, use_graph)
+        if prefill:
+            self.prefill(prompt)
+        else:
+            self.teacher_force(prompt, use_graph)
         out = []
         while True:
             out.append(int(self.tok))      # device -> host read of the token the last step chose
