@@ -178,9 +178,54 @@ def run_tp(a):
         dist.destroy_process_group()
 
 
+def run_prefill(a):
+    """Prompt processing at the TinyLlama shape: Model.prefill (batched GEMM on the tensor cores, every matrix read
+    once per 256 tokens) against stepping through the prompt (one graph replay per token, what the reference does).
+    Device time by CUDA events around the whole prompt, median of 5; both leave the same next token (checked)."""
+    c = config(TINYLLAMA)
+    sd = random_llama_state(c, "cuda", 0)
+    m = Model(sd, c, DecodeConfig(group=128, max_ctx=4096 + 16, seed=0))
+    res = {"gpu": torch.cuda.get_device_name(0), "prompts": {}}
+    g = torch.Generator().manual_seed(0)
+
+    def timed(fn, reps=5):
+        ts = []
+        for _ in range(reps):
+            m.reset(0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+
+    for n in (128, 512, 2048, 4096):
+        prompt = torch.randint(0, c.vocab_size, (n,), generator=g).cuda()
+        m.prepare(n + 8)
+        m.reset(0)
+        m.prefill(prompt)
+        tok_prefill = int(m.tok)
+        m.reset(0)
+        m.teacher_force(prompt)
+        tok_steps = int(m.tok)
+        ms_p = timed(lambda: m.prefill(prompt))
+        ms_s = timed(lambda: m.teacher_force(prompt), reps=3)
+        res["prompts"][n] = {"prefill_ms": round(ms_p, 3), "prefill_tok_s": round(n / ms_p * 1e3, 1),
+                             "stepping_ms": round(ms_s, 3), "stepping_tok_s": round(n / ms_s * 1e3, 1),
+                             "speedup": round(ms_s / ms_p, 2), "same_next_token": tok_prefill == tok_steps,
+                             "step_kernel": "persistent" if m.persistent else "multi"}
+        print(n, res["prompts"][n], flush=True)
+    res["status"] = {"gemm": m.K.gemm_status(), "step": m.step_error()}
+    txt = json.dumps(res, indent=1)
+    print(txt)
+    if a.out:
+        Path(a.out).write_text(txt)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["ctx", "tp"])
+    ap.add_argument("what", choices=["ctx", "tp", "prefill"])
     ap.add_argument("--quant", default="rtn", choices=["rtn", "gptq"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--layers", type=int, default=80)
@@ -194,7 +239,7 @@ def main():
     a = ap.parse_args()
     if a.tokens is None:
         a.tokens = 128 if a.what == "tp" else 64
-    {"ctx": run_ctx, "tp": run_tp}[a.what](a)
+    {"ctx": run_ctx, "tp": run_tp, "prefill": run_prefill}[a.what](a)
 
 
 if __name__ == "__main__":

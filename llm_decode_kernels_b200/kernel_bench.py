@@ -1,10 +1,11 @@
 """Kernel micro-benchmarks (the reference's bench/kernel_bench.py, re-done for a B200).
 
-    python -m llm_decode_kernels_b200.kernel_bench [bandwidth] [gemv] [attention] [--out FILE.json]
+    python -m llm_decode_kernels_b200.kernel_bench [bandwidth] [gemv] [attention] [gemm] [--out FILE.json]
 
 bandwidth : achievable HBM read bandwidth, register loads (b200_bw_read) and bulk-copy ring (b200_bw_read_bulk)
 gemv      : the single-GEMV configuration (5632 x 2048, g128) and every TinyLlama / Llama-3-70B GEMV shape, all GEMV
             kernels of the library, cold weights (enough distinct copies to exceed the L2 rotate inside one graph)
+gemm      : the prompt's batched GEMM on the tcgen05 tensor cores, TinyLlama shapes at 16 / 64 / 256 tokens (on request)
 attention : paged split-K attention, 32 query / 4 KV heads, head_dim 64, page 16, batch 1 at contexts 128..8192 and
             batch 8 with contexts drawn from [128, 8192]; KV pools larger than the L2 where the case allows
 
@@ -283,15 +284,50 @@ def headline_kernels(K, peak_gbs):
     return res
 
 
+def bench_gemm(K, shapes=None, tokens=(16, 64, 256)):
+    """The prompt's batched W4A16 GEMM (b200_gemm_w4a16) on the TinyLlama matrix shapes at 16 / 64 / 256 tokens:
+    microseconds, dense TFLOP/s (2 T N K), the rate at which the packed weights stream, and the time the same work
+    takes as T GEMV launches (tile layout). Checked against an fp32 product with the dequantized matrix first."""
+    out = {}
+    for name in shapes or ("qkv 2560x2048", "o 2048x2048", "gate_up 11264x2048", "down 2048x5632",
+                           "lm_head 32000x2048"):
+        N, Kd = GEMV_SHAPES[name]
+        torch.manual_seed(0)
+        ql = QuantLinear((torch.randn(N, Kd, device="cuda") * 0.02).half(), 128, keep_ref=True)
+        tiled = K.gemv_tile_repack(ql.packed, ql.sz, 128)
+        x1, y1 = torch.randn(Kd, device="cuda").half(), torch.empty(N, dtype=torch.half, device="cuda")
+        gemv_us = graph_time_us(lambda: [K.gemv_w4a16_tiled(tiled, x1, y1, N, Kd) for _ in range(20)], 20)
+        row = {"gemv_us": gemv_us}
+        for T in tokens:
+            x = torch.randn(T, Kd, device="cuda").half()
+            y = torch.empty(T, N, dtype=torch.half, device="cuda")
+            K.gemm_w4a16(ql.packed, ql.sz, x, y, 128)
+            ref = x.float() @ ql.w_ref.float().t()
+            err = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+            assert err <= 2e-3, (name, T, err)
+            st = graph_stats(lambda: [K.gemm_w4a16(ql.packed, ql.sz, x, y, 128) for _ in range(10)], 10)
+            row[f"T{T}"] = {"us": st["us"], "iqr_us": st["iqr_us"], "tflops": round(2 * T * N * Kd / st["us"] / 1e6, 1),
+                            "weight_gbps": round(gemv_bytes(N, Kd) / st["us"] / 1e3, 1),
+                            "vs_T_gemvs": round(T * gemv_us / st["us"], 1), "max_rel_err": round(err, 6),
+                            "sm_mhz": st["sm_mhz"]}
+        out[name] = row
+    out["status"] = K.gemm_status()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("sections", nargs="*", default=["bandwidth", "gemv", "attention"])
     ap.add_argument("--out", default=None)
+    ap.add_argument("--gemm-shape", action="append", default=None, help="gemm: only this shape (a key of GEMV_SHAPES)")
+    ap.add_argument("--gemm-tokens", type=int, action="append", default=None, help="gemm: only this many tokens")
     a = ap.parse_args()
     K = ext.load()
     res = {"gpu": torch.cuda.get_device_name(0)}
+    run = {"bandwidth": bench_bandwidth, "gemv": bench_gemv, "attention": bench_attention,
+           "gemm": lambda k: bench_gemm(k, a.gemm_shape, tuple(a.gemm_tokens or (16, 64, 256)))}
     for s in a.sections:
-        res[s] = {"bandwidth": bench_bandwidth, "gemv": bench_gemv, "attention": bench_attention}[s](K)
+        res[s] = run[s](K)
     txt = json.dumps(res, indent=1)
     print(txt)
     if a.out:

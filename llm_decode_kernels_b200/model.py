@@ -598,7 +598,53 @@ class Model:
                 logits[i].copy_(self.logits)
         return logits
 
-    def prefill(self, tokens, collect_logits=False):
+    def _prefill_state(self, T):
+        """Static buffers of a prompt chunk of T tokens (kept per T and attention geometry, so that a recorded graph
+        stays valid)."""
+        key = (T, self.part_size, self.max_splits)
+        cache = self.__dict__.setdefault("_prefill_cache", {})
+        if key not in cache:
+            if len(cache) >= 4:   # a few chunk sizes at most: the scratch of a chunk is tens of MB
+                cache.pop(next(iter(cache)))
+            dev, nq, nkv, D, S = self.tok.device, self.n_q, self.n_kv, self.D, self.max_splits
+            h16 = dict(dtype=torch.half, device=dev)
+            f32 = dict(dtype=torch.float32, device=dev)
+            cache[key] = {
+                "T": T, "graph": None, "ids": torch.zeros(T, dtype=torch.long, device=dev),
+                "arange": torch.arange(T, dtype=torch.int32, device=dev), "pos": torch.zeros(T, dtype=torch.int32, device=dev),
+                "bt": self.bt.view(1, -1).expand(T, -1).contiguous(),
+                "x": torch.empty(T, self.H, **h16), "normed": torch.empty(T, self.H, **h16),
+                "qkv": torch.empty(T, (nq + 2 * nkv) * D, **h16), "q": torch.empty(T, nq, D, **h16),
+                "attn": torch.empty(T, nq, D, **h16), "o": torch.empty(T, self.H, **h16),
+                "gu": torch.empty(T, 2 * self.I, **h16), "act": torch.empty(T, self.I, **h16),
+                "down": torch.empty(T, self.H, **h16), "o_part": torch.empty(T, nq, S, D, **f32),
+                "m_part": torch.empty(T, nq, S, **f32), "l_part": torch.empty(T, nq, S, **f32)}
+        st = cache[key]
+        st["bt"].copy_(self.bt.view(1, -1).expand(T, -1))   # the block table may have been replaced since
+        return st
+
+    def _prefill_chunk(self, st):
+        """The launches of one prompt chunk: reads st["ids"] / st["pos"], leaves the final-norm output in st["normed"]."""
+        K, G, T, nq, nkv, D = self.K, self.cfg.group, st["T"], self.n_q, self.n_kv, self.D
+        x, normed, qkv, q, attn = st["x"], st["normed"], st["qkv"], st["q"], st["attn"]
+        torch.index_select(self.emb, 0, st["ids"], out=x)
+        delta = None
+        for li, lw in enumerate(self.layers):
+            K.add_rmsnorm_batched(x, delta, lw["ln1"], normed, self.eps)
+            K.gemm_w4a16(lw["qkv"].packed, lw["qkv"].sz, normed, qkv, G)
+            K.rope_append_batched(qkv, self.cos, self.sin, st["pos"], st["bt"], self.kv[li, 0], self.kv[li, 1], nq, nkv)
+            q.copy_(qkv[:, : nq * D].view(T, nq, D))
+            K.paged_attention_batched(q, self.kv[li, 0], self.kv[li, 1], st["bt"], st["pos"], self.part_size,
+                                      st["o_part"], st["m_part"], st["l_part"], attn)
+            K.gemm_w4a16(lw["o"].packed, lw["o"].sz, attn.view(T, nq * D), st["o"], G)
+            K.add_rmsnorm_batched(x, st["o"], lw["ln2"], normed, self.eps)
+            K.gemm_w4a16(lw["gu"].packed, lw["gu"].sz, normed, st["gu"], G)
+            K.swiglu_batched(st["gu"], st["act"])
+            K.gemm_w4a16(lw["down"].packed, lw["down"].sz, st["act"], st["down"], G)
+            delta = st["down"]
+        K.add_rmsnorm_batched(x, delta, self.norm_f, normed, self.eps)
+
+    def prefill(self, tokens, collect_logits=False, use_graph=True):
         """Process a prompt T tokens at a time instead of one step per token: every weight matrix is read once per
         chunk of up to gemm_max_tokens() tokens (b200_gemm_w4a16, tcgen05 tensor cores), the small operators run in
         their batched forms, and attention runs as a batch of T queries over the same block table, query t seeing
@@ -606,8 +652,8 @@ class Model:
         runtime/model.py:267-276). Leaves the runtime exactly where teacher_force(tokens) would: K/V rows of the
         prompt in the cache, self.logits / self.tok from the last prompt token, the position behind the prompt.
         The history entries of the prompt positions before the last are not written. Returns the logits of every
-        prompt position, fp16 [len, V], when collect_logits is set. One GPU, row-major packed weights kept
-        (keep_packed=True)."""
+        prompt position, fp16 [len, V], when collect_logits is set. With use_graph a long prompt replays one CUDA graph
+        per whole chunk from its second chunk on. One GPU, row-major packed weights kept (keep_packed=True)."""
         if self.tp != 1:
             raise ValueError("prefill() is single-GPU; tensor-parallel ranks step through the prompt")
         if self.off:
@@ -630,38 +676,28 @@ class Model:
         if ids.device.type != "cuda":
             ids = ids.pin_memory().to(dev, non_blocking=True)
         h16 = dict(dtype=torch.half, device=dev)
-        nq, nkv, D, S = self.n_q, self.n_kv, self.D, self.max_splits
         # tokens per chunk: the GEMM's limit, and split scratch of at most 256 MB
-        chunk = max(1, min(K.gemm_max_tokens(), (256 << 20) // (nq * S * D * 4)))
+        chunk = max(1, min(K.gemm_max_tokens(), (256 << 20) // (self.n_q * self.max_splits * self.D * 4)))
         all_logits = torch.empty(n, self.V_full, **h16) if collect_logits else None
         for c0 in range(0, n, chunk):
             T = min(chunk, n - c0)
-            x = self.emb.index_select(0, ids[c0:c0 + T])
-            pos = torch.arange(self.host_pos + c0, self.host_pos + c0 + T, dtype=torch.int32, device=dev)
-            bt = self.bt.view(1, -1).expand(T, -1).contiguous()
-            normed, qkv = torch.empty(T, self.H, **h16), torch.empty(T, (nq + 2 * nkv) * D, **h16)
-            q, attn = torch.empty(T, nq, D, **h16), torch.empty(T, nq, D, **h16)
-            o, act, down = torch.empty(T, self.H, **h16), torch.empty(T, self.I, **h16), torch.empty(T, self.H, **h16)
-            gu = torch.empty(T, 2 * self.I, **h16)
-            o_part = torch.empty(T, nq, S, D, dtype=torch.float32, device=dev)
-            m_part, l_part = (torch.empty(T, nq, S, dtype=torch.float32, device=dev) for _ in range(2))
-            delta = None
-            for li, lw in enumerate(self.layers):
-                K.add_rmsnorm_batched(x, delta, lw["ln1"], normed, self.eps)
-                K.gemm_w4a16(lw["qkv"].packed, lw["qkv"].sz, normed, qkv, G)
-                K.rope_append_batched(qkv, self.cos, self.sin, pos, bt, self.kv[li, 0], self.kv[li, 1], nq, nkv)
-                q.copy_(qkv[:, : nq * D].view(T, nq, D))
-                K.paged_attention_batched(q, self.kv[li, 0], self.kv[li, 1], bt, pos, self.part_size, o_part, m_part,
-                                          l_part, attn)
-                K.gemm_w4a16(lw["o"].packed, lw["o"].sz, attn.view(T, nq * D), o, G)
-                K.add_rmsnorm_batched(x, o, lw["ln2"], normed, self.eps)
-                K.gemm_w4a16(lw["gu"].packed, lw["gu"].sz, normed, gu, G)
-                K.swiglu_batched(gu, act)
-                K.gemm_w4a16(lw["down"].packed, lw["down"].sz, act, down, G)
-                delta = down
-            K.add_rmsnorm_batched(x, delta, self.norm_f, normed, self.eps)
+            st = self._prefill_state(T)
+            st["ids"].copy_(ids[c0:c0 + T])
+            torch.add(st["arange"], self.host_pos + c0, out=st["pos"])
+            if st["graph"] is not None:
+                st["graph"].replay()
+            else:
+                self._prefill_chunk(st)
+                if use_graph and T == chunk and n - c0 > 2 * chunk:
+                    # more whole chunks follow: record the launches (recording runs nothing) and replay them from here on
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        self._prefill_chunk(st)
+                    st["graph"] = graph
             if collect_logits:
-                K.gemm_w4a16(self.lm_head.packed, self.lm_head.sz, normed, all_logits[c0:c0 + T], G)
+                K.gemm_w4a16(self.lm_head.packed, self.lm_head.sz, st["normed"], all_logits[c0:c0 + T], G)
+        normed = st["normed"]
         if collect_logits:
             self.logits.copy_(all_logits[n - 1])
         else:   # only the last position's logits are needed to go on: one GEMV
