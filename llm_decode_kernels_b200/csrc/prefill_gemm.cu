@@ -66,12 +66,17 @@ DEVI bool mbar_try_wait(uint64_t* b, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// false if the phase did not complete within the limit, or another role of the CTA has given up (fail flag)
+// false if the phase did not complete within the limit, or another role of the CTA has given up (fail flag).
+// SLEEP_NS > 0: back off between polls. The dequantizing warps run stages ahead and then wait; eighteen warps polling
+// at full rate would take the issue slots the one MMA-issuing thread needs.
+template <int SLEEP_NS>
 DEVI bool mbar_wait_bounded(uint64_t* b, uint32_t parity, volatile int* fail) {
+  if (mbar_try_wait(b, parity)) return true;
 #pragma unroll 1
   for (int i = 0; i < kPfSpinLimit; ++i) {
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if (mbar_try_wait(b, parity)) return true;
-    if (fail && (i & 255) == 255 && *fail) return false;
+    if (fail && (i & 63) == 63 && *fail) return false;
   }
   return false;
 }
@@ -214,24 +219,39 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint32_t* __
           rsz[u] = __ldg(szp + (((c_begin + j + kPfPrefetch) * kPfChunk + qt * 16) >> log2G));
         }
         // the decision is the warp's, so that its lanes stay together for the __syncwarp below
-        if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait_bounded(&sh.mma_done[s], (use - 1) & 1, fail))) {
+        if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait_bounded<128>(&sh.mma_done[s], (use - 1) & 1, fail))) {
           *fail = 1;
           go = false;
           break;
         }
-        const half2 s2 = __half2half2(__low2half(csz));
+        // (q - z) * s per pair of weights, the arithmetic of dequant_w4a16_kernel. The nibbles at bits 4-7 / 20-23 are
+        // taken where they stand, as 1024 + 16 q, and multiplied by s / 16 - the same real product, hence the same
+        // rounding, whenever s / 16 is exact in fp16 (checked; a subnormal scale takes the shifted form). That leaves
+        // one shift and four logic operations per word on the ALU pipe, which is what bounds this loop.
+        const half sc = __low2half(csz), sc16 = __hmul(sc, __float2half_rn(0.0625f));
+        const half2 s2 = __half2half2(sc), s2h = __half2half2(sc16);
         const half2 zl = __hadd2(__half2half2(__high2half(csz)), k1024);
+        const half2 zh = __hfma2(__half2half2(__high2half(csz)), __float2half2_rn(16.f), k1024);
+        // ... and 1024 + 16 z must be sixteen times what 1024 + z rounds z to (it is, for the format's integer zeros)
+        const bool exact16 = __heq(__hmul(sc16, __float2half_rn(16.f)), sc) &&
+                             __heq(__hsub(__low2half(zh), __low2half(k1024)),
+                                   __hmul(__hsub(__low2half(zl), __low2half(k1024)), __float2half_rn(16.f)));
         const uint32_t w2[2] = {cw.x, cw.y};
         uint8_t* dst = base + s * stage_bytes;
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          const uint32_t w = w2[q];
+          const uint32_t w = w2[q], w8 = w >> 8;
           uint4 o;
           o.x = as_u32(__hmul2(__hsub2(nib_lo(w), zl), s2));
-          o.y = as_u32(__hmul2(__hsub2(nib_lo(w >> 4), zl), s2));
-          o.z = as_u32(__hmul2(__hsub2(nib_lo(w >> 8), zl), s2));
-          o.w = as_u32(__hmul2(__hsub2(nib_lo(w >> 12), zl), s2));
-          if (!valid) o = make_uint4(0u, 0u, 0u, 0u);
+          o.z = as_u32(__hmul2(__hsub2(nib_lo(w8), zl), s2));
+          if (exact16) {
+            o.y = as_u32(__hmul2(__hsub2(as_h2((w & 0x00F000F0u) | 0x64006400u), zh), s2h));
+            o.w = as_u32(__hmul2(__hsub2(as_h2((w8 & 0x00F000F0u) | 0x64006400u), zh), s2h));
+          } else {
+            o.y = as_u32(__hmul2(__hsub2(nib_lo(w >> 4), zl), s2));
+            o.w = as_u32(__hmul2(__hsub2(nib_lo(w >> 12), zl), s2));
+          }
+          // rows past N carry zero words and a zero scale: their products are zeros without a special case
           *reinterpret_cast<uint4*>(dst + sw128_offset(r, 2 * qt + q)) = o;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
@@ -246,7 +266,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint32_t* __
       const uint32_t idesc = umma_idesc_f16(kPfRows, Tpad);
       bool ok = true;
       for (int j = 0, s = 0, use = 0; j < n && ok; ++j) {
-        ok = mbar_wait_bounded(&sh.a_full[s], use & 1, fail) && mbar_wait_bounded(&sh.b_full[s], use & 1, fail);
+        ok = mbar_wait_bounded<0>(&sh.a_full[s], use & 1, fail) && mbar_wait_bounded<0>(&sh.b_full[s], use & 1, fail);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t da = umma_desc_sw128(smem_addr(base + s * stage_bytes));
@@ -266,7 +286,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint32_t* __
       pdl_wait();   // X is the predecessor's output; the weights, read by the other warps meanwhile, are not
       int issued = 0;
       for (int j = 0, s = 0, use = 0; j < n; ++j) {
-        if (use >= 1 && !mbar_wait_bounded(&sh.mma_done[s], (use - 1) & 1, fail)) {
+        if (use >= 1 && !mbar_wait_bounded<32>(&sh.mma_done[s], (use - 1) & 1, fail)) {
           *fail = 1;
           break;
         }
@@ -277,7 +297,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint32_t* __
       }
       if (*fail)   // giving up: let the copies still in flight land before the CTA's shared memory goes away
         for (int j = issued > ns ? issued - ns : 0; j < issued; ++j)
-          mbar_wait_bounded(&sh.b_full[j % ns], (j / ns) & 1, nullptr);
+          mbar_wait_bounded<64>(&sh.b_full[j % ns], (j / ns) & 1, nullptr);
     }
   }
   __syncwarp();
@@ -285,7 +305,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint32_t* __
   // ---- epilogue 1: accumulator -> fp32 partial tile P[token][128 features] in shared memory (over the idle stages)
   float* P = reinterpret_cast<float*>(base);
   if (warp < kPfDequantWarps) {
-    const bool ok = mbar_wait_bounded(&sh.acc_done, 0, fail);
+    const bool ok = mbar_wait_bounded<256>(&sh.acc_done, 0, fail);
     if (!ok) *fail = 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
