@@ -133,10 +133,14 @@ int b200_paged_attention_batched_v(int version, const void* q, const void* kc, c
  * [(n_q + 2 n_kv) * D] vector of the step (left untouched), every block rotates its own query heads, and the block
  * of the last split rotates k, stores k and v at position *pos of the caches and attends to them. The context
  * pos + 1 must lie within max_splits * PS. Pages or splits the ring kernel does not cover run as the two separate
- * kernels. D in {64, 128}; cos_t, sin_t fp32 [max_pos, D/2]. */
+ * kernels. D in {64, 128}; cos_t, sin_t fp32 [max_pos, D/2].
+ * arrive: NULL, or n_kv ints that are zero before the first call. With it the split partials are merged inside the
+ * same launch by the last block of each kv head to finish (an arrival count, nobody waits; the count is back at zero
+ * when the call completes), so no combine kernel is launched: same numbers, one launch less. Calls that share an
+ * arrive array must not overlap. */
 int b200_rope_paged_attention(void* qkv, const float* cos_t, const float* sin_t, void* kc, void* vc, const int* bt,
                               const int* pos, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
-                              float* o_part, float* m_part, float* l_part, void* out, void* stream);
+                              float* o_part, float* m_part, float* l_part, void* out, int* arrive, void* stream);
 
 /* Health word of the attention kernels on the current device (no counterpart in the reference): *code = 0, or 1 once
  * a thread block gave up a bounded wait for its own asynchronous copies, in which case the outputs of that call are

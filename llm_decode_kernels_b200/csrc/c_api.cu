@@ -45,7 +45,7 @@ cudaError_t paged_attention_status(int* code);
 cudaError_t rope_paged_attention_dispatch(void* qkv, const float* cos_t, const float* sin_t, void* kc, void* vc,
                                           const int* bt, const int* pos, int n_q, int n_kv, int D, int log2P, int PS,
                                           int max_splits, float* o_part, float* m_part, float* l_part, void* out,
-                                          cudaStream_t st);
+                                          int* arrive, cudaStream_t st);
 cudaError_t tp_allreduce_add_rmsnorm_dispatch(const void* const* peers, int rank, int W, size_t off, void* x,
                                               const void* w, void* out, int H, float eps, cudaStream_t st);
 cudaError_t tp_allgather_dispatch(const void* const* peers, int rank, int W, size_t off, void* dst, int n,
@@ -205,7 +205,7 @@ int b200_paged_attention(int version, const void* q, const void* kc, const void*
 
 int b200_rope_paged_attention(void* qkv, const float* cos_t, const float* sin_t, void* kc, void* vc, const int* bt,
                               const int* pos, int n_q, int n_kv, int D, int log2P, int PS, int max_splits,
-                              float* o_part, float* m_part, float* l_part, void* out, void* stream) {
+                              float* o_part, float* m_part, float* l_part, void* out, int* arrive, void* stream) {
   REQUIRE(qkv && cos_t && sin_t && kc && vc && bt && pos && out, B200_ERR_ARG);
   REQUIRE(n_q > 0 && n_kv > 0 && PS > 0 && max_splits > 0 && max_splits <= 65535 && log2P >= 0 && log2P < 16,
           B200_ERR_ARG);
@@ -216,7 +216,7 @@ int b200_rope_paged_attention(void* qkv, const float* cos_t, const float* sin_t,
   REQUIRE(hpg == 1 || hpg == 2 || hpg == 4 || hpg == 8, B200_ERR_SHAPE);
   REQUIRE(aligned16(kc) && aligned16(vc) && aligned16(qkv) && aligned16(cos_t) && aligned16(sin_t), B200_ERR_ALIGN);
   return finish(b200::rope_paged_attention_dispatch(qkv, cos_t, sin_t, kc, vc, bt, pos, n_q, n_kv, D, log2P, PS,
-                                                    max_splits, o_part, m_part, l_part, out, S(stream)));
+                                                    max_splits, o_part, m_part, l_part, out, arrive, S(stream)));
 }
 
 int b200_paged_attention_status(int* code) {
@@ -295,7 +295,8 @@ int b200_embed_row(const void* emb, const long long* tok, void* x, int H, int V,
 static inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
 size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D, int grid) {
-  const size_t per_layer = (size_t)(n_q + 2 * n_kv) * D + (size_t)n_q * D + H + I + H;
+  if (grid <= 0 || n_q <= 0) return 0;
+  const size_t per_layer = b200::step_words_per_layer(H, I, n_q, n_kv, D, b200::step_att_slices(grid, n_q));
   return (per_layer * L + (size_t)grid * 4) * sizeof(uint32_t);
 }
 
@@ -329,6 +330,7 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
   p.cos_t = d->cos_t; p.sin_t = d->sin_t; p.bt = d->bt; p.tok = d->tok; p.pos = d->pos; p.history = d->history;
   p.logits = (half*)d->logits; p.xchg = (uint32_t*)d->xchg; p.ctrl = (b200::StepCtrl*)d->ctrl;
   p.trace = d->trace;
+  p.att_slices = b200::step_att_slices(d->grid, d->n_q);
   // shared-memory plan
   const int ncw = b200::decode_step_consumer_warps();
   const int resid_bytes = align_up(2 * d->H, 128);

@@ -9,13 +9,14 @@
 //     copies (cp.async.bulk + mbarrier transaction counts). Neither weights nor cached K/V depend on this step's
 //     activations, so the producer runs ahead of the computation by the depth of the ring and HBM never idles
 //     while CTAs wait for each other;
-//   * 12 consumer warps do the arithmetic out of the ring on the tensor cores (see "inner product" below), with the
-//     row length K split across the warps: warp w owns the 128-column units w, w + 12, ... of every row tile, so it
+//   * 11 consumer warps do the arithmetic out of the ring on the tensor cores (see "inner product" below), with the
+//     row length K split across the warps: warp w owns the 128-column units w, w + 11, ... of every row tile, so it
 //     needs only its own 128-element pieces of the activation vector and fetches exactly those - no CTA-wide staging
 //     pass and no barrier in front of a GEMV. The warps' partial sums meet in shared memory once per matrix.
-//     (Thirteen warps, not seventeen: a thread then has 128 registers instead of 96, and this kernel must not spill -
+//     (Twelve warps in all, three per scheduler: a thread then has 168 registers, and this kernel must not spill -
 //     with 227 KB of the SM's memory configured as shared there is next to no L1 left, so spilled registers would
-//     be fetched from the L2, a microsecond each time, in a kernel whose phases last a microsecond;)
+//     be fetched from the L2, a microsecond each time, in a kernel whose phases last a microsecond. A thirteenth
+//     warp puts four on one scheduler and caps every thread at 128 registers, seventeen warps at 96;)
 //   * CTAs exchange activation vectors through global memory WITHOUT grid barriers: every fp16 result is stored
 //     as a 32-bit word (tag << 16 | value) whose tag is this step's epoch; a consumer polls the words it needs until
 //     all carry the current tag. One store + one load crosses the chip instead of fence + atomic + poll + load.
@@ -50,9 +51,11 @@
 //
 // Phases per layer (the reference's operator order, with the same rounding points as its fused kernels):
 //   A  resid += down[l-1] (layer 0: resid = embedding row);  x = RMSNorm(resid) * ln1;  qkv = Wqkv x
-//   B  attention: CTA h < n_q takes query head h: RoPE on q and k, append k, v to the paged cache, then per-warp
-//      online softmax over the cached tokens (from the ring) plus the new token, merged once across warps
-//   C  o = Wo attn
+//   B  attention: query head h is shared by J CTAs (as many as the grid has to spare, at most 4), CTA h + j n_q
+//      taking every J-th 128-token stage of the context: RoPE on q and k, (slice 0) append k, v to the paged cache,
+//      then per-warp online softmax over the slice's cached tokens (from the ring), merged once across warps; the
+//      slice's normalised output and log-sum-exp go to the exchange
+//   C  o = Wo attn, attn merged from the J slices of each head while it is staged
 //   D  resid += o;  x = RMSNorm(resid) * ln2;  act = SwiGLU(Wgate x, Wup x)
 //   E  down = Wdown act
 // then resid += down;  x = RMSNorm(resid) * norm_f;  logits = Whead x;  per-CTA argmax candidates; CTA 0 merges
@@ -72,14 +75,18 @@ namespace b200 {
 
 namespace {
 
-constexpr int kNCW = 12;                    // consumer warps (with the producer: 13 warps, 128 registers a thread)
+#ifndef B200_STEP_CONSUMER_WARPS
+#define B200_STEP_CONSUMER_WARPS 11   // build-time knob for measurements
+#endif
+constexpr int kNCW = B200_STEP_CONSUMER_WARPS;   // consumer warps (with the producer: 12 warps = 3 per scheduler, 168 registers)
 constexpr int kNT = kNCW * 32;              // consumer threads
 constexpr int kThreads = kNT + 32;          // + producer warp
 constexpr int kMaxStages = 16;
 constexpr int kSpinLimit = 1 << 18;         // polls / try_waits before a wait gives up (tens of milliseconds)
 constexpr int kHeaderBytes = 2048;
-constexpr int kMaxKvTokens = 128;           // cached tokens per ring stage in attention (3 rounds of 12 warps x 4 tokens)
+constexpr int kMaxKvTokens = 128;           // cached tokens per ring stage in attention (3 rounds of 11 warps x 4 tokens)
 constexpr int kKvRounds = (kMaxKvTokens + 4 * kNCW - 1) / (4 * kNCW);
+constexpr int kSliceMinContext = 1152;      // cached tokens from which attention is cut into context slices
 constexpr int kPollBatch = 4;               // exchange granules a lane keeps in flight while it polls (plain staging)
 constexpr int kNormBatch = 2;               // the same where a norm follows: units of the residual stream per pass
 
@@ -255,6 +262,32 @@ DEVI uint2 poll4(const Cta& c, const uint32_t* p) {
   poll_many<1>(c, p, 0, 1, out);
   return out[0];
 }
+// The same for granules at unrelated places: entry k is at word offset off[k] from `base` (32-bit offsets: a dozen
+// 64-bit pointers would not fit beside a dozen granules in flight); bit k of `mask` says whether entry k is in use
+// (warp-uniform).
+template <int NB>
+DEVI void poll_list(const Cta& c, const uint32_t* base, const uint32_t (&off)[NB], uint32_t mask, uint2 (&out)[NB]) {
+  uint4 v[NB];
+#pragma unroll
+  for (int k = 0; k < NB; ++k)
+    if ((mask >> k) & 1u) v[k] = ld_poll4(base + off[k]);
+  int spins = 0;
+  for (;;) {
+    bool ok = true;
+#pragma unroll
+    for (int k = 0; k < NB; ++k)
+      if (((mask >> k) & 1u) && !tags_ok(c, v[k])) ok = false;
+    if (ok || *c.abort()) break;
+    if (++spins > kSpinLimit) { raise(c, ERR_POLL); break; }
+    if ((spins & 255) == 0 && ((volatile StepCtrl*)c.ctrl())->abort) { *c.abort() = 1; break; }
+#pragma unroll
+    for (int k = 0; k < NB; ++k)
+      if (((mask >> k) & 1u) && !tags_ok(c, v[k])) v[k] = ld_poll4(base + off[k]);
+  }
+#pragma unroll
+  for (int k = 0; k < NB; ++k)
+    if ((mask >> k) & 1u) out[k] = payload(v[k]);
+}
 
 // ---- x staging, per warp ------------------------------------------------------------------------------------------
 // Warp w stages the units w, w + kNCW, ... of the activation vector: lane l holds granule l (4 values) of a unit.
@@ -308,6 +341,60 @@ DEVI void stage_plain(const Cta& c, const uint32_t* E, int K, int warp, int lane
 #pragma unroll
     for (int k = 0; k < kPollBatch; ++k)
       if (k < nb) put_unit(c, u0 + kNCW * k, v[k], lane);
+  }
+  __syncwarp();
+}
+
+// x <- the attention output, merged from the J context slices of every head while it is staged: slice j of head h
+// left its normalised output o_j (Eatt + j n_att) and its log-sum-exp l_j as two fp16 words, value and remainder
+// (Else + h * step_lse_words(J) + 2 j); x = sum_j e^(l_j - max l) o_j / sum_j e^(l_j - max l). A slice that saw no
+// token has l_j = -inf and o_j = 0. Lane l of the warp that owns unit u holds 4 values of one head.
+DEVI void stage_attn(const Cta& c, const uint32_t* Eatt, const uint32_t* Else, int J, int n_att, int D, int warp,
+                     int lane) {
+  constexpr int NL = (kStepMaxAttSlices + 1) / 2;   // granules of log-sum-exp words per head
+  const int nunit = n_att >> 7, lsew = step_lse_words(J), ng = lsew >> 2;
+  const uint32_t lbase = (uint32_t)(Else - Eatt);
+  for (int u = warp; u < nunit; u += kNCW) {
+    const int i = 128 * u + 4 * lane, h = i / D;
+    // While the slices are still at work the warp polls the log-sum-exp words only: one or two addresses per head,
+    // the same for all lanes of a head, instead of J granules per lane - 148 CTAs polling every partial would keep
+    // the L2 busy with nothing else. When those are there the outputs are too, or nearly (the second poll checks
+    // their tags all the same). One unit at a time: more granules in flight would not fit into the registers, and
+    // this kernel must not spill.
+    uint32_t loff[NL], ooff[kStepMaxAttSlices];   // word offsets from Eatt (Else lies behind it)
+#pragma unroll
+    for (int g = 0; g < NL; ++g) loff[g] = lbase + (uint32_t)(h * lsew + 4 * g);
+#pragma unroll
+    for (int k = 0; k < kStepMaxAttSlices; ++k) ooff[k] = (uint32_t)(k * n_att + i);
+    uint2 lv[NL], v[kStepMaxAttSlices];
+    poll_list(c, Eatt, loff, (1u << ng) - 1u, lv);
+    poll_list(c, Eatt, ooff, (1u << J) - 1u, v);
+    float lse[kStepMaxAttSlices], M = -CUDART_INF_F;
+#pragma unroll
+    for (int k = 0; k < kStepMaxAttSlices; ++k) {
+      lse[k] = -CUDART_INF_F;
+      if (k < J) {
+        const uint2 pr = lv[k >> 1];
+        const float2 f = __half22float2(as_h2((k & 1) ? pr.y : pr.x));   // (value, remainder)
+        lse[k] = f.x + f.y;
+        M = fmaxf(M, lse[k]);
+      }
+    }
+    float W = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int k = 0; k < kStepMaxAttSlices; ++k) {
+      if (k < J) {
+        const float w = __expf(lse[k] - M);   // the slice with the step's own token is never empty: M is finite
+        const float2 x01 = __half22float2(as_h2(v[k].x)), x23 = __half22float2(as_h2(v[k].y));
+        W += w;
+        o0 = fmaf(w, x01.x, o0), o1 = fmaf(w, x01.y, o1), o2 = fmaf(w, x23.x, o2), o3 = fmaf(w, x23.y, o3);
+      }
+    }
+    const float rW = 1.f / W;
+    uint2 o;
+    o.x = as_u32(__floats2half2_rn(o0 * rW, o1 * rW));
+    o.y = as_u32(__floats2half2_rn(o2 * rW, o3 * rW));
+    put_unit(c, u, o, lane);
   }
   __syncwarp();
 }
@@ -432,13 +519,14 @@ DEVI int kv_tokens_per_stage(const StepParams& p) {
   return t & ~((1 << p.log2P) - 1);
 }
 
-// Producer: the cached K/V rows [0, pos) of one kv head, page by page. Whole pages are copied; rows at or beyond
-// pos in the last page are ignored by the consumer.
-DEVI void produce_kv(const Cta& c, const StepParams& p, const StepLayer& ly, int kvh, int pos, RingPos& rp, int lane) {
+// Producer: the cached K/V rows [0, pos) of one kv head, page by page, for context slice j of J: the stages j, j + J,
+// ... of the context. Whole pages are copied; rows at or beyond pos in the last page are ignored by the consumer.
+DEVI void produce_kv(const Cta& c, const StepParams& p, const StepLayer& ly, int kvh, int j, int J, int pos, RingPos& rp,
+                     int lane) {
   const int tps = kv_tokens_per_stage(p), pps = tps >> p.log2P;
   const uint32_t page_bytes = (uint32_t)(p.D * 2) << p.log2P;
   const int nst = (pos + tps - 1) / tps;
-  for (int st = 0; st < nst; ++st, advance(rp, c.p->ns)) {
+  for (int st = j; st < nst; st += J, advance(rp, c.p->ns)) {
     const int slot = rp.slot;
     if (!wait_bar(c, c.empty(slot), rp.parity, ERR_EMPTY, 200)) return;
     const int pg0 = st * pps, npg = min(pps, ((pos + (1 << p.log2P) - 1) >> p.log2P) - pg0);
@@ -600,16 +688,39 @@ DEVI void reduce_emit(const Cta& c, const Mat& m, const Slice& s, const float* p
   }
 }
 
-// ---- attention for one query head -------------------------------------------------------------------------------------
-// All consumer threads of the CTA. q, k, v of this step come from the tagged qkv exchange, tokens 0..pos-1 from ring
-// stages filled by produce_kv. Lane (t = lane >> 3, c = lane & 7) of warp w owns token slot 4 w + t of a stage and
-// dims [c D/8, (c+1) D/8) of it; each warp keeps a private online-softmax state, merged once at the end.
+// ---- attention for one query head, one context slice ------------------------------------------------------------------
+// All consumer threads of the CTA. q, k, v of this step come from the tagged qkv exchange, the cached tokens of slice
+// j (ring stages j, j + J, ... of the context) from ring stages filled by produce_kv; slice 0 also takes the token
+// of this step and writes it to the cache. Lane (t = lane >> 3, c = lane & 7) of warp w owns token slot 4 w + t of a
+// stage and dims [c D/8, (c+1) D/8) of it; each warp keeps a private online-softmax state, merged once at the end.
+// Output: the slice's normalised partial at Eattn + j n_att and its log-sum-exp at Else (see stage_attn).
 template <int D>
-DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly, const uint32_t* Eqkv, uint32_t* Eattn,
-                         int h, int pos, RingPos& rp, int tid, int trace_at) {
+DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly, uint32_t* E, int u, int pos,
+                         RingPos& rp, int tid, int trace_at) {
+  // E: the layer's exchange block; u: attention unit = head u % n_q, slice u / n_q. Whatever the publishing code at
+  // the end needs is recomputed there from u and the parameter block: the fold loop in between is where this kernel's
+  // register pressure peaks, and every value carried across it costs a register there.
   constexpr int D2 = D / 2, G4 = D / 4, DPL = D / 8;
   const int warp = tid >> 5, lane = tid & 31, ts = lane >> 3, ch = lane & 7;
+  const int J = p.att_slices, h = u % p.n_q, j = u / p.n_q;
+  const int Js = pos >= kSliceMinContext ? J : 1;            // stride of a slice's stages: 1 = slice 0 takes them all
   const int hpg = p.n_q / p.n_kv, kvh = h / hpg;
+  const int tps = kv_tokens_per_stage(p);
+  const int nst = (pos + tps - 1) / tps;                       // stages of the whole context
+  const uint32_t* Eqkv = E;
+  if (j > 0 && (j >= nst || Js == 1)) {
+    // no cached token falls into this slice: an empty partial, without touching q, k, v or the ring
+    uint32_t* Eo = E + (size_t)(p.n_q + 2 * p.n_kv) * D + (size_t)j * p.n_q * D + (size_t)h * D;
+    uint32_t* El = E + (size_t)(p.n_q + 2 * p.n_kv) * D + (size_t)J * p.n_q * D + (size_t)h * step_lse_words(J) + 2 * j;
+    const uint32_t ninf = c.tagw | 0xFC00u;                    // fp16 -inf
+    if (tid < D) st_tagged(Eo + tid, c.tagw);
+    if (tid == 0) {
+      st_tagged(El, ninf);
+      st_tagged(El + 1, c.tagw);
+      if ((J & 1) && j == J - 1) { st_tagged(El + 2, ninf); st_tagged(El + 3, c.tagw); }
+    }
+    return;
+  }
   float* qf = c.att();                                         // [D] rotated q * 1/sqrt(D)
   half* knew = reinterpret_cast<half*>(c.att() + D);           // [D] rotated k of this step
   half* vnew = knew + D;                                     // [D]
@@ -643,13 +754,13 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
       } else {
         knew[i] = ra;
         knew[i + D2] = rb;
-        if (h % hpg == 0) { ly.kc[row_new + i] = ra; ly.kc[row_new + i + D2] = rb; }
+        if (h % hpg == 0 && j == 0) { ly.kc[row_new + i] = ra; ly.kc[row_new + i + D2] = rb; }
       }
     } else {
       const int i = tid - D;
       const half v = raw[2 * D + i];
       vnew[i] = v;
-      if (h % hpg == 0) ly.vc[row_new + i] = v;
+      if (h % hpg == 0 && j == 0) ly.vc[row_new + i] = v;
     }
   }
   consumer_sync();
@@ -710,18 +821,18 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
   };
 
   // The cached tokens come stage by stage from the ring. The token of this step (rotated k, v in the attention
-  // scratch) rides along as token number nt of the last stage: a stage holds at most kMaxKvTokens tokens and the
-  // warps' slots cover 4 kNCW kKvRounds > kMaxKvTokens, so there is always a slot for it and it costs no chain of its own.
-  static_assert(4 * kNCW * kKvRounds > kMaxKvTokens, "the last stage needs a spare slot for the token of this step");
-  const int tps = kv_tokens_per_stage(p);
-  const int nst = (pos + tps - 1) / tps;
+  // scratch) belongs to slice 0 and rides along as token number nt of that slice's last stage: a stage holds at most
+  // kMaxKvTokens tokens and the warps' slots cover 4 kNCW kKvRounds > kMaxKvTokens, so there is always a slot for it
+  // and it costs no chain of its own.
+  static_assert(4 * kNCW * kKvRounds > kMaxKvTokens, "a stage needs a spare slot for the token of this step");
+  const bool takes_new = j == 0;
   const uint32_t knew_off = (uint32_t)(reinterpret_cast<const uint8_t*>(knew) - c.smem) + ch * DPL * 2;
   const uint32_t vnew_off = (uint32_t)(reinterpret_cast<const uint8_t*>(vnew) - c.smem) + ch * DPL * 2;
 #ifdef B200_STEP_TRACE
   long long waited = 0;
 #endif
-  for (int st = 0; st < max(nst, 1); ++st) {
-    const bool have = st < nst, last = st >= nst - 1;   // nst == 0 (empty cache): one pass without a ring stage
+  for (int st = j; st < nst || (nst == 0 && st == 0); st += Js) {  // nst == 0 (empty cache, slice 0): one pass
+    const bool have = st < nst, last = st + Js >= nst;              // without a ring stage
     const int slot = rp.slot;
 #ifdef B200_STEP_TRACE
     const long long w0 = now_ns();
@@ -738,10 +849,10 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
       bool valid[kKvRounds];
 #pragma unroll
       for (int r = 0; r < kKvRounds; ++r) {
-        const int j = 4 * warp + ts + 4 * kNCW * r;
-        valid[r] = j < nt || (last && j == nt);
-        koff[r] = j < nt ? kbase + (uint32_t)j * (D * 2) : knew_off;
-        voff[r] = j < nt ? vbase + (uint32_t)j * (D * 2) : vnew_off;
+        const int jt = 4 * warp + ts + 4 * kNCW * r;   // token slot of the stage
+        valid[r] = jt < nt || (takes_new && last && jt == nt);
+        koff[r] = jt < nt ? kbase + (uint32_t)jt * (D * 2) : knew_off;
+        voff[r] = jt < nt ? vbase + (uint32_t)jt * (D * 2) : vnew_off;
       }
       fold(koff, voff, valid);
     }
@@ -782,7 +893,18 @@ DEVI void attention_head(const Cta& c, const StepParams& p, const StepLayer& ly,
       o = fmaf(a, wo[w * D + tid], o);
       L = fmaf(a, wl[w], L);
     }
-    st_tagged(Eattn + (size_t)h * D + tid, c.tagw | (uint32_t)__half_as_ushort(__float2half(o / L)));
+    const int Jp = p.att_slices, hp = u % p.n_q, jp = u / p.n_q;
+    uint32_t* Eo = E + (size_t)(p.n_q + 2 * p.n_kv) * D + (size_t)jp * p.n_q * D + (size_t)hp * D;
+    uint32_t* El = E + (size_t)(p.n_q + 2 * p.n_kv) * D + (size_t)Jp * p.n_q * D + (size_t)hp * step_lse_words(Jp) + 2 * jp;
+    const uint32_t ninf = c.tagw | 0xFC00u;
+    st_tagged(Eo + tid, c.tagw | (uint32_t)__half_as_ushort(__float2half(o / L)));
+    if (tid == 0) {   // log-sum-exp of the slice as an fp16 value and the fp16 remainder
+      const float lse = M + __logf(L);
+      const half hi = __float2half(lse), lo = __float2half(lse - __half2float(hi));
+      st_tagged(El, c.tagw | (uint32_t)__half_as_ushort(hi));
+      st_tagged(El + 1, c.tagw | (uint32_t)__half_as_ushort(lo));
+      if ((Jp & 1) && jp == Jp - 1) { st_tagged(El + 2, ninf); st_tagged(El + 3, c.tagw); }
+    }
   }
   stamp(c, trace_at + 2);
   consumer_sync();
@@ -826,7 +948,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   c.tagw = ((epoch % 65535u) + 1u) << 16;
   const int pos = p.pos[0];
   const int hpg = p.n_q / p.n_kv;
-  const int per_layer = n_qkv + n_att + p.H + p.I + p.H;   // exchange words per layer
+  // Context slices per query head in attention (the exchange layout always has room for J). Slicing pays from about
+  // 1200 cached tokens on: below that the K/V copies of 96 more CTAs delay the weight stream (an SM's copy engine takes
+  // ~1 us for the 16 page copies of a stage) and the merge costs the o projection's staging a second trip through
+  // the L2, which together outweigh a fold that is shorter by one or two stages. In a step below the threshold slice
+  // 0 takes the whole context and the others publish empty partials (every exchange word is rewritten in every
+  // step - the tag invariant - but nobody waits for these). Every CTA reads the same pos, so all agree.
+  const int J = p.att_slices;
+  const bool sliced = pos >= kSliceMinContext && J > 1;
+  const int per_layer = (int)step_words_per_layer(p.H, p.I, p.n_q, p.n_kv, p.D, J);   // exchange words per layer
 
   if (warp == kNCW) {
     // ================= producer =================
@@ -838,7 +968,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
                            {(const uint8_t*)ly.w[2], p.I, p.H, 1},
                            {(const uint8_t*)ly.w[3], p.H, p.I, 0}};
       produce(c, mats[0], sl[0], rp, lane);
-      for (int h = cta; h < p.n_q && !*c.abort(); h += ncta) produce_kv(c, p, ly, h / hpg, pos, rp, lane);
+      for (int u = cta; u < p.n_q * J && !*c.abort(); u += ncta)   // attention unit u: head u % n_q, slice u / n_q
+        if (sliced || u < p.n_q) produce_kv(c, p, ly, (u % p.n_q) / hpg, u / p.n_q, sliced ? J : 1, pos, rp, lane);
 #pragma unroll
       for (int k = 1; k < 4; ++k)
         if (!*c.abort()) produce(c, mats[k], sl[k], rp, lane);
@@ -873,7 +1004,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
   unsigned long long best = 0ull;
   // RoPE factors and the page of this step's token depend only on pos: the attention CTAs fetch them now, off the
   // critical path, into the attention scratch (first read two barriers into the first attention phase)
-  if (cta < p.n_q) {
+  if (cta < p.n_q * J) {
     float* rope = c.att() + 4 * p.D + kNCW * p.D + 2 * kNCW;
     if (tid < (p.D >> 1)) {
       rope[tid] = p.cos_t[(size_t)pos * (p.D >> 1) + tid];
@@ -890,7 +1021,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     const bool is_head = l == p.L;
     const StepLayer& ly = lys[is_head ? 0 : l];
     uint32_t* E = p.xchg + (size_t)l * per_layer;
-    uint32_t *Eqkv = E, *Eatt = E + n_qkv, *Eo = Eatt + n_att, *Eact = Eo + p.H, *Edown = Eact + p.I;
+    uint32_t *Eqkv = E, *Eatt = E + n_qkv, *Else = Eatt + (size_t)J * n_att;
+    uint32_t *Eo = Else + p.n_q * step_lse_words(J), *Eact = Eo + p.H, *Edown = Eact + p.I;
     Mat m;
     const uint32_t* Ein;
     const half* nw = nullptr;   // norm weight: non-null selects "residual add + RMSNorm" staging
@@ -934,7 +1066,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
       }
       stage_norm(c, Ein, emb_row, nw, n_in, p.eps, warp, lane);
     }
-    else if (s.nt > 0) stage_plain(c, Ein, n_in, warp, lane);
+    else if (s.nt > 0) {
+      if (ph == 1 && sliced) stage_attn(c, Eatt, Else, J, n_att, p.D, warp, lane);
+      else stage_plain(c, Ein, n_in, warp, lane);   // one slice: its normalised output is the attention output
+    }
     const int tr_at = kTraceHead + kTracePerLayer * l + kTracePerPhase * ph;
     stamp(c, tr_at);
     gemv(c, m, s, part, pstride, rp, warp, lane, tr_at + 1);
@@ -945,8 +1080,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const __grid_c
     stamp(c, tr_at + 4);
     if (is_head) break;
     if (ph == 0) {
-      for (int h = cta; h < p.n_q; h += ncta) {
-        attention_head<D>(c, p, ly, Eqkv, Eatt, h, pos, rp, tid, kTraceHead + kTracePerLayer * l + 4 * kTracePerPhase);
+      for (int u = cta; u < p.n_q * J; u += ncta) {
+        attention_head<D>(c, p, ly, E, u, pos, rp, tid, kTraceHead + kTracePerLayer * l + 4 * kTracePerPhase);
         if (consumer_sync_or(*c.abort())) return;
       }
       stamp(c, kTraceHead + kTracePerLayer * l + 4 * kTracePerPhase + 3);

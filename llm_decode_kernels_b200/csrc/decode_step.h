@@ -50,7 +50,27 @@ struct StepParams {
   int stage_bytes, ns;   // stage pitch and number of stages of the ring
   int part_stride;       // row slots per warp in a partial-sum buffer of the layer phases (two buffers)
   int part_stride_head;  // the same for the LM head (one buffer over the same area)
+  int att_slices;        // J: context slices per query head in attention (step_att_slices)
 };
+
+// Attention of the step: query head h is worked on by J CTAs, slice j taking the ring stages j, j + J, ... of the
+// cached context; J = as many as the grid has CTAs for, at most kStepMaxAttSlices. Each slice publishes a normalised
+// partial output and its log-sum-exp (two fp16 words: value and remainder); the CTAs that stage the attention output
+// for the o projection merge the J partials while they stage.
+#ifndef B200_STEP_MAX_SLICES
+#define B200_STEP_MAX_SLICES 4   // build-time knob for measurements: 1 = one CTA per query head
+#endif
+constexpr int kStepMaxAttSlices = B200_STEP_MAX_SLICES;
+inline int step_att_slices(int grid, int n_q) {
+  const int j = grid / n_q;
+  return j < 1 ? 1 : (j > kStepMaxAttSlices ? kStepMaxAttSlices : j);
+}
+// exchange words per query head for the log-sum-exps: pairs (value, remainder) per slice, padded to whole granules
+__host__ __device__ inline int step_lse_words(int J) { return (2 * J + 3) & ~3; }
+// exchange words of one layer: qkv, J partial attention outputs, log-sum-exps, o, act, down
+__host__ __device__ inline size_t step_words_per_layer(int H, int I, int n_q, int n_kv, int D, int J) {
+  return (size_t)(n_q + 2 * n_kv) * D + (size_t)J * n_q * D + (size_t)n_q * step_lse_words(J) + H + I + H;
+}
 
 size_t decode_step_plan_smem(StepParams& p, int resid_bytes, int xin_bytes, int xsum_bytes, int att_bytes,
                              int part_bytes, int table_bytes);

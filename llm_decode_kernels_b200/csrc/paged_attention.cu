@@ -517,7 +517,8 @@ __global__ void __launch_bounds__(kMmaThreads, D == 64 ? 4 : 2)
 paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, const half* __restrict__ vc,
                       const int* __restrict__ bt, int bt_stride, const int* __restrict__ pos_ptr, int n_kv, int log2P,
                       int PS, float scale, float* __restrict__ o_part, float* __restrict__ m_part,
-                      float* __restrict__ l_part, half* __restrict__ out, int max_splits, const RopeArgs ra) {
+                      float* __restrict__ l_part, half* __restrict__ out, int max_splits, const RopeArgs ra,
+                      int* __restrict__ arrive) {
   static_assert(!ROPE || KH == 1, "the fused RoPE path is written for one kv head per block");
   pdl_launch_dependents();
   pdl_wait();
@@ -535,7 +536,7 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
   __shared__ uint64_t full[NS], empty[NS];
   __shared__ float wm[kAttnWarps][8], wl[kAttnWarps][8];
   __shared__ int bt_s[kBtCache];
-  __shared__ int fail_s;
+  __shared__ int fail_s, last_s;
 
   const int kvh0 = blockIdx.x * KH, split = blockIdx.y, b = blockIdx.z;
   const int n_q = n_kv * HPG;
@@ -768,6 +769,10 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
           bar_wait(&full[k % NS], (uint32_t)(k / NS) & 1u, kWaitLimit);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kAttnThreads) : "memory");
+      if (arrive != nullptr && nsplit > 1 && tid == 0) {   // keep the arrival count whole for the calls that follow
+        int* cnt = arrive + (size_t)b * gridDim.x + blockIdx.x;
+        if (atomicAdd(cnt, 1) == nsplit - 1) *cnt = 0;
+      }
       return;
     }
   }
@@ -801,11 +806,44 @@ paged_attn_mma_kernel(const half* __restrict__ q, const half* __restrict__ kc, c
       out[hq * D + d] = __float2half(o / L);
     } else {
       o_part[(hq * max_splits + split) * D + d] = o;
-      if (d == 0) {   // the combine kernel works in natural-log units
+      if (d == 0) {   // the combine step works in natural-log units
         m_part[hq * max_splits + split] = M * 0.69314718055994530942f;
         l_part[hq * max_splits + split] = L;
       }
     }
+  }
+  if (arrive == nullptr || nsplit == 1) return;   // the combine kernel follows / nothing to combine
+
+  // ---- combine as the last block to arrive: every block of (sequence, kv head) takes a ticket after its partials
+  // are out; the one that draws the last ticket merges all splits (nobody waits), then zeroes the count for the next
+  // call. Blocks of splits beyond the live context never get here and are not counted.
+  __threadfence();
+  asm volatile("bar.sync 1, %0;" ::"n"(kAttnThreads) : "memory");
+  if (tid == 0) {
+    int* cnt = arrive + (size_t)b * gridDim.x + blockIdx.x;
+    last_s = atomicAdd(cnt, 1) == nsplit - 1;
+    if (last_s) *cnt = 0;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kAttnThreads) : "memory");
+  if (!last_s) return;
+  __threadfence();
+  for (int i = tid; i < KH * HPG * D; i += kAttnThreads) {
+    const int hk = i / (HPG * D), h = (i / D) % HPG, d = i % D;
+    const size_t hq = (size_t)b * n_q + (kvh0 + hk) * HPG + h;
+    const float* mp = m_part + hq * max_splits;
+    const float* lp = l_part + hq * max_splits;
+    const float* op = o_part + hq * max_splits * D + d;
+    float M = -CUDART_INF_F, L = 0.f, acc_o = 0.f;   // same arithmetic, in the same order, as paged_attn_combine_kernel
+#pragma unroll 8
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = __ldcg(mp + s), ls = __ldcg(lp + s), os = __ldcg(op + (size_t)s * D);
+      const float Mn = fmaxf(M, ms);
+      const float a = __expf(M - Mn), c = __expf(ms - Mn);
+      L = fmaf(L, a, c * ls);
+      acc_o = fmaf(acc_o, a, c * os);
+      M = Mn;
+    }
+    out[hq * D + d] = __float2half(acc_o / L);
   }
 }
 
@@ -867,19 +905,20 @@ static cudaError_t launch_mma(const AttnArgs& a, int dev, cudaStream_t st) {
   if (e != cudaSuccess) return e;
   B200_LAUNCH(paged_attn_mma_kernel<D, HPG, KH, false>, dim3(a.n_kv / KH, a.max_splits, a.B), dim3(kMmaThreads),
               attn_ring_bytes<D>(), st, a.q, a.kc, a.vc, a.bt, a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale,
-              a.o_part, a.m_part, a.l_part, a.out, a.max_splits, RopeArgs{nullptr, nullptr, nullptr, nullptr});
+              a.o_part, a.m_part, a.l_part, a.out, a.max_splits, RopeArgs{nullptr, nullptr, nullptr, nullptr},
+              (int*)nullptr);
   return cudaPeekAtLastError();
 }
 
 // the same kernel with RoPE + KV-append folded in: a.q is the raw qkv vector of the step
 template <int D, int HPG>
-static cudaError_t launch_mma_rope(const AttnArgs& a, const RopeArgs& r, int dev, cudaStream_t st) {
+static cudaError_t launch_mma_rope(const AttnArgs& a, const RopeArgs& r, int* arrive, int dev, cudaStream_t st) {
   static bool configured[64] = {};
   const cudaError_t e = allow_ring(paged_attn_mma_kernel<D, HPG, 1, true>, attn_ring_bytes<D>(), &configured[dev]);
   if (e != cudaSuccess) return e;
   B200_LAUNCH(paged_attn_mma_kernel<D, HPG, 1, true>, dim3(a.n_kv, a.max_splits, a.B), dim3(kMmaThreads),
               attn_ring_bytes<D>(), st, a.q, a.kc, a.vc, a.bt, a.bt_stride, a.pos, a.n_kv, a.log2P, a.PS, a.scale,
-              a.o_part, a.m_part, a.l_part, a.out, a.max_splits, r);
+              a.o_part, a.m_part, a.l_part, a.out, a.max_splits, r, arrive);
   return cudaPeekAtLastError();
 }
 
@@ -953,11 +992,12 @@ cudaError_t rope_append_dispatch(void* qkv, const float* cos_t, const float* sin
                                  cudaStream_t st);
 
 // RoPE + KV-append + attention (+ combine) for one sequence. Where the ring kernel does not apply (page or split
-// size), the two stand-alone kernels run one after the other: same result, one launch more.
+// size), the two stand-alone kernels run one after the other: same result, one launch more. arrive: nullptr, or
+// n_kv zeroed ints - the combine then happens inside the attention kernel (one launch in all).
 cudaError_t rope_paged_attention_dispatch(void* qkv, const float* cos_t, const float* sin_t, void* kc, void* vc,
                                           const int* bt, const int* pos, int n_q, int n_kv, int D, int log2P, int PS,
                                           int max_splits, float* o_part, float* m_part, float* l_part, void* out,
-                                          cudaStream_t st) {
+                                          int* arrive, cudaStream_t st) {
   const int hpg = n_q / n_kv;
   const bool ring_ok = log2P >= 3 && log2P <= 6 && PS % (1 << log2P) == 0;
   if (!ring_ok) {
@@ -974,12 +1014,12 @@ cudaError_t rope_paged_attention_dispatch(void* qkv, const float* cos_t, const f
   const RopeArgs r = {cos_t, sin_t, (half*)kc, (half*)vc};
   cudaError_t e = cudaErrorInvalidValue;
 #define B200_ROPE_CASE(DD, H) \
-  if (D == DD && hpg == H) e = launch_mma_rope<DD, H>(a, r, dev, st);
+  if (D == DD && hpg == H) e = launch_mma_rope<DD, H>(a, r, arrive, dev, st);
   B200_ROPE_CASE(64, 1) B200_ROPE_CASE(64, 2) B200_ROPE_CASE(64, 4) B200_ROPE_CASE(64, 8)
   B200_ROPE_CASE(128, 1) B200_ROPE_CASE(128, 2) B200_ROPE_CASE(128, 4) B200_ROPE_CASE(128, 8)
 #undef B200_ROPE_CASE
   if (e != cudaSuccess) return e;
-  if (max_splits > 1) {
+  if (max_splits > 1 && arrive == nullptr) {   // with an arrival array the last block of each head has combined
     B200_LAUNCH(paged_attn_combine_kernel, dim3(n_q, 1), dim3(D), 0, st, o_part, m_part, l_part, pos, PS, max_splits, D,
                 (half*)out);
     e = cudaPeekAtLastError();

@@ -87,9 +87,9 @@ def run_ctx(a):
         return Model(sd, c, DecodeConfig(group=128, quant=quant, qparams=qparams, max_ctx=max_ctx, seed=0,
                                          fuse_rope_attention=a.fuse_rope, **kw))
 
-    m = build()
+    m = build(**({"step_kernel": a.step_kernel} if a.step_kernel != "auto" else {}))
     m.kv.normal_()
-    for ctx in (512, 1024, 2048, 4096, 8192):
+    for ctx in a.contexts or (512, 1024, 2048, 4096, 8192):
         m.prepare(ctx + a.tokens + 8)
         us = time_decode(m, ctx, a.tokens)
         nbytes = m.bytes_per_token(ctx + a.tokens // 2)
@@ -98,7 +98,7 @@ def run_ctx(a):
                                 "step_kernel": "persistent" if m.persistent else "multi", "part_size": m.part_size}
         print(ctx, res["contexts"][ctx], flush=True)
     del m
-    for name, kw in (("all fused, one launch per operator", dict(step_kernel="multi")),
+    for name, kw in () if a.no_ablations else (("all fused, one launch per operator", dict(step_kernel="multi")),
                      ("dequant-in-GEMV off", dict(ablate=("dequant",))),
                      ("residual+RMSNorm off", dict(ablate=("norm",))),
                      ("SwiGLU off", dict(ablate=("swiglu",))),
@@ -235,6 +235,10 @@ def main():
                     help="tp: tensor-core GEMV from the tile layout (default) / from the row-major tensors / the "
                          "segmented CUDA-core GEMV")
     ap.add_argument("--fuse-rope", action="store_true", help="ctx: RoPE + KV-append inside the attention kernel")
+    ap.add_argument("--step-kernel", default="auto", choices=["auto", "persistent", "multi"],
+                    help="ctx: force the step kernel of the sweep (default: the model's own choice per context)")
+    ap.add_argument("--contexts", type=int, nargs="*", default=None, help="ctx: the contexts of the sweep")
+    ap.add_argument("--no-ablations", action="store_true", help="ctx: skip the ablation runs")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     if a.tokens is None:

@@ -46,7 +46,8 @@ SIGNATURES = {
                                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p],
     "b200_rope_paged_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p],
     "b200_paged_attention_status": [c_void_p],
     "b200_comm_header_bytes": [],
     "b200_comm_alloc": [c_size_t, c_void_p],
@@ -324,9 +325,10 @@ class Ops:
             m_part.data_ptr(), l_part.data_ptr(), out.data_ptr(), _stream()), "paged_attention_batched")
 
     def rope_paged_attention(self, qkv, cos_t, sin_t, pos, bt, kc, vc, n_q, n_kv, part_size, o_part, m_part, l_part,
-                             out):
+                             out, arrive=None):
         """rope_append + paged_attention of one sequence in one partial-kernel launch. qkv fp16 [(n_q + 2 n_kv) D]
-        (not modified), caches [pages, n_kv, P, D], o_part fp32 [n_q, S, D], m/l_part [n_q, S], out fp16 [n_q, D]."""
+        (not modified), caches [pages, n_kv, P, D], o_part fp32 [n_q, S, D], m/l_part [n_q, S], out fp16 [n_q, D].
+        arrive: None, or int32 [n_kv] of zeros - the splits are then merged inside the same launch (no combine kernel)."""
         for t_, n_ in ((qkv, "qkv"), (kc, "kc"), (vc, "vc"), (out, "out")):
             _cuda(t_, n_, torch.float16)
         _cuda(cos_t, "cos_t", torch.float32), _cuda(sin_t, "sin_t", torch.float32)
@@ -339,10 +341,13 @@ class Ops:
         S = o_part.shape[1]
         if tuple(o_part.shape) != (n_q, S, D) or tuple(m_part.shape) != (n_q, S) or m_part.shape != l_part.shape:
             raise RuntimeError("split buffers have inconsistent shapes")
+        if arrive is not None and (_cuda(arrive, "arrive", torch.int32).numel() < n_kv):
+            raise RuntimeError("arrive must hold n_kv ints")
         self._check(self.lib.b200_rope_paged_attention(
             qkv.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(),
             pos.data_ptr(), int(n_q), int(n_kv), D, _ilog2_exact(kc.shape[2], "page size"), int(part_size), S,
-            o_part.data_ptr(), m_part.data_ptr(), l_part.data_ptr(), out.data_ptr(), _stream()), "rope_paged_attention")
+            o_part.data_ptr(), m_part.data_ptr(), l_part.data_ptr(), out.data_ptr(),
+            None if arrive is None else arrive.data_ptr(), _stream()), "rope_paged_attention")
 
     def paged_attention_status(self):
         """0, or 1 once an attention block gave up a bounded wait for its own copies (outputs invalid). Synchronises."""

@@ -76,7 +76,7 @@ class DecodeConfig:
                                  # prepared context cap is within PERSISTENT_MAX_CTX
 
 
-PERSISTENT_MAX_CTX = 2048   # beyond this the in-kernel attention (one CTA per query head) stops paying off
+PERSISTENT_MAX_CTX = 12288   # beyond this the one-launch-per-operator step, whose attention uses every SM, is faster
 
 
 class Linear:
@@ -306,6 +306,8 @@ class Model:
         self.o_part = torch.empty(self.n_q, n_splits, self.D, dtype=torch.float32, device=dev)
         self.m_part = torch.empty(self.n_q, n_splits, dtype=torch.float32, device=dev)
         self.l_part = torch.empty_like(self.m_part)
+        # arrival counts of the split blocks per kv head: the last one to finish merges the splits (no combine launch)
+        self.attn_arrive = torch.zeros(self.n_kv, dtype=torch.int32, device=dev)
         self.graph = None               # a captured graph holds the old geometry
         self._setup_persistent_step()
 
@@ -449,7 +451,8 @@ class Model:
                                            self.attn.view(1, self.n_q, self.D))
         elif self.cfg.fuse_rope_attention:   # RoPE, cache append and attention in one partial-kernel launch
             self.K.rope_paged_attention(self.qkv, self.cos, self.sin, self.pos, self.bt, kc, vc, self.n_q, self.n_kv,
-                                        self.part_size, self.o_part, self.m_part, self.l_part, self.attn)
+                                        self.part_size, self.o_part, self.m_part, self.l_part, self.attn,
+                                        self.attn_arrive)
         elif self.D == 64:
             self.K.rope_append(self.qkv, self.cos, self.sin, self.pos, self.bt, kc, vc, self.n_q, self.n_kv)
             self.K.paged_attention(self.qkv[: self.n_q * self.D], kc, vc, self.bt, self.pos, self.part_size,

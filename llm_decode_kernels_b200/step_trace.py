@@ -38,8 +38,11 @@ def main():
     ap.add_argument("--ctx", type=int, default=256)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--define", action="append", default=[],
+                    help="further macros of the build under trace, e.g. B200_STEP_MAX_SLICES=1 (one CTA per query head)")
     a = ap.parse_args()
-    lib = B.build(defines=("B200_STEP_TRACE",), lib=B.PKG / "libb200decode_trace.so")
+    tag = "".join("_" + d.split("=")[-1] for d in a.define)
+    lib = B.build(defines=("B200_STEP_TRACE", *a.define), lib=B.PKG / f"libb200decode_trace{tag}.so")
     ext.load_library(path=lib)
     from .model import DecodeConfig, Model
     from .shapes import TINYLLAMA, config, random_llama_state

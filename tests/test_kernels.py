@@ -291,8 +291,10 @@ def test_attention_page_sizes_and_poisoned_tail(K, page):
 @pytest.mark.parametrize("D,n_q,n_kv,page", [(64, 32, 4, 16), (128, 8, 2, 16), (64, 8, 8, 32), (64, 16, 4, 4)])
 def test_rope_attention_in_one_launch(K, D, n_q, n_kv, page):
     """b200_rope_paged_attention against b200_rope_append(_batched) followed by b200_paged_attention_batched: the
-    attention output and both caches bit for bit (page 4: the entry point falls back to the two kernels)."""
+    attention output and both caches bit for bit (page 4: the entry point falls back to the two kernels); and the
+    same again with the splits merged inside the launch by the last block to arrive (the count returns to zero)."""
     torch.manual_seed(D + page)
+    arrive = torch.zeros(n_kv, dtype=torch.int32, device=dev)
     cos, sin = (t.to(dev) for t in R.rope_tables(3000, D))
     for ctx, PS in ((1, 64), (17, 64), (64, 64), (65, 64), (300, 128), (1000, 256), (2049, 512)):
         n_pages = (ctx + page - 1) // page + 2
@@ -318,6 +320,12 @@ def test_rope_attention_in_one_launch(K, D, n_q, n_kv, page):
         assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2), (ctx, PS)
         if page >= 8:
             assert torch.equal(q1, qkv)      # the fused kernel leaves qkv alone
+        q3, kc3, vc3 = qkv.clone(), kc.clone(), vc.clone()
+        o3, m3, l3, out3 = bufs()
+        out3.fill_(float("nan"))
+        K.rope_paged_attention(q3, cos, sin, pos, bt, kc3, vc3, n_q, n_kv, PS, o3, m3, l3, out3, arrive)
+        assert torch.equal(out3, out2), ("last-arriver combine", D, n_q, n_kv, page, ctx, PS)
+        assert torch.equal(kc3, kc2) and torch.equal(vc3, vc2) and int(arrive.abs().sum()) == 0
     assert K.paged_attention_status() == 0
 
 

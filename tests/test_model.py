@@ -144,6 +144,30 @@ def test_against_oracle_model(shape, step_kernel):
             break
 
 
+def test_persistent_step_sliced_attention_long_context():
+    """Beyond 1152 cached tokens the persistent step cuts every head's context into slices on different CTAs and
+    merges them while staging the o projection. Teacher-forced across that threshold against the oracle: the logits of
+    the positions on both sides of it, and the cache the step wrote."""
+    c = hf_cfg(512, 2, 8, 2, 1024, 1500)
+    sd = random_state(c, 29)
+    n = 1400
+    m = Model(sd, c, DecodeConfig(group=128, max_ctx=n + 8, page=16, seed=7, step_kernel="persistent"))
+    ocfg = types.SimpleNamespace(group=128, quant="rtn", qparams=None, max_ctx=n + 8, page=16, shuffle_pages=True)
+    o = MO.OracleModel(sd, c, ocfg, packed=packed_of(m), block_table=m.bt.cpu())
+    torch.manual_seed(4)
+    stream = torch.randint(0, c.vocab_size, (n,)).tolist()
+    ref = o.teacher_force(stream, collect_logits=True)
+    m.prepare(n + 8, use_graph=True)
+    assert m.persistent
+    m.reset(0)
+    got = m.teacher_force(stream, collect_logits=True).cpu()
+    assert m.step_error() == 0
+    check_logits_and_tokens(got[1050:], ref[1050:])        # 102 steps below the threshold, 248 above
+    check_logits_and_tokens(got[:64], ref[:64])
+    scale = o.kv.float().abs().max().item()      # same layout, same block table
+    assert (m.kv.cpu().float() - o.kv.float()).abs().max().item() <= KERNEL_TOL * scale
+
+
 # ---- the benchmark's own shape -------------------------------------------------------------------------------------
 TINY = dict(H=2048, n_q=32, n_kv=4, I=5632, V=32000)   # TinyLlama-1.1B: head_dim 64, group 128, pages of 16 tokens
 
