@@ -349,7 +349,10 @@ DEVI void stage_plain(const Cta& c, const uint32_t* E, int K, int warp, int lane
 // left its normalised output o_j (Eatt + j n_att) and its log-sum-exp l_j as two fp16 words, value and remainder
 // (Else + h * step_lse_words(J) + 2 j); x = sum_j e^(l_j - max l) o_j / sum_j e^(l_j - max l). A slice that saw no
 // token has l_j = -inf and o_j = 0. Lane l of the warp that owns unit u holds 4 values of one head.
-DEVI void stage_attn(const Cta& c, const uint32_t* Eatt, const uint32_t* Else, int J, int n_att, int D, int warp,
+// A function of its own, called (with the CTA's state by value, in registers) only in steps with a sliced context:
+// inlined, its code would lengthen the one loop body that serves every phase of the step, and the GEMV phases, which
+// run out of the instruction cache, slow down by a fifth when that body outgrows it.
+__device__ __noinline__ void stage_attn(const Cta c, const uint32_t* Eatt, const uint32_t* Else, int J, int n_att, int D, int warp,
                      int lane) {
   constexpr int NL = (kStepMaxAttSlices + 1) / 2;   // granules of log-sum-exp words per head
   const int nunit = n_att >> 7, lsew = step_lse_words(J), ng = lsew >> 2;
