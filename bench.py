@@ -181,7 +181,7 @@ def peak_hbm_gbs():
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch (175,900,160 + 4,468,992) over the algorithmic bytes of
 # that launch (6 layers + LM head + embedding row + KV at context 40: 175,499,264). Traffic grows with the layers in
 # proportion to the bytes, so the 22-layer figure is this ratio times the step's bytes.
-STEP_TRAFFIC_OVER_ALGORITHMIC = 180369152 / 175499264
+STEP_TRAFFIC_OVER_ALGORITHMIC = 180634368 / 175499264
 
 
 def parity_gate(dev, step_kernel, n_tokens=40):
