@@ -381,12 +381,13 @@ struct NormArgs {
 // kernel of its own. The block that has computed a tile group's rows
 //   1. rounds them to fp16 and pushes them, 16 bytes at a time, into slot data[rank] of EVERY rank's exchange block
 //      (its own included): plain peer stores over NVLink,
-//   2. tells every peer "my rows of group g, call number c, are with you" (release store into the peer's flag word
-//      flags[g][rank]) and waits until every peer has said the same (acquire loads of the local flag words, bounded),
+//   2. after its last round tells every peer "the rows of block b, call number c, are with you" (release store into
+//      the peer's flag word flags[b][rank]) and waits until every peer has said the same (acquire loads of the local
+//      flag words, bounded): one NVLink round trip per block and GEMV, however many rounds the block has,
 //   3. adds the W copies - all in LOCAL memory by now - in rank order with fp32 accumulation, rounds once, and stores
-//      the sum to y. Every rank adds the same numbers in the same order: the sums are bit-identical on all ranks.
-// The block of the same index on each peer does the same for the same rows, so nobody waits for anything that depends
-// on this GPU's scheduling; the wait is one NVLink round trip, overlapped over all blocks of the grid. Slot reuse:
+//      the sums to y. Every rank adds the same numbers in the same order: the sums are bit-identical on all ranks.
+// The block of the same index on each peer does the same for the same rows (the ranks launch the same grid), so
+// nobody waits for anything that depends on this GPU's scheduling. Slot reuse:
 // a rank reaches call c + 1 on a slot only after another exchange has completed in between (the o_proj and down_proj
 // slots alternate, and the logits gather follows the last layer), which every peer can only have joined after it was
 // done reading this slot. N % 8 == 0. A wait that runs out sets the block's error word and leaves y's rows alone.
@@ -612,43 +613,55 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
       if (!ALLRED) __syncthreads();
     }
     if (ALLRED) {
-      // this round's tile group: tiles [gidx * tpr, (gidx + 1) * tpr), rows from row0 on, `nchunk` pieces of 8 rows
-      __shared__ uint32_t call_s;
-      __shared__ int failed_s;
+      // this round's tile group: tiles [gidx * tpr, (gidx + 1) * tpr), rows from row0 on, `nchunk` pieces of 8 rows:
+      // pushed to every rank now; flags, wait and sum follow once for all rounds of the block
       const int gidx = r * gridDim.x + blockIdx.x, row0 = 16 * gidx * tiles_per_round;
       const int nrows = max(0, min(N - row0, 16 * tiles_per_round)), nchunk = nrows >> 3;
-      uint8_t* mine = ar.P.p[ar.rank] + ar.off;
-      if (tid == 0) {
-        call_s = *reinterpret_cast<volatile uint32_t*>(mine) + 1u;   // read after the wait on the previous kernel
-        failed_s = 0;
-      }
-      __syncthreads();   // rowbuf complete, call number known
-      const uint32_t call = call_s;
+      __syncthreads();   // rowbuf complete
       const size_t data_off = ar.off + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + ((size_t)ar.rank * N + row0) * 2;
       for (int i = tid; i < nchunk * ar.W; i += kMmaGemvThreads) {
         const int p = i / nchunk, c = i - p * nchunk;
         st_peer16(ar.P.p[p] + data_off + 16 * (size_t)c, reinterpret_cast<const uint4*>(rowbuf)[c]);
       }
-      __syncthreads();   // every push of this block is issued before any of its flags
-      if (tid < ar.W && tid != ar.rank && nchunk > 0) {
-        __threadfence_system();
-        const size_t flag_off = ar.off + kGemvSlotCtrlBytes + ((size_t)gidx * kCommMaxRanks) * 4;
-        st_release_sys(reinterpret_cast<uint32_t*>(ar.P.p[tid] + flag_off) + ar.rank, call);
-        const uint32_t* here = reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + flag_off) + tid;
-        const uint32_t set_limit = *reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + kCommLimitOff);
-        const int limit = set_limit ? (int)set_limit : kCommSpinLimit;
-        int spins = 0;
-        while ((int32_t)(ld_acquire_sys(here) - call) < 0) {
-          if (++spins > limit) {
-            failed_s = 1;
-            atomicExch(reinterpret_cast<uint32_t*>(ar.P.p[ar.rank] + kCommErrorOff), COMM_ERR_PEER_WAIT);
-            break;
-          }
-          if (spins > 256) __nanosleep(200);
+      __syncthreads();   // rowbuf and part are free for the next round
+    }
+  }
+  if (ALLRED) {
+    // One flag round per block, after all its pushes: block b of every rank handles the same tile groups (same grid,
+    // same rounds on all ranks), so "my rows of block b, call c, are with you" covers them all, and the wait - one
+    // NVLink round trip - is paid once per GEMV instead of once per round.
+    __shared__ uint32_t call_s;
+    __shared__ int failed_s;
+    uint8_t* mine = ar.P.p[ar.rank] + ar.off;
+    if (tid == 0) {
+      call_s = *reinterpret_cast<volatile uint32_t*>(mine) + 1u;   // the call counter moves when the whole grid is done
+      failed_s = 0;
+    }
+    __syncthreads();   // every push of this block is issued before any of its flags
+    const uint32_t call = call_s;
+    if (tid < ar.W && tid != ar.rank) {
+      const size_t flag_off = ar.off + kGemvSlotCtrlBytes + ((size_t)blockIdx.x * kCommMaxRanks) * 4;
+      // release at system scope: orders the block's pushes (made visible to this thread by the barrier) before the flag
+      st_release_sys(reinterpret_cast<uint32_t*>(ar.P.p[tid] + flag_off) + ar.rank, call);
+      const uint32_t* here = reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + flag_off) + tid;
+      const uint32_t set_limit = *reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + kCommLimitOff);
+      const int limit = set_limit ? (int)set_limit : kCommSpinLimit;
+      int spins = 0;
+      while ((int32_t)(ld_acquire_sys(here) - call) < 0) {
+        if (++spins > limit) {
+          failed_s = 1;
+          atomicExch(reinterpret_cast<uint32_t*>(ar.P.p[ar.rank] + kCommErrorOff), COMM_ERR_PEER_WAIT);
+          break;
         }
+        if (spins > 256) __nanosleep(200);
       }
-      __syncthreads();
-      if (!failed_s) {
+    }
+    __syncthreads();
+    if (!failed_s) {
+      // add the W copies - all in LOCAL memory by now - in rank order, fp32, one rounding
+      for (int r = 0; r < rounds; ++r) {
+        const int gidx = r * gridDim.x + blockIdx.x, row0 = 16 * gidx * tiles_per_round;
+        const int nrows = max(0, min(N - row0, 16 * tiles_per_round)), nchunk = nrows >> 3;
         const uint8_t* base = mine + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + (size_t)row0 * 2;
         for (int c = tid; c < nchunk; c += kMmaGemvThreads) {
           float acc[8];
@@ -668,12 +681,9 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
           reinterpret_cast<uint4*>(y + row0)[c] = o;
         }
       }
-      __syncthreads();   // rowbuf, part and the shared words are free for the next round
     }
-  }
-  if (ALLRED) {
     // the last block to finish closes the call: the slot's call counter moves on, the ticket goes back to zero
-    uint32_t* ctrl = reinterpret_cast<uint32_t*>(ar.P.p[ar.rank] + ar.off);
+    uint32_t* ctrl = reinterpret_cast<uint32_t*>(mine);
     __syncthreads();
     if (tid == 0) {
       __threadfence();
@@ -753,7 +763,7 @@ static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const vo
   }
   const NormArgs na = norm ? *norm : NormArgs{nullptr, nullptr, nullptr, 0.f};
   const AllReduceArgs ar = allred ? *allred : AllReduceArgs{};
-  if (allred && (mode != 1 || norm || rounds * blocks > kCommMaxGroups || N % 8)) return cudaErrorInvalidValue;
+  if (allred && (mode != 1 || norm || blocks > kCommMaxGroups || N % 8)) return cudaErrorInvalidValue;
   auto kern = mode == 0 ? gemv_w4a16_mma_kernel<false, false, false, false>
               : allred  ? gemv_w4a16_mma_kernel<true, false, false, true>
               : norm    ? (mode == 2 ? gemv_w4a16_mma_kernel<true, true, true, false>

@@ -44,8 +44,8 @@ DEVI uint4 ld_peer16(const void* p) {
 // A "GEMV slot" of the exchange block, at a caller-chosen offset (multiple of 256 bytes):
 //   [0, 256)                       control: uint32 calls (exchanges completed on this slot), uint32 done (blocks of
 //                                  the running call that have finished)
-//   [256, 256 + 64 KB)             uint32 flags[kCommMaxGroups][16]: flags[g][r] = latest call for which rank r's
-//                                  rows of tile group g have arrived here
+//   [256, 256 + 64 KB)             uint32 flags[kCommMaxGroups][16]: flags[b][r] = latest call for which the rows of
+//                                  rank r's block b (all its tile groups) have arrived here
 //   [256 + 64 KB, ... + 16 N 2)    fp16 data[r][N] for r < W: rank r's partial rows, pushed here by rank r
 constexpr int kCommMaxGroups = 1024;
 constexpr size_t kGemvSlotCtrlBytes = 256;
