@@ -119,7 +119,7 @@ def run_ctx(a):
 
 
 def tp_record(rank, world, local, dist, layers=80, ctx=4096, tokens=128, tp_comm="p2p", gemv="tiled",
-              fuse_norm_gemv=True):
+              allreduce="kernel"):
     """Build this rank's shard of the 70B-shape model, decode `tokens` tokens from a pre-filled context `ctx` and
     return the record (a dict; identical on every rank up to the rank-local fields). `dist` is the initialised
     torch.distributed module, or None for one GPU."""
@@ -129,7 +129,7 @@ def tp_record(rank, world, local, dist, layers=80, ctx=4096, tokens=128, tp_comm
     cfg = DecodeConfig(group=128, max_ctx=ctx + tokens + 16, page=16, device=dev, seed=0, tp_rank=rank,
                        tp_world=world, tp_comm=tp_comm, step_kernel="multi", tile_weights=gemv == "tiled",
                        keep_packed=False, gemv_stage=(2, 16, 0, 0) if gemv == "segmented" else None,
-                       fuse_norm_gemv=fuse_norm_gemv)
+                       tp_allreduce=allreduce)
     m = Model(LazyRandomState(c, dev, 0), c, cfg)
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
@@ -172,7 +172,7 @@ def run_tp(a):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"),
                                 timeout=datetime.timedelta(seconds=600))
-    line = tp_record(rank, world, local, dist, a.layers, a.ctx, a.tokens, a.tp_comm, a.gemv, not a.exchange_kernel)
+    line = tp_record(rank, world, local, dist, a.layers, a.ctx, a.tokens, a.tp_comm, a.gemv, a.allreduce)
     if rank == 0:
         print(json.dumps(line), flush=True)
         if a.out:
@@ -238,9 +238,9 @@ def main():
     ap.add_argument("--gemv", default="tiled", choices=["tiled", "rowmajor", "segmented"],
                     help="tp: tensor-core GEMV from the tile layout (default) / from the row-major tensors / the "
                          "segmented CUDA-core GEMV")
-    ap.add_argument("--exchange-kernel", action="store_true",
-                    help="tp: sum the row-split projections in a kernel of their own (fused with add+RMSNorm) instead of "
-                         "inside the GEMV (DecodeConfig.fuse_norm_gemv=False)")
+    ap.add_argument("--allreduce", default="kernel", choices=["kernel", "gemv"],
+                    help="tp: sum the row-split projections in a kernel of their own fused with add+RMSNorm (default), "
+                         "or inside the GEMV (DecodeConfig.tp_allreduce)")
     ap.add_argument("--fuse-rope", action="store_true", help="ctx: RoPE + KV-append inside the attention kernel")
     ap.add_argument("--step-kernel", default="auto", choices=["auto", "persistent", "multi"],
                     help="ctx: force the step kernel of the sweep (default: the model's own choice per context)")

@@ -67,6 +67,12 @@ class DecodeConfig:
                                  # NVLink peer memory, fused with the residual add + RMSNorm that follows (all GPUs in
                                  # one node; the step is captured in a CUDA graph); "nccl" = torch.distributed
                                  # all_reduce / all_gather, launched eagerly
+    tp_allreduce: str = "kernel" # tp_comm="p2p": where the all-reduce of o_proj / down_proj happens. "kernel": one
+                                 # exchange kernel fused with the residual add + RMSNorm that follows
+                                 # (b200_tp_allreduce_add_rmsnorm); "gemv": inside the row-split GEMV itself
+                                 # (b200_gemv_w4a16_tiled_allreduce), the norm inside the next GEMV - two launches
+                                 # less per layer. Measured on 2 and 4 GPUs "kernel" is 4-5 % faster (the GEMV's
+                                 # blocks all end in the same NVLink round trip), so it is the default
     ablate: tuple = ()           # fusions switched off for ablation runs, any of "dequant" (dequantize the matrix to
                                  # an fp16 buffer, then an fp16 matrix-vector product), "norm", "swiglu" (the two
                                  # that fused=False switches off together) and "rope" (rotation and cache append as
@@ -243,12 +249,14 @@ class Model:
         if self.tp > 1:
             if cfg.tp_comm not in ("p2p", "nccl"):
                 raise ValueError(f"tp_comm must be 'p2p' or 'nccl', got {cfg.tp_comm!r}")
+            if cfg.tp_allreduce not in ("kernel", "gemv"):
+                raise ValueError(f"tp_allreduce must be 'kernel' or 'gemv', got {cfg.tp_allreduce!r}")
             if cfg.tp_comm == "p2p":
                 if self.off & {"norm"}:
                     raise ValueError("tp_comm='p2p' fuses the all-reduce with residual add + RMSNorm; it cannot run "
                                      "with that fusion switched off (use tp_comm='nccl')")
                 # exchange block: two regions for the all-reduce inside the o_proj / down_proj GEMVs (they alternate),
-                # the logit shard, and - for fuse_norm_gemv=False, where the exchange is a kernel of its own fused with
+                # the logit shard, and - for tp_allreduce="kernel", where the exchange is a kernel of its own fused with
                 # add + RMSNorm - two plain slots the row-split projections write their partials into
                 gslot = self.K.tp_gemv_slot_bytes(self.H, self.tp)
                 self.comm = TP.PeerComm(self.K, self.tp_rank, self.tp, [gslot, gslot, 2 * self.V, 2 * self.H, 2 * self.H],
@@ -256,7 +264,7 @@ class Model:
                 self.logits_local = self.comm.slot(2)
         every = [lw[n] for lw in self.layers for n in ("qkv", "o", "gu", "down")] + [self.lm_head]
         self.norm_in_gemv = (cfg.fuse_norm_gemv and not self.off and all(lin.tiled is not None for lin in every)
-                             and (self.tp == 1 or self.comm is not None))
+                             and (self.tp == 1 or (self.comm is not None and cfg.tp_allreduce == "gemv")))
         if self.comm is not None and not self.norm_in_gemv:
             self.o, self.down = self.comm.slot(3), self.comm.slot(4)
         self.set_attention_partition(cfg.max_ctx)

@@ -28,7 +28,7 @@ def _rank_main(rank, world, port, out, modes, tp_comm, fuse):
         c = _cfg()
         sd = {k: (v * 3 if v.dim() == 2 else v) for k, v in random_llama_state(c, "cpu", 3).items()}
         m = Model(sd, c, DecodeConfig(max_ctx=96, seed=4, device=f"cuda:{rank}", tp_rank=rank, tp_world=world,
-                                      tp_comm=tp_comm, fuse_norm_gemv=fuse))
+                                      tp_comm=tp_comm, tp_allreduce="gemv" if fuse else "kernel"))
         assert m.norm_in_gemv == (fuse and tp_comm == "p2p")
         assert not m.persistent and m.n_q == 8 // world and m.V == 3000 // world
         assert (m.comm is not None) == (tp_comm == "p2p")
