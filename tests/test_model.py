@@ -168,6 +168,38 @@ def test_persistent_step_sliced_attention_long_context():
     assert (m.kv.cpu().float() - o.kv.float()).abs().max().item() <= KERNEL_TOL * scale
 
 
+def test_persistent_step_matches_multi_kernel_step_at_long_context():
+    """5,000 cached tokens (40 ring stages a head, cut into slices over the CTAs): the persistent step against the
+    one-launch-per-operator step, whose attention kernel is checked against the oracle up to 16k tokens on its own.
+    Both start from the same prompt, processed by prefill()."""
+    c = hf_cfg(512, 2, 8, 2, 1024, 1500)
+    sd = random_state(c, 31)
+    n, new = 5000, 6
+    torch.manual_seed(6)
+    prompt = torch.randint(0, c.vocab_size, (n,))
+    out = {}
+    for kind in ("persistent", "multi"):
+        m = Model(sd, c, DecodeConfig(group=128, max_ctx=n + 64, page=16, seed=9, step_kernel=kind))
+        m.prepare(n + 64, use_graph=True)
+        assert m.persistent == (kind == "persistent")
+        m.reset(0)
+        m.prefill(prompt)
+        first = int(m.tok)
+        logits = []
+        for _ in range(new):
+            m.run_step()
+            logits.append(m.logits.clone())
+        assert m.step_error() == 0 and m.K.gemm_status() == 0
+        out[kind] = (first, torch.stack(logits).float().cpu(), m.history[n:n + new].cpu())
+        del m
+    assert out["persistent"][0] == out["multi"][0]            # same prefill, same first token
+    a, b = out["persistent"][1], out["multi"][1]
+    scale = b.abs().max().item()
+    assert (a[0] - b[0]).abs().max().item() <= KERNEL_TOL * scale   # first step: identical inputs
+    if torch.equal(out["persistent"][2], out["multi"][2]):          # same tokens fed back: all steps comparable
+        assert (a - b).abs().max().item() <= LOGIT_TOL * scale
+
+
 # ---- the benchmark's own shape -------------------------------------------------------------------------------------
 TINY = dict(H=2048, n_q=32, n_kv=4, I=5632, V=32000)   # TinyLlama-1.1B: head_dim 64, group 128, pages of 16 tokens
 
