@@ -294,6 +294,10 @@ int b200_embed_row(const void* emb, const long long* tok, void* x, int H, int V,
 
 static inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
+#ifndef B200_STEP_UPS
+#define B200_STEP_UPS 32   // tile-unit blocks per ring stage of the persistent step (build-time knob for measurements)
+#endif
+
 size_t b200_decode_step_xchg_bytes(int L, int H, int I, int n_q, int n_kv, int D, int grid) {
   if (grid <= 0 || n_q <= 0) return 0;
   const size_t per_layer = b200::step_words_per_layer(H, I, n_q, n_kv, D, b200::step_att_slices(grid, n_q));
@@ -351,7 +355,7 @@ int b200_decode_step(const b200_step_desc* d, void* stream) {
     part_bytes = align_up((a > b ? a : b) * 4, 128);
   }
   const int table_bytes = align_up(d->L * (int)sizeof(b200::StepLayer), 128);
-  p.ups = 32;
+  p.ups = B200_STEP_UPS;
   p.stage_w = p.ups * b200::kTileUnitBytes;
   p.stage_bytes = align_up(p.stage_w, 128);
   // attention copies whole KV pages into a stage, K rows in one half and V rows in the other
