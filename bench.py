@@ -184,6 +184,34 @@ def peak_hbm_gbs():
 STEP_TRAFFIC_OVER_ALGORITHMIC = 180634368 / 175499264
 
 
+def prompt_record(m, n):
+    """A prompt of n tokens through Model.prefill (W4A16 GEMM on the tcgen05 tensor cores, every matrix read once per
+    256 tokens) against stepping through it one graph replay per token, which is what the reference does: device time
+    around the whole prompt, median of 3, and whether both leave the same next token."""
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, m.V_full, (n,), generator=g).to(m.tok.device)
+    m.prepare(n + 8)
+
+    def timed(fn):
+        ts = []
+        for _ in range(3):
+            m.reset(0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[1], int(m.tok)
+    m.reset(0)
+    m.prefill(prompt)            # warm-up: scratch buffers, launch attributes
+    ms_p, tok_p = timed(lambda: m.prefill(prompt))
+    ms_s, tok_s = timed(lambda: m.teacher_force(prompt))
+    return {"tokens": n, "prefill_ms": round(ms_p, 3), "prefill_tok_s": round(n / ms_p * 1e3, 1),
+            "stepping_ms": round(ms_s, 3), "stepping_tok_s": round(n / ms_s * 1e3, 1),
+            "same_next_token": tok_p == tok_s, "gemm_status": m.K.gemm_status()}
+
+
 def parity_gate(dev, step_kernel, n_tokens=40):
     """The accuracy gate in front of the speed numbers: a 2-layer model of the benchmark's widths (hidden 2048,
     intermediate 5632, 32/4 heads x 64, vocabulary 32000) through the step kernel that is about to be timed, against
@@ -371,6 +399,7 @@ def run_b200_arm(args, rank, world, local_rank):
     if rank == 0 and not args.no_kernels:
         from llm_decode_kernels_b200.kernel_bench import headline_kernels
         kernels = headline_kernels(K, peak)
+        kernels["prompt_256"] = prompt_record(m, 256)
     persistent = m.persistent
     del m, gg, bufs, lins
     torch.cuda.empty_cache()
