@@ -138,7 +138,35 @@ def cpu_reference_leg(budget_s, threads, layers_sample=None, log=lambda *a: None
         how = (f"{n} decode steps at ctx 2..{n + 1} on {built} of {L} layers + LM head, per-layer time scaled "
                f"x{L / built:.0f}")
     return {"value": 1.0 / per_token, "unit": "tok/s", "cores": threads, "kind": "port", "sample": how,
-            "s_per_token": per_token}
+            "s_per_token": per_token, "ops_us": cpu_op_times()}
+
+
+def cpu_op_times():
+    """The single-operator configurations on the host's cores, with the oracle's functions (the reference's ref_ops
+    restated): the 5632 x 2048 GEMV from its dequantized fp16 matrix, and paged attention for one sequence (32 query /
+    4 kv heads x 64, pages of 16) at contexts 2048 and 8192. Microseconds, best of 3 after a warm-up call."""
+    from oracle import ops_oracle as R
+    g = torch.Generator().manual_seed(2)
+
+    def best(fn):
+        fn()
+        ts = []
+        for _ in range(3):
+            t0 = time.time()
+            fn()
+            ts.append(time.time() - t0)
+        return round(min(ts) * 1e6, 1)
+    w = (torch.randn(5632, 2048, generator=g) * 0.02).half()
+    x = torch.randn(2048, generator=g).half()
+    out = {"gemv_config1_5632x2048": best(lambda: R.gemv_ref(w, x))}
+    q = torch.randn(32, 64, generator=g).half()
+    for ctx in (2048, 8192):
+        pages = ctx // 16 + 2
+        kc = torch.randn(pages, 4, 16, 64, generator=g).half()
+        vc = torch.randn(pages, 4, 16, 64, generator=g).half()
+        bt = torch.randperm(pages, generator=g).int()
+        out[f"attention_b1_ctx{ctx}"] = best(lambda: R.paged_attention_ref(q, kc, vc, bt, ctx, 16))
+    return out
 
 
 def run_reference_arm(args, rank):
@@ -153,7 +181,7 @@ def run_reference_arm(args, rank):
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
             "config": workload_config(),
             "cpu_baseline": {"value": round(r["value"], 4), "unit": "tok/s", "cores": threads, "kind": "port",
-                             "sample": r["sample"]},
+                             "sample": r["sample"], "ops_us": r["ops_us"]},
             "e2e": {"value": round(r["value"], 4), "unit": "tok/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -178,7 +206,7 @@ def peak_hbm_gbs():
 
 
 # Measured with ncu on the same kernel, TinyLlama shape cut to 6 layers (profiles/decode_step_kernel_tinyllama_6layers.md):
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch (175,900,160 + 4,468,992) over the algorithmic bytes of
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch (175,887,616 + 4,746,752) over the algorithmic bytes of
 # that launch (6 layers + LM head + embedding row + KV at context 40: 175,499,264). Traffic grows with the layers in
 # proportion to the bytes, so the 22-layer figure is this ratio times the step's bytes.
 STEP_TRAFFIC_OVER_ALGORITHMIC = 180634368 / 175499264
