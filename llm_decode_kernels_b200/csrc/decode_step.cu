@@ -350,8 +350,9 @@ DEVI void stage_plain(const Cta& c, const uint32_t* E, int K, int warp, int lane
 // (Else + h * step_lse_words(J) + 2 j); x = sum_j e^(l_j - max l) o_j / sum_j e^(l_j - max l). A slice that saw no
 // token has l_j = -inf and o_j = 0. Lane l of the warp that owns unit u holds 4 values of one head.
 // A function of its own, called (with the CTA's state by value, in registers) only in steps with a sliced context:
-// inlined, its code would lengthen the one loop body that serves every phase of the step, and the GEMV phases, which
-// run out of the instruction cache, slow down by a fifth when that body outgrows it.
+// inlined into the one loop body that serves every phase of the step it made the GEMV phases of EVERY step a fifth
+// slower (measured; what the compiler does with that loop depends on everything in it - moving put_unit out of line,
+// which shrinks the body by 12 KB, costs 6 %, and so does doing two tiles at once in gemv()).
 __device__ __noinline__ void stage_attn(const Cta c, const uint32_t* Eatt, const uint32_t* Else, int J, int n_att, int D, int warp,
                      int lane) {
   constexpr int NL = (kStepMaxAttSlices + 1) / 2;   // granules of log-sum-exp words per head
@@ -580,8 +581,9 @@ DEVI void tile_unit(const Cta& c, const uint8_t* tu, int u, int lane, float& ya,
 // (tile 0 unit 0, tile 0 unit 1, ..., tile 1 unit 0, ...), `ups` of them per ring stage; warp w takes the blocks of
 // units w, w + kNCW, ... of every tile, two at a time where the ring stage holds both (two independent instruction
 // streams for the scheduler to interleave). The activations are re-read from shared memory for every block: keeping
-// them in registers across tiles was measured and loses - it pushes the kernel over its 168 registers, and a
-// spilled register costs an L2 round trip here. When the warp has passed its last unit of a tile, lanes t == 0 leave the
+// them in registers across tiles was measured and loses - it pushes the kernel over its registers, and a spilled
+// register costs an L2 round trip here. Doing two tiles of a stage together (four independent blocks) was measured
+// too and loses 3 %. When the warp has passed its last unit of a tile, lanes t == 0 leave the
 // two partial sums of rows g and g + 8 in part[warp][16 * tile + row slot]. A warp whose units do not exist
 // (K < 1024) only keeps the ring's barriers moving.
 DEVI void gemv(const Cta& c, const Mat& m, const Slice& s, float* part, int pstride, RingPos& rp, int warp, int lane,
