@@ -298,6 +298,20 @@ size_t b200_tp_gemv_slot_bytes(int N, int W);
 int b200_gemv_w4a16_tiled_allreduce(const void* Wt, const void* x, void* y, int N, int K, const void* const* peers,
                                     int rank, int W, size_t slot_off, void* stream);
 
+/* The same exchange with the sum on the consumer's side and no flag round. b200_gemv_w4a16_tiled_push computes this
+ * rank's partial rows and pushes them, as 32-bit words (tag << 16 | fp16 row) carrying the slot's call number, into
+ * every rank's region; it writes no y and waits for nobody. b200_tp_pushed_add_rmsnorm, launched after it on every
+ * rank, polls the W x H words that are (or are about to be) in its OWN region until they carry the call's tag
+ * (bounded; on a timeout b200_comm_error = 1 and the outputs are untouched), adds the W copies in rank order (fp32,
+ * one rounding: the same bits on every rank), then x <- x + sum, out <- RMSNorm(x) * w as b200_add_rmsnorm, and moves
+ * the region's call counter on. A word that carries the tag is its own arrival flag, so the exchange costs one
+ * NVLink flight and no system-scope fence. The region is that of b200_tp_gemv_slot_bytes(H, W); the same rules for
+ * alternating regions apply. N of the push == H of the consumer. */
+int b200_gemv_w4a16_tiled_push(const void* Wt, const void* x, int N, int K, const void* const* peers, int rank, int W,
+                               size_t slot_off, void* stream);
+int b200_tp_pushed_add_rmsnorm(const void* const* peers, int rank, int W, size_t slot_off, void* x, const void* w,
+                               void* out, int H, float eps, void* stream);
+
 /* Replaces the all-gather of the vocabulary-split LM head: dst[r * n + i] = rank r's fp16 shard[i] found at slot_off
  * of its block. Same flag round. dst 16-byte aligned when n % 8 == 0. */
 int b200_tp_allgather(const void* const* peers, int rank, int W, size_t slot_off, void* dst, int n, void* stream);

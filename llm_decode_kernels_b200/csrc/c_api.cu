@@ -20,7 +20,9 @@ cudaError_t gemv_w4a16_tiled_norm_dispatch(const void* Wt, const void* x_in, con
                                            float eps, void* x_out, void* y, int N, int K, int swiglu, cudaStream_t st);
 cudaError_t gemv_w4a16_tiled_allreduce_dispatch(const void* Wt, const void* x, void* y, int N, int K,
                                                 const void* const* peers, int rank, int W, size_t slot_off,
-                                                cudaStream_t st);
+                                                int tagged, cudaStream_t st);
+cudaError_t tp_pushed_add_rmsnorm_dispatch(const void* const* peers, int rank, int W, size_t off, void* x, const void* w,
+                                           void* out, int H, float eps, cudaStream_t st);
 size_t gemv_allreduce_slot_bytes(int N, int W);
 cudaError_t dequant_w4a16_dispatch(const void* Wp, const void* SZ, void* out, int N, int K, int log2G,
                                    cudaStream_t st);
@@ -460,18 +462,41 @@ size_t b200_tp_gemv_slot_bytes(int N, int W) {
   return b200::gemv_allreduce_slot_bytes(N, W);
 }
 
-int b200_gemv_w4a16_tiled_allreduce(const void* Wt, const void* x, void* y, int N, int K, const void* const* peers,
-                                    int rank, int W, size_t slot_off, void* stream) {
-  REQUIRE(Wt && x && y && N > 0 && K > 0, B200_ERR_ARG);
+static int gemv_push_or_allreduce(const void* Wt, const void* x, void* y, int N, int K, const void* const* peers,
+                                  int rank, int W, size_t slot_off, int tagged, void* stream) {
+  REQUIRE(Wt && x && (y || tagged) && N > 0 && K > 0, B200_ERR_ARG);
   REQUIRE(K % 128 == 0 && N % 8 == 0, B200_ERR_SHAPE);
   REQUIRE(K <= 65536, B200_ERR_LIMIT);
   REQUIRE(peers && W >= 1 && W <= b200::comm_max_ranks() && rank >= 0 && rank < W, B200_ERR_ARG);
   REQUIRE(slot_off >= (size_t)b200::comm_header_bytes() && slot_off % 256 == 0, B200_ERR_ALIGN);
   for (int r = 0; r < W; ++r) REQUIRE(peers[r] && aligned16(peers[r]), B200_ERR_ARG);
   REQUIRE(aligned16(Wt) && (reinterpret_cast<uintptr_t>(x) & 7u) == 0 && aligned16(y), B200_ERR_ALIGN);
-  const cudaError_t e = b200::gemv_w4a16_tiled_allreduce_dispatch(Wt, x, y, N, K, peers, rank, W, slot_off, S(stream));
-  if (e == cudaErrorInvalidValue) return B200_ERR_LIMIT;   // more tile groups than the slot has flag rows
+  const cudaError_t e =
+      b200::gemv_w4a16_tiled_allreduce_dispatch(Wt, x, y, N, K, peers, rank, W, slot_off, tagged, S(stream));
+  if (e == cudaErrorInvalidValue) return B200_ERR_LIMIT;   // more thread blocks than the slot has flag rows
   return finish(e);
+}
+
+int b200_gemv_w4a16_tiled_allreduce(const void* Wt, const void* x, void* y, int N, int K, const void* const* peers,
+                                    int rank, int W, size_t slot_off, void* stream) {
+  return gemv_push_or_allreduce(Wt, x, y, N, K, peers, rank, W, slot_off, 0, stream);
+}
+
+int b200_gemv_w4a16_tiled_push(const void* Wt, const void* x, int N, int K, const void* const* peers, int rank, int W,
+                               size_t slot_off, void* stream) {
+  return gemv_push_or_allreduce(Wt, x, nullptr, N, K, peers, rank, W, slot_off, 1, stream);
+}
+
+int b200_tp_pushed_add_rmsnorm(const void* const* peers, int rank, int W, size_t slot_off, void* x, const void* w,
+                               void* out, int H, float eps, void* stream) {
+  REQUIRE(peers && W >= 1 && W <= b200::comm_max_ranks() && rank >= 0 && rank < W, B200_ERR_ARG);
+  REQUIRE(slot_off >= (size_t)b200::comm_header_bytes() && slot_off % 256 == 0, B200_ERR_ALIGN);
+  REQUIRE(peers[rank] && aligned16(peers[rank]), B200_ERR_ARG);
+  REQUIRE(x && w && out && H > 0, B200_ERR_ARG);
+  REQUIRE(H % 8 == 0, B200_ERR_SHAPE);
+  REQUIRE(H <= 32768, B200_ERR_LIMIT);
+  REQUIRE(aligned16(x) && aligned16(w) && aligned16(out), B200_ERR_ALIGN);
+  return finish(b200::tp_pushed_add_rmsnorm_dispatch(peers, rank, W, slot_off, x, w, out, H, eps, S(stream)));
 }
 
 int b200_tp_allgather(const void* const* peers, int rank, int W, size_t slot_off, void* dst, int n, void* stream) {

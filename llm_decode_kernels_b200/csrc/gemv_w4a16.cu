@@ -531,6 +531,11 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
   const uint4* xbase = g == 0 ? xin + 4 * t : zeros;
   const int xstride = g == 0 ? 16 : 0;
 
+  // ALLRED, tagged form: the tag of this call (the slot's call counter was last written by the kernel that consumed
+  // the previous call's rows, which this stream has waited for)
+  uint32_t push_tag = 0u;
+  if (ALLRED && ar.tagged)
+    push_tag = comm_tag(*reinterpret_cast<const volatile uint32_t*>(ar.P.p[ar.rank] + ar.off) + 1u);
   for (int r = 0; r < rounds; ++r, tile += tile_step) {
     float ya = 0.f, yb = 0.f;
     if (tile < ntiles) {
@@ -618,14 +623,27 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
       const int gidx = r * gridDim.x + blockIdx.x, row0 = 16 * gidx * tiles_per_round;
       const int nrows = max(0, min(N - row0, 16 * tiles_per_round)), nchunk = nrows >> 3;
       __syncthreads();   // rowbuf complete
-      const size_t data_off = ar.off + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + ((size_t)ar.rank * N + row0) * 2;
-      for (int i = tid; i < nchunk * ar.W; i += kMmaGemvThreads) {
-        const int p = i / nchunk, c = i - p * nchunk;
-        st_peer16(ar.P.p[p] + data_off + 16 * (size_t)c, reinterpret_cast<const uint4*>(rowbuf)[c]);
+      if (ar.tagged) {
+        // tagged words: 8 rows = 32 bytes = two 16-byte stores per peer; a word with this call's tag is its own flag
+        const size_t data_off = ar.off + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + ((size_t)ar.rank * N + row0) * 4;
+        for (int i = tid; i < 2 * nchunk * ar.W; i += kMmaGemvThreads) {
+          const int p = i / (2 * nchunk), c = i - p * 2 * nchunk;   // c: 16-byte piece = 4 rows
+          const uint2 h4 = reinterpret_cast<const uint2*>(rowbuf)[c];
+          const uint4 wv = make_uint4(push_tag | (h4.x & 0xFFFFu), push_tag | (h4.x >> 16), push_tag | (h4.y & 0xFFFFu),
+                                      push_tag | (h4.y >> 16));
+          st_peer16(ar.P.p[p] + data_off + 16 * (size_t)c, wv);
+        }
+      } else {
+        const size_t data_off = ar.off + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + ((size_t)ar.rank * N + row0) * 2;
+        for (int i = tid; i < nchunk * ar.W; i += kMmaGemvThreads) {
+          const int p = i / nchunk, c = i - p * nchunk;
+          st_peer16(ar.P.p[p] + data_off + 16 * (size_t)c, reinterpret_cast<const uint4*>(rowbuf)[c]);
+        }
       }
       __syncthreads();   // rowbuf and part are free for the next round
     }
   }
+  if (ALLRED && ar.tagged) return;   // the sum happens where the rows are consumed (tp_pushed_add_rmsnorm_kernel)
   if (ALLRED) {
     // One flag round per block, after all its pushes: block b of every rank handles the same tile groups (same grid,
     // same rounds on all ranks), so "my rows of block b, call c, are with you" covers them all, and the wait - one
@@ -836,12 +854,13 @@ cudaError_t gemv_w4a16_tiled_dispatch(const void* Wt, const void* x, void* y, in
 // block as this process sees it, slot_off = offset of a GEMV slot (gemv_slot_bytes) inside every block.
 cudaError_t gemv_w4a16_tiled_allreduce_dispatch(const void* Wt, const void* x, void* y, int N, int K,
                                                 const void* const* peers, int rank, int W, size_t slot_off,
-                                                cudaStream_t st) {
+                                                int tagged, cudaStream_t st) {
   AllReduceArgs ar = {};
   for (int r = 0; r < W; ++r) ar.P.p[r] = (uint8_t*)peers[r];
   ar.rank = rank;
   ar.W = W;
   ar.off = slot_off;
+  ar.tagged = tagged;
   return launch_mma(1, Wt, nullptr, x, y, N, K, 7, st, nullptr, &ar);
 }
 size_t gemv_allreduce_slot_bytes(int N, int W) { return gemv_slot_bytes(N, W); }

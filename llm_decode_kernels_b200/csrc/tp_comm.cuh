@@ -47,15 +47,20 @@ DEVI uint4 ld_peer16(const void* p) {
 //   [256, 256 + 64 KB)             uint32 flags[kCommMaxGroups][16]: flags[b][r] = latest call for which the rows of
 //                                  rank r's block b (all its tile groups) have arrived here
 //   [256 + 64 KB, ... + 16 N 2)    fp16 data[r][N] for r < W: rank r's partial rows, pushed here by rank r
+// Tagged form of the same slot (GEMV that only pushes, sum in tp_pushed_add_rmsnorm_kernel): the data area holds
+// uint32 words[r][N] = (tag << 16 | fp16 row), tag = low 16 bits of the call number, never 0; no flags are used - a
+// word that carries the call's tag IS the arrival of its row, so the exchange costs one NVLink flight and no fence.
 constexpr int kCommMaxGroups = 1024;
 constexpr size_t kGemvSlotCtrlBytes = 256;
 constexpr size_t kGemvSlotFlagBytes = (size_t)kCommMaxGroups * kCommMaxRanks * 4;
-inline size_t gemv_slot_bytes(int N, int W) { return kGemvSlotCtrlBytes + kGemvSlotFlagBytes + (size_t)W * N * 2; }
+inline size_t gemv_slot_bytes(int N, int W) { return kGemvSlotCtrlBytes + kGemvSlotFlagBytes + (size_t)W * N * 4; }
+DEVI uint32_t comm_tag(uint32_t call) { return ((call % 65535u) + 1u) << 16; }
 
 struct AllReduceArgs {
   CommPeers P;
   int rank, W;     // W == 0: no exchange, the GEMV stores its rows to y
   size_t off;      // offset of the GEMV slot inside every rank's block
+  int tagged;      // 1: push tagged words and return (no flags, no wait, no sum, y untouched)
 };
 
 DEVI void st_peer16(void* p, uint4 v) {

@@ -119,7 +119,7 @@ def run_ctx(a):
 
 
 def tp_record(rank, world, local, dist, layers=80, ctx=4096, tokens=128, tp_comm="p2p", gemv="tiled",
-              allreduce="kernel"):
+              allreduce="auto"):
     """Build this rank's shard of the 70B-shape model, decode `tokens` tokens from a pre-filled context `ctx` and
     return the record (a dict; identical on every rank up to the rank-local fields). `dist` is the initialised
     torch.distributed module, or None for one GPU."""
@@ -148,8 +148,7 @@ def tp_record(rank, world, local, dist, layers=80, ctx=4096, tokens=128, tp_comm
            "config": {"workload": f"llama-3-70b-shape W4A16 g128 RTN, {layers} layers, batch 1, context {ctx}, "
                                   f"{tokens} greedy tokens", "tp": world, "comm": tp_comm if world > 1 else None,
                       "gemv": gemv, "graph": m.graph is not None,
-                      "allreduce": ("inside the row-split GEMV" if m.norm_in_gemv else "exchange kernel fused with "
-                                    "add+RMSNorm") if world > 1 and tp_comm == "p2p" else None},
+                      "allreduce": m.tp_allreduce if world > 1 and tp_comm == "p2p" else None},
            "bytes_per_token_per_gpu": nbytes, "floor_us_at_peak": round(nbytes / peak / 1e3, 1),
            "frac_of_hbm_per_gpu": round(nbytes / us / 1e3 / peak, 4), "peak_hbm_gbs": peak, "peak_source": kind,
            "exchanges_per_token": 2 * layers + 1 if world > 1 else 0, "build_s": round(build_s, 1),
@@ -238,9 +237,8 @@ def main():
     ap.add_argument("--gemv", default="tiled", choices=["tiled", "rowmajor", "segmented"],
                     help="tp: tensor-core GEMV from the tile layout (default) / from the row-major tensors / the "
                          "segmented CUDA-core GEMV")
-    ap.add_argument("--allreduce", default="kernel", choices=["kernel", "gemv"],
-                    help="tp: sum the row-split projections in a kernel of their own fused with add+RMSNorm (default), "
-                         "or inside the GEMV (DecodeConfig.tp_allreduce)")
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "kernel", "gemv", "push"],
+                    help="tp: how the row-split projections are summed over the ranks (DecodeConfig.tp_allreduce)")
     ap.add_argument("--fuse-rope", action="store_true", help="ctx: RoPE + KV-append inside the attention kernel")
     ap.add_argument("--step-kernel", default="auto", choices=["auto", "persistent", "multi"],
                     help="ctx: force the step kernel of the sweep (default: the model's own choice per context)")

@@ -63,6 +63,9 @@ SIGNATURES = {
     "b200_tp_allgather": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_int, c_void_p],
     "b200_gemv_w4a16_tiled_allreduce": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_size_t,
                                         c_void_p],
+    "b200_gemv_w4a16_tiled_push": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_size_t, c_void_p],
+    "b200_tp_pushed_add_rmsnorm": [c_void_p, c_int, c_int, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_float,
+                                   c_void_p],
     "b200_paged_attention_noalloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_void_p, c_void_p],
     "b200_rope_append_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
@@ -414,6 +417,23 @@ class Ops:
         self._check(self.lib.b200_gemv_w4a16_tiled_allreduce(tiled.data_ptr(), x.data_ptr(), y.data_ptr(), int(N),
                                                              int(K), peers, int(rank), len(peers), int(slot_off),
                                                              _stream()), "gemv_tiled_allreduce")
+
+    def gemv_tiled_push(self, tiled, x, N, K, peers, rank, slot_off):
+        """The row-split GEMV that pushes its partial rows, as tagged words, into every rank's exchange region and
+        returns (b200_gemv_w4a16_tiled_push); tp_pushed_add_rmsnorm on every rank consumes them."""
+        _cuda(tiled, "tiled", torch.uint8), _cuda(x, "x", torch.float16)
+        if x.numel() != K:
+            raise RuntimeError("gemv_tiled_push: x must hold K values")
+        self._check(self.lib.b200_gemv_w4a16_tiled_push(tiled.data_ptr(), x.data_ptr(), int(N), int(K), peers,
+                                                        int(rank), len(peers), int(slot_off), _stream()),
+                    "gemv_tiled_push")
+
+    def tp_pushed_add_rmsnorm(self, peers, rank, slot_off, x, w, out, eps):
+        """x <- x + (sum over the ranks of the rows pushed into this rank's region), out <- RMSNorm(x) * w."""
+        _cuda(x, "x", torch.float16), _cuda(w, "w", torch.float16), _cuda(out, "out", torch.float16)
+        self._check(self.lib.b200_tp_pushed_add_rmsnorm(peers, int(rank), len(peers), int(slot_off), x.data_ptr(),
+                                                        w.data_ptr(), out.data_ptr(), x.numel(), float(eps),
+                                                        _stream()), "tp_pushed_add_rmsnorm")
 
     def tp_allgather(self, peers, rank, slot_off, dst, n):
         _cuda(dst, "dst", torch.float16)

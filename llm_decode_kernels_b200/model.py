@@ -67,12 +67,15 @@ class DecodeConfig:
                                  # NVLink peer memory, fused with the residual add + RMSNorm that follows (all GPUs in
                                  # one node; the step is captured in a CUDA graph); "nccl" = torch.distributed
                                  # all_reduce / all_gather, launched eagerly
-    tp_allreduce: str = "kernel" # tp_comm="p2p": where the all-reduce of o_proj / down_proj happens. "kernel": one
-                                 # exchange kernel fused with the residual add + RMSNorm that follows
-                                 # (b200_tp_allreduce_add_rmsnorm); "gemv": inside the row-split GEMV itself
-                                 # (b200_gemv_w4a16_tiled_allreduce), the norm inside the next GEMV - two launches
-                                 # less per layer. Measured on 2 and 4 GPUs "kernel" is 4-5 % faster (the GEMV's
-                                 # blocks all end in the same NVLink round trip), so it is the default
+    tp_allreduce: str = "auto"   # tp_comm="p2p": how the partial rows of o_proj / down_proj are summed over the ranks.
+                                 # "kernel": the GEMV writes its rows locally; one exchange kernel does a flag round,
+                                 # loads the peers' rows, sums, residual add + RMSNorm (b200_tp_allreduce_add_rmsnorm).
+                                 # "gemv": inside the row-split GEMV itself (b200_gemv_w4a16_tiled_allreduce), the
+                                 # norm inside the next GEMV - two launches less per layer. "push": the GEMV pushes
+                                 # tagged words into every rank's region and returns; the consumer kernel polls its
+                                 # own memory, sums, add + RMSNorm (b200_gemv_w4a16_tiled_push +
+                                 # b200_tp_pushed_add_rmsnorm) - no flag round, no fence. "auto": what measured
+                                 # fastest for the number of ranks
     ablate: tuple = ()           # fusions switched off for ablation runs, any of "dequant" (dequantize the matrix to
                                  # an fp16 buffer, then an fp16 matrix-vector product), "norm", "swiglu" (the two
                                  # that fused=False switches off together) and "rope" (rotation and cache append as
@@ -246,11 +249,13 @@ class Model:
         if "rope" in self.off:
             self.kv_heads = torch.arange(self.n_kv, device=dev)
         self.comm = None
+        # measured on the 70B shape (tok/s at 2 / 4 / 8 ranks): kernel 120.6 / 132.8 / 140.1, gemv 114.5 / 127.8 / 151.3
+        self.tp_allreduce = cfg.tp_allreduce if cfg.tp_allreduce != "auto" else ("gemv" if self.tp >= 8 else "kernel")
         if self.tp > 1:
             if cfg.tp_comm not in ("p2p", "nccl"):
                 raise ValueError(f"tp_comm must be 'p2p' or 'nccl', got {cfg.tp_comm!r}")
-            if cfg.tp_allreduce not in ("kernel", "gemv"):
-                raise ValueError(f"tp_allreduce must be 'kernel' or 'gemv', got {cfg.tp_allreduce!r}")
+            if cfg.tp_allreduce not in ("auto", "kernel", "gemv", "push"):
+                raise ValueError(f"tp_allreduce must be 'auto', 'kernel', 'gemv' or 'push', got {cfg.tp_allreduce!r}")
             if cfg.tp_comm == "p2p":
                 if self.off & {"norm"}:
                     raise ValueError("tp_comm='p2p' fuses the all-reduce with residual add + RMSNorm; it cannot run "
@@ -264,8 +269,12 @@ class Model:
                 self.logits_local = self.comm.slot(2)
         every = [lw[n] for lw in self.layers for n in ("qkv", "o", "gu", "down")] + [self.lm_head]
         self.norm_in_gemv = (cfg.fuse_norm_gemv and not self.off and all(lin.tiled is not None for lin in every)
-                             and (self.tp == 1 or (self.comm is not None and cfg.tp_allreduce == "gemv")))
-        if self.comm is not None and not self.norm_in_gemv:
+                             and (self.tp == 1 or (self.comm is not None and self.tp_allreduce == "gemv")))
+        tiled_rows = all(lw[n].tiled is not None for lw in self.layers for n in ("o", "down"))
+        if self.comm is not None and self.tp_allreduce == "push" and not tiled_rows:
+            raise ValueError("tp_allreduce='push' needs the tile-layout copies of o_proj / down_proj (tile_weights)")
+        self.tp_push = self.comm is not None and self.tp_allreduce == "push"
+        if self.comm is not None and not self.norm_in_gemv and not self.tp_push:
             self.o, self.down = self.comm.slot(3), self.comm.slot(4)
         self.set_attention_partition(cfg.max_ctx)
 
@@ -416,6 +425,10 @@ class Model:
         row-split projection, held in exchange slot `slot`: the sum over the ranks happens here, inside the same
         kernel (tp_comm='p2p') or by an NCCL all-reduce in front of it."""
         if self.tp > 1 and delta is not None:
+            if self.tp_push:   # the rows were pushed, as tagged words, into GEMV region `slot` of every rank
+                self.K.tp_pushed_add_rmsnorm(self.comm.peers, self.tp_rank, self.comm.offsets[slot], self.x, w,
+                                             self.normed, self.eps)
+                return
             if self.comm is not None:
                 self.K.tp_allreduce_add_rmsnorm(self.comm.peers, self.tp_rank, self.comm.offsets[3 + slot], self.x, w,
                                                 self.normed, self.eps)
@@ -488,14 +501,14 @@ class Model:
             self.add_norm(delta, lw["ln1"], 1)
             self.linear(lw["qkv"], self.normed, self.qkv)
             self.attention(li)
-            self.linear(lw["o"], self.attn.view(-1), self.o)
+            self.row_split_partial(lw["o"], self.attn.view(-1), self.o, 0)
             self.add_norm(self.o, lw["ln2"], 0)
             if lw["gu"].paired:   # act = SwiGLU(Wgate x, Wup x) in one launch
                 self.K.gemv_w4a16_tiled(lw["gu"].tiled, self.normed, self.act, self.I, lw["gu"].K, swiglu=True)
             else:
                 self.linear(lw["gu"], self.normed, self.gu)
                 self.swiglu()
-            self.linear(lw["down"], self.act, self.down)
+            self.row_split_partial(lw["down"], self.act, self.down, 1)
             delta = self.down
         self.add_norm(delta, self.norm_f, 1)
         self.linear(self.lm_head, self.normed, self.logits_local)
@@ -532,6 +545,15 @@ class Model:
         if self.comm is not None:   # every rank gathers the whole vocabulary and takes the same argmax: no broadcast
             K.tp_allgather(self.comm.peers, self.tp_rank, self.comm.offsets[2], self.logits, self.V)
         K.argmax(self.logits, self.tok, self.pos, self.history)
+
+    def row_split_partial(self, lin, x, y, slot):
+        """o_proj / down_proj of the step whose norm is a kernel of its own: this rank's partial rows go to y (one
+        GPU: the result; tensor parallel: a slot of the exchange block) or, with tp_allreduce="push", as tagged words
+        into GEMV region `slot` of every rank's block."""
+        if self.tp_push:
+            self.K.gemv_tiled_push(lin.tiled, x, lin.N, lin.K, self.comm.peers, self.tp_rank, self.comm.offsets[slot])
+        else:
+            self.linear(lin, x, y)
 
     def row_split_linear(self, lin, x, y, slot):
         """o_proj / down_proj. Tensor parallel: this rank's column shard times its x, summed over the ranks inside the

@@ -532,6 +532,48 @@ def test_gemv_with_allreduce_inside(K):
                                (ctypes.c_void_p * 1)(0), 0, hdr)
 
 
+def test_gemv_push_and_its_consumer(K):
+    """b200_gemv_w4a16_tiled_push + b200_tp_pushed_add_rmsnorm on one GPU. W = 1: the pushed words, summed by the
+    consumer, give the bits of GEMV followed by add_rmsnorm, call after call (the tag moves on). W = 2 with a second
+    local block standing in for a peer that never pushes: the consumer's bounded poll runs out, the error word is
+    set, x and out are left alone."""
+    import ctypes
+    torch.manual_seed(9)
+    hdr = K.comm_header_bytes()
+    N, Kd = 2048, 1024
+    ql = PQ.QuantLinear((torch.randn(N, Kd) * 0.05).half(), 128, keep_ref=False)
+    tiled = K.gemv_tile_repack(ql.packed.to(dev), ql.sz.to(dev), 128)
+    w = (1 + 0.1 * torch.randn(N, device=dev)).half()
+    nbytes = hdr + 2 * ((K.tp_gemv_slot_bytes(N, 2) + 255) // 256 * 256)
+    mine, silent = K.comm_alloc(nbytes), K.comm_alloc(nbytes)
+    try:
+        one = (ctypes.c_void_p * 1)(mine)
+        for it in range(3):
+            xin = torch.randn(Kd, device=dev).half()
+            resid = torch.randn(N, device=dev).half()
+            y = torch.empty(N, dtype=torch.half, device=dev)
+            K.gemv_w4a16_tiled(tiled, xin, y, N, Kd)
+            x_ref, out_ref = resid.clone(), torch.empty(N, dtype=torch.half, device=dev)
+            K.add_rmsnorm(x_ref, y, w, out_ref, 1e-5)
+            x_got, out_got = resid.clone(), torch.empty(N, dtype=torch.half, device=dev)
+            K.gemv_tiled_push(tiled, xin, N, Kd, one, 0, hdr)
+            K.tp_pushed_add_rmsnorm(one, 0, hdr, x_got, w, out_got, 1e-5)
+            assert torch.equal(x_got, x_ref) and torch.equal(out_got, out_ref), it
+        assert K.comm_error(mine) == 0
+        two = (ctypes.c_void_p * 2)(mine, silent)
+        K.comm_set_wait_limit(mine, 2000)
+        x_got, out_got = torch.full((N,), 3.0, dtype=torch.half, device=dev), torch.full((N,), 7.0, dtype=torch.half, device=dev)
+        K.gemv_tiled_push(tiled, xin, N, Kd, two, 0, hdr)       # pushes into both blocks; nobody pushes as rank 1
+        K.tp_pushed_add_rmsnorm(two, 0, hdr, x_got, w, out_got, 1e-5)
+        torch.cuda.synchronize()                                 # returns: the poll is bounded
+        assert K.comm_error(mine) == 1 and bool((x_got == 3.0).all()) and bool((out_got == 7.0).all())
+        K.comm_reset(mine)
+        assert K.comm_error(mine) == 0
+    finally:
+        K.comm_free(mine)
+        K.comm_free(silent)
+
+
 def test_exchange_wait_that_runs_out_is_reported(K):
     """A peer that never signals: the exchange kernel gives up after its bound, reports it and leaves the outputs
     alone. Made on one GPU without any fault: the "peer" is a second local block that no kernel ever writes, and the

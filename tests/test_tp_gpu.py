@@ -28,8 +28,8 @@ def _rank_main(rank, world, port, out, modes, tp_comm, fuse):
         c = _cfg()
         sd = {k: (v * 3 if v.dim() == 2 else v) for k, v in random_llama_state(c, "cpu", 3).items()}
         m = Model(sd, c, DecodeConfig(max_ctx=96, seed=4, device=f"cuda:{rank}", tp_rank=rank, tp_world=world,
-                                      tp_comm=tp_comm, tp_allreduce="gemv" if fuse else "kernel"))
-        assert m.norm_in_gemv == (fuse and tp_comm == "p2p")
+                                      tp_comm=tp_comm, tp_allreduce=fuse if isinstance(fuse, str) else ("gemv" if fuse else "kernel")))
+        assert m.norm_in_gemv == (fuse is True and tp_comm == "p2p")
         assert not m.persistent and m.n_q == 8 // world and m.V == 3000 // world
         assert (m.comm is not None) == (tp_comm == "p2p")
         g = torch.Generator().manual_seed(1)
@@ -73,7 +73,8 @@ def _spawn(world, out, modes, tp_comm, fuse, limit_s=150):
 @pytest.mark.parametrize("tp_comm,modes,fuse", [
     ("nccl", (False,), True),          # NCCL collectives: launched eagerly
     ("p2p", (False, True), True),      # all-reduce inside the row-split GEMVs: eager, then one graph
-    ("p2p", (False, True), False)])    # exchange kernels of their own, fused with add + RMSNorm
+    ("p2p", (False, True), False),     # exchange kernels of their own, fused with add + RMSNorm
+    ("p2p", (False, True), "push")])   # GEMVs that push tagged words, consumed by the add + RMSNorm kernel
 def test_tp2_matches_single_gpu(tmp_path, tp_comm, modes, fuse):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
