@@ -249,8 +249,11 @@ class Model:
         if "rope" in self.off:
             self.kv_heads = torch.arange(self.n_kv, device=dev)
         self.comm = None
-        # measured on the 70B shape (tok/s at 2 / 4 / 8 ranks): kernel 120.6 / 132.8 / 140.1, gemv 114.5 / 127.8 / 151.3
-        self.tp_allreduce = cfg.tp_allreduce if cfg.tp_allreduce != "auto" else ("gemv" if self.tp >= 8 else "kernel")
+        # measured on the 70B shape (tok/s at 2 / 4 / 8 ranks): push 132.1 / 151.4 / 181.0, kernel 120.6 / 133.9 /
+        # 140.6, gemv 114.5 / 127.8 / 150.3. The push form needs the tile-layout copies (its GEMV is the tiled one).
+        self.tp_allreduce = cfg.tp_allreduce
+        if self.tp_allreduce == "auto":
+            self.tp_allreduce = "push" if (cfg.tile_weights and cfg.gemv_stage is None) else "kernel"
         if self.tp > 1:
             if cfg.tp_comm not in ("p2p", "nccl"):
                 raise ValueError(f"tp_comm must be 'p2p' or 'nccl', got {cfg.tp_comm!r}")
