@@ -377,20 +377,21 @@ struct NormArgs {
 
 //
 // ALLRED = true (tile layout, tensor-parallel row-split projections o_proj / down_proj): the kernel's rows are this
-// rank's PARTIAL sums, and the all-reduce over the ranks happens here, tile group by tile group, instead of in a
-// kernel of its own. The block that has computed a tile group's rows
-//   1. rounds them to fp16 and pushes them, 16 bytes at a time, into slot data[rank] of EVERY rank's exchange block
-//      (its own included): plain peer stores over NVLink,
-//   2. after its last round tells every peer "the rows of block b, call number c, are with you" (release store into
-//      the peer's flag word flags[b][rank]) and waits until every peer has said the same (acquire loads of the local
-//      flag words, bounded): one NVLink round trip per block and GEMV, however many rounds the block has,
-//   3. adds the W copies - all in LOCAL memory by now - in rank order with fp32 accumulation, rounds once, and stores
-//      the sums to y. Every rank adds the same numbers in the same order: the sums are bit-identical on all ranks.
-// The block of the same index on each peer does the same for the same rows (the ranks launch the same grid), so
-// nobody waits for anything that depends on this GPU's scheduling. Slot reuse:
-// a rank reaches call c + 1 on a slot only after another exchange has completed in between (the o_proj and down_proj
-// slots alternate, and the logits gather follows the last layer), which every peer can only have joined after it was
-// done reading this slot. N % 8 == 0. A wait that runs out sets the block's error word and leaves y's rows alone.
+// rank's PARTIAL sums, and they leave the kernel over NVLink instead of through y. The block that has computed a tile
+// group's rows rounds them to fp16 and stores them as 32-bit words (tag << 16 | row), tag = the slot's call number,
+// into words[rank][row] of EVERY rank's exchange region (its own included): plain 16-byte peer stores. A word that
+// carries the call's tag is its own arrival flag - no flag round, no fence. Then either
+//   * tagged = 1 (b200_gemv_w4a16_tiled_push): the kernel is done; tp_pushed_add_rmsnorm_kernel on every rank polls
+//     its own region, sums and goes on with residual add + RMSNorm; or
+//   * tagged = 0 (b200_gemv_w4a16_tiled_allreduce): after its last round the block collects the rows of its own
+//     tile groups from its OWN region - the peers' blocks of the same index push exactly those (the ranks launch the
+//     same grid) -, polling each word until it carries the tag (bounded), adds the W copies in rank order with fp32
+//     accumulation, rounds once and stores the sums to y: bit-identical on all ranks. The last block of the grid
+//     moves the slot's call counter on.
+// Slot reuse: a rank reaches call c + 1 on a slot only after another exchange has completed in between (the o_proj
+// and down_proj slots alternate, and the logits gather follows the last layer), which every peer can only have joined
+// after it was done reading this slot. N % 8 == 0. A wait that runs out sets the block's error word and leaves y's
+// rows alone.
 template <bool TILED, bool SWIGLU, bool NORM, bool ALLRED>
 __global__ void __launch_bounds__(kMmaGemvThreads, 2)
 gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ, const uint2* __restrict__ X,
@@ -531,10 +532,10 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
   const uint4* xbase = g == 0 ? xin + 4 * t : zeros;
   const int xstride = g == 0 ? 16 : 0;
 
-  // ALLRED, tagged form: the tag of this call (the slot's call counter was last written by the kernel that consumed
-  // the previous call's rows, which this stream has waited for)
+  // ALLRED: the tag of this call (the slot's call counter was last written by the kernel that closed the previous
+  // call on this slot, which this stream has waited for)
   uint32_t push_tag = 0u;
-  if (ALLRED && ar.tagged)
+  if (ALLRED)
     push_tag = comm_tag(*reinterpret_cast<const volatile uint32_t*>(ar.P.p[ar.rank] + ar.off) + 1u);
   for (int r = 0; r < rounds; ++r, tile += tile_step) {
     float ya = 0.f, yb = 0.f;
@@ -623,7 +624,7 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
       const int gidx = r * gridDim.x + blockIdx.x, row0 = 16 * gidx * tiles_per_round;
       const int nrows = max(0, min(N - row0, 16 * tiles_per_round)), nchunk = nrows >> 3;
       __syncthreads();   // rowbuf complete
-      if (ar.tagged) {
+      {
         // tagged words: 8 rows = 32 bytes = two 16-byte stores per peer; a word with this call's tag is its own flag
         const size_t data_off = ar.off + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + ((size_t)ar.rank * N + row0) * 4;
         for (int i = tid; i < 2 * nchunk * ar.W; i += kMmaGemvThreads) {
@@ -633,64 +634,50 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
                                       push_tag | (h4.y >> 16));
           st_peer16(ar.P.p[p] + data_off + 16 * (size_t)c, wv);
         }
-      } else {
-        const size_t data_off = ar.off + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + ((size_t)ar.rank * N + row0) * 2;
-        for (int i = tid; i < nchunk * ar.W; i += kMmaGemvThreads) {
-          const int p = i / nchunk, c = i - p * nchunk;
-          st_peer16(ar.P.p[p] + data_off + 16 * (size_t)c, reinterpret_cast<const uint4*>(rowbuf)[c]);
-        }
       }
       __syncthreads();   // rowbuf and part are free for the next round
     }
   }
-  if (ALLRED && ar.tagged) return;   // the sum happens where the rows are consumed (tp_pushed_add_rmsnorm_kernel)
+  if (ALLRED && ar.tagged) return;   // push only: the sum happens where the rows are consumed (tp_pushed_add_rmsnorm_kernel)
   if (ALLRED) {
-    // One flag round per block, after all its pushes: block b of every rank handles the same tile groups (same grid,
-    // same rounds on all ranks), so "my rows of block b, call c, are with you" covers them all, and the wait - one
-    // NVLink round trip - is paid once per GEMV instead of once per round.
-    __shared__ uint32_t call_s;
+    // The sum inside the GEMV: block b of every rank handles the same tile groups (same grid, same rounds on all
+    // ranks), so the rows this block has pushed are the rows it now collects - from its OWN region, where the peers'
+    // copies are arriving. A word that carries the call's tag has arrived; no flag, no fence. Round after round, the
+    // early rounds' rows are there long before the poll gets to them: one NVLink flight is exposed per GEMV.
     __shared__ int failed_s;
     uint8_t* mine = ar.P.p[ar.rank] + ar.off;
-    if (tid == 0) {
-      call_s = *reinterpret_cast<volatile uint32_t*>(mine) + 1u;   // the call counter moves when the whole grid is done
-      failed_s = 0;
-    }
-    __syncthreads();   // every push of this block is issued before any of its flags
-    const uint32_t call = call_s;
-    if (tid < ar.W && tid != ar.rank) {
-      const size_t flag_off = ar.off + kGemvSlotCtrlBytes + ((size_t)blockIdx.x * kCommMaxRanks) * 4;
-      // release at system scope: orders the block's pushes (made visible to this thread by the barrier) before the flag
-      st_release_sys(reinterpret_cast<uint32_t*>(ar.P.p[tid] + flag_off) + ar.rank, call);
-      const uint32_t* here = reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + flag_off) + tid;
-      const uint32_t set_limit = *reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + kCommLimitOff);
-      const int limit = set_limit ? (int)set_limit : kCommSpinLimit;
-      int spins = 0;
-      while ((int32_t)(ld_acquire_sys(here) - call) < 0) {
-        if (++spins > limit) {
+    if (tid == 0) failed_s = 0;
+    __syncthreads();
+    const uint32_t set_limit = *reinterpret_cast<const uint32_t*>(ar.P.p[ar.rank] + kCommLimitOff);
+    const int limit = set_limit ? (int)set_limit : kCommSpinLimit;
+    for (int r = 0; r < rounds; ++r) {
+      const int gidx = r * gridDim.x + blockIdx.x, row0 = 16 * gidx * tiles_per_round;
+      const int nrows = max(0, min(N - row0, 16 * tiles_per_round)), nchunk = nrows >> 3;
+      const uint8_t* base = mine + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + (size_t)row0 * 4;
+      for (int c = tid; c < nchunk; c += kMmaGemvThreads) {
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+        bool bad = false;
+        for (int q = 0; q < ar.W && !bad; ++q) {   // rank order, fp32, one rounding: the same bits on every rank
+          const uint8_t* src = base + ((size_t)q * N + 8 * (size_t)c) * 4;
+          uint4 v0 = ld_peer16(src), v1 = ld_peer16(src + 16);
+          int spins = 0;
+          while (((((v0.x ^ push_tag) | (v0.y ^ push_tag) | (v0.z ^ push_tag) | (v0.w ^ push_tag) | (v1.x ^ push_tag) |
+                    (v1.y ^ push_tag) | (v1.z ^ push_tag) | (v1.w ^ push_tag)) >> 16) != 0)) {
+            if (++spins > limit) { bad = true; break; }
+            if (spins > 256) __nanosleep(200);
+            v0 = ld_peer16(src);
+            v1 = ld_peer16(src + 16);
+          }
+          const uint32_t wd[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] += __half2float(__ushort_as_half((unsigned short)(wd[k] & 0xFFFFu)));
+        }
+        if (bad) {   // a peer's rows never came: say so and leave y's rows alone
           failed_s = 1;
           atomicExch(reinterpret_cast<uint32_t*>(ar.P.p[ar.rank] + kCommErrorOff), COMM_ERR_PEER_WAIT);
-          break;
-        }
-        if (spins > 256) __nanosleep(200);
-      }
-    }
-    __syncthreads();
-    if (!failed_s) {
-      // add the W copies - all in LOCAL memory by now - in rank order, fp32, one rounding
-      for (int r = 0; r < rounds; ++r) {
-        const int gidx = r * gridDim.x + blockIdx.x, row0 = 16 * gidx * tiles_per_round;
-        const int nrows = max(0, min(N - row0, 16 * tiles_per_round)), nchunk = nrows >> 3;
-        const uint8_t* base = mine + kGemvSlotCtrlBytes + kGemvSlotFlagBytes + (size_t)row0 * 2;
-        for (int c = tid; c < nchunk; c += kMmaGemvThreads) {
-          float acc[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-          for (int q = 0; q < ar.W; ++q) {
-            float f[8];
-            unpack8(ld_peer16(base + (size_t)q * N * 2 + 16 * (size_t)c), f);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] += f[k];
-          }
+        } else {
           uint4 o;
           o.x = as_u32(__floats2half2_rn(acc[0], acc[1]));
           o.y = as_u32(__floats2half2_rn(acc[2], acc[3]));
@@ -699,6 +686,7 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
           reinterpret_cast<uint4*>(y + row0)[c] = o;
         }
       }
+      if (failed_s) break;   // do not spend a whole bounded wait on every further row
     }
     // the last block to finish closes the call: the slot's call counter moves on, the ticket goes back to zero
     uint32_t* ctrl = reinterpret_cast<uint32_t*>(mine);

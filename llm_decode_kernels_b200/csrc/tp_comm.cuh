@@ -44,12 +44,11 @@ DEVI uint4 ld_peer16(const void* p) {
 // A "GEMV slot" of the exchange block, at a caller-chosen offset (multiple of 256 bytes):
 //   [0, 256)                       control: uint32 calls (exchanges completed on this slot), uint32 done (blocks of
 //                                  the running call that have finished)
-//   [256, 256 + 64 KB)             uint32 flags[kCommMaxGroups][16]: flags[b][r] = latest call for which the rows of
-//                                  rank r's block b (all its tile groups) have arrived here
-//   [256 + 64 KB, ... + 16 N 2)    fp16 data[r][N] for r < W: rank r's partial rows, pushed here by rank r
-// Tagged form of the same slot (GEMV that only pushes, sum in tp_pushed_add_rmsnorm_kernel): the data area holds
-// uint32 words[r][N] = (tag << 16 | fp16 row), tag = low 16 bits of the call number, never 0; no flags are used - a
-// word that carries the call's tag IS the arrival of its row, so the exchange costs one NVLink flight and no fence.
+//   [256, 256 + 64 KB)             reserved (flag rows of an earlier form of the exchange)
+//   [256 + 64 KB, ... + 16 N 4)    uint32 words[r][N] for r < W: rank r's partial rows as (tag << 16 | fp16), pushed
+//                                  here by rank r; tag = low 16 bits of the call number + 1, never 0. A word that
+//                                  carries the call's tag IS the arrival of its row: no flags, no fence, one NVLink
+//                                  flight.
 constexpr int kCommMaxGroups = 1024;
 constexpr size_t kGemvSlotCtrlBytes = 256;
 constexpr size_t kGemvSlotFlagBytes = (size_t)kCommMaxGroups * kCommMaxRanks * 4;
