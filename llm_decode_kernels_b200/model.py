@@ -70,12 +70,12 @@ class DecodeConfig:
     tp_allreduce: str = "auto"   # tp_comm="p2p": how the partial rows of o_proj / down_proj are summed over the ranks.
                                  # "kernel": the GEMV writes its rows locally; one exchange kernel does a flag round,
                                  # loads the peers' rows, sums, residual add + RMSNorm (b200_tp_allreduce_add_rmsnorm).
-                                 # "gemv": inside the row-split GEMV itself (b200_gemv_w4a16_tiled_allreduce), the
-                                 # norm inside the next GEMV - two launches less per layer. "push": the GEMV pushes
-                                 # tagged words into every rank's region and returns; the consumer kernel polls its
-                                 # own memory, sums, add + RMSNorm (b200_gemv_w4a16_tiled_push +
-                                 # b200_tp_pushed_add_rmsnorm) - no flag round, no fence. "auto": what measured
-                                 # fastest for the number of ranks
+                                 # "push": the GEMV pushes tagged words into every rank's region and returns; the
+                                 # consumer kernel polls its own memory, sums, add + RMSNorm
+                                 # (b200_gemv_w4a16_tiled_push + b200_tp_pushed_add_rmsnorm) - no flag round, no
+                                 # fence. "gemv": the same push, and the GEMV's blocks collect and sum their own
+                                 # rows (b200_gemv_w4a16_tiled_allreduce), the norm inside the next GEMV - two
+                                 # launches less per layer. "auto": what measured fastest for the number of ranks
     ablate: tuple = ()           # fusions switched off for ablation runs, any of "dequant" (dequantize the matrix to
                                  # an fp16 buffer, then an fp16 matrix-vector product), "norm", "swiglu" (the two
                                  # that fused=False switches off together) and "rope" (rotation and cache append as
@@ -249,11 +249,12 @@ class Model:
         if "rope" in self.off:
             self.kv_heads = torch.arange(self.n_kv, device=dev)
         self.comm = None
-        # measured on the 70B shape (tok/s at 2 / 4 / 8 ranks): push 132.1 / 151.4 / 181.0, kernel 120.6 / 133.9 /
-        # 140.6, gemv 114.5 / 127.8 / 150.3. The push form needs the tile-layout copies (its GEMV is the tiled one).
+        # measured on the 70B shape (tok/s at 2 / 4 / 8 ranks): push 133 / 151 / 183, gemv 131 / - / 189, kernel 121 /
+        # 134 / 141. Push and gemv need the tile-layout copies (their GEMV is the tiled one).
         self.tp_allreduce = cfg.tp_allreduce
         if self.tp_allreduce == "auto":
-            self.tp_allreduce = "push" if (cfg.tile_weights and cfg.gemv_stage is None) else "kernel"
+            tiled = cfg.tile_weights and cfg.gemv_stage is None
+            self.tp_allreduce = ("gemv" if self.tp >= 8 and cfg.fuse_norm_gemv else "push") if tiled else "kernel"
         if self.tp > 1:
             if cfg.tp_comm not in ("p2p", "nccl"):
                 raise ValueError(f"tp_comm must be 'p2p' or 'nccl', got {cfg.tp_comm!r}")
