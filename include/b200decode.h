@@ -287,12 +287,14 @@ int b200_tp_allreduce_add_rmsnorm(const void* const* peers, int rank, int W, siz
 /* The row-split projection AND its all-reduce in one kernel (o_proj, down_proj of a tensor-parallel layer): y[N] = sum
  * over the W ranks of (that rank's W_r x_r), every rank calling with its own column shard in tile layout
  * (b200_gemv_w4a16_tile_repack) and its own x. Each thread block pushes the rows it has computed into every rank's
- * exchange block over NVLink and, once after its last row, signals, waits (bounded) for the peers' copies of the same
- * rows and adds the W copies in rank order (fp32, one rounding): bit-identical sums on all ranks, no exchange kernel,
- * no NCCL call. All ranks must call with the same N and K (they launch the same grid). y is local
- * memory (fp16 [N], 16-byte aligned); feed it as `delta` to b200_gemv_w4a16_tiled_norm. slot_off: offset, a multiple
- * of 256, of a region of b200_tp_gemv_slot_bytes(N, W) bytes inside every rank's block, used by this call sequence
- * only; successive calls must alternate between at least two such regions (o_proj / down_proj do). N % 8 == 0.
+ * exchange region over NVLink as 32-bit words (tag << 16 | fp16 row), tag = the region's call number; after its last
+ * row it collects the same rows from its OWN region, where the peers' copies arrive, polling each word until it
+ * carries the tag (bounded; on a timeout b200_comm_error = 1 and those rows of y are left alone), and adds the W
+ * copies in rank order (fp32, one rounding): bit-identical sums on all ranks, no flag round, no exchange kernel, no
+ * NCCL call. All ranks must call with the same N and K (they launch the same grid). y is local memory (fp16 [N],
+ * 16-byte aligned); feed it as `delta` to b200_gemv_w4a16_tiled_norm. slot_off: offset, a multiple of 256, of a
+ * region of b200_tp_gemv_slot_bytes(N, W) bytes inside every rank's block, used by this call sequence only;
+ * successive calls must alternate between at least two such regions (o_proj / down_proj do). N % 8 == 0.
  * B200_ERR_LIMIT if the launch would have more than 1024 thread blocks. W = 1 is allowed (no peer, y = W x). */
 size_t b200_tp_gemv_slot_bytes(int N, int W);
 int b200_gemv_w4a16_tiled_allreduce(const void* Wt, const void* x, void* y, int N, int K, const void* const* peers,
