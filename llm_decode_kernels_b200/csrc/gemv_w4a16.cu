@@ -399,11 +399,10 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
                       const AllReduceArgs ar) {
   extern __shared__ __align__(16) uint8_t mma_smem[];
   const int nunit = K >> 7;                                                // 128-weight units per row
-  uint4* xin = reinterpret_cast<uint4*>(mma_smem);                         // [K/8] staged x, 16 bytes = one word's 8
-  uint4* zeros = xin + (K >> 3);                                           // 64 zero bytes: B of the lanes with g != 0
-  float* part = reinterpret_cast<float*>(zeros + 4);                       // [kMmaGemvWarps][16]
-  float* xsg = part + kMmaGemvWarps * 16;                                  // [nunit] sum of x over each unit
-  __shared__ float red[kMmaGemvWarps], red2[kMmaGemvWarps];
+  uint4* xin = reinterpret_cast<uint4*>(mma_smem);                         // [K/8]: per unit 256 bytes of byte digits
+  float* part = reinterpret_cast<float*>(xin + (K >> 3) + 4);              // [kMmaGemvWarps][16]
+  float* xsg = part + kMmaGemvWarps * 16;                                  // [nunit][2]: 2^-s sum X and 2^-s per unit
+  __shared__ float red2[kMmaGemvWarps];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   pdl_launch_dependents();
 
@@ -467,9 +466,39 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
   }
   pdl_wait();
 
-  // ---- stage x: (residual add + RMSNorm ->) max|x| -> power-of-two scale -> (x0 x1) 2^s, (x2 x3) 2^(s-4), ... and
-  // the unit sums
-  float mx = 0.f;
+  // ---- stage x: (residual add + RMSNorm ->) per 128-element unit: 15-bit fixed point X = round(x 2^s), s from the
+  // unit's max|x|, split into two signed byte digits laid out as the B fragments of the integer MMAs, and the unit's
+  // 2^-s sum X and 2^-s. One warp per unit, lane = granule of 4 activations; no block-wide maximum, no barrier before
+  // the units can be written.
+  // xin words [unit][digit n = 0 (hi), 1 (lo)][t = 0..3][MMA m = 0..3][register r = 0..1]: lane (n, t) of the MMA loop
+  // loads its eight registers with two 16-byte reads. Register r of MMA m pairs with word 2 (m / 2) + r of the lane's
+  // four weight words, low nibbles (m even: elements e0 e4 e1 e5 of the word, in byte order) or high nibbles (m odd:
+  // e2 e6 e3 e7). Granule l = 4 elements of word (l % 8) / 2: e0..e3 on even lanes, e4..e7 on odd ones.
+  auto put_unit = [&](int u, uint2 v) {
+    const uint32_t m2 = __vmaxu2(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu);   // max |x| from the fp16 bit patterns
+    const uint32_t mxb = __reduce_max_sync(0xffffffffu, max(m2 & 0xFFFFu, m2 >> 16));
+    const bool finite = mxb < 0x7C00u;
+    const int sh = 28 - max((int)(mxb >> 10), 1);             // 2^sh max|x| in [2^13, 2^14)
+    const float scl = __int_as_float((sh + 127) << 23);
+    constexpr float kMagic = 12582912.f + 128.f;              // 1.5 2^23 + 128: rounds to an integer, offset for the lo digit
+    const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
+    const uint32_t w0 = __float_as_uint(fmaf(a.x, scl, kMagic)), w1 = __float_as_uint(fmaf(a.y, scl, kMagic));
+    const uint32_t w2 = __float_as_uint(fmaf(b.x, scl, kMagic)), w3 = __float_as_uint(fmaf(b.y, scl, kMagic));
+    const uint32_t kM = __float_as_uint(kMagic);
+    const int xsum_i = __reduce_add_sync(0xffffffffu, (int)(w0 - kM) + (int)(w1 - kM) + (int)(w2 - kM) + (int)(w3 - kM));
+    const float resc = finite ? __int_as_float((127 - sh) << 23) : __int_as_float(0x7fc00000);   // 2^-sh, or NaN
+    if (lane == 0) {
+      xsg[2 * u] = (float)xsum_i * resc;
+      xsg[2 * u + 1] = resc;
+    }
+    const uint32_t lo = __byte_perm(__byte_perm(w0, w1, 0x0040), __byte_perm(w2, w3, 0x0040), 0x5410) ^ 0x80808080u;
+    const uint32_t hi = __byte_perm(__byte_perm(w0, w1, 0x0051), __byte_perm(w2, w3, 0x0051), 0x5410);
+    const int tt = lane >> 3, wd = (lane & 7) >> 1, odd = lane & 1;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(xin) + (size_t)u * 64 + tt * 8 + ((wd >> 1) * 2 + odd) * 2 + (wd & 1);
+    const uint32_t hi_o = __shfl_xor_sync(0xffffffffu, hi, 1), lo_o = __shfl_xor_sync(0xffffffffu, lo, 1);
+    dst[0] = odd ? __byte_perm(hi, hi_o, 0x3726) : __byte_perm(hi, hi_o, 0x5140);
+    dst[32] = odd ? __byte_perm(lo, lo_o, 0x3726) : __byte_perm(lo, lo_o, 0x5140);
+  };
   if (NORM) {
     float ss = 0.f;
     for (int i = tid; i < (K >> 2); i += kMmaGemvThreads) {
@@ -486,51 +515,24 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
     }
     ss = warp_sum(ss);
     if (lane == 0) red2[warp] = ss;
-    __syncthreads();
+    __syncthreads();   // the residual values of every unit are in xin; the sum of squares is complete
     float tot = 0.f;
 #pragma unroll
     for (int k = 0; k < kMmaGemvWarps; ++k) tot += red2[k];
     const float rinv = rsqrtf(tot / (float)K + na.eps);
-    for (int i = tid; i < (K >> 2); i += kMmaGemvThreads) {   // this thread's own granules again
-      const uint2 r = reinterpret_cast<uint2*>(xin)[i], w = __ldg(na.nw + i);
+    for (int u = warp; u < nunit; u += kMmaGemvWarps) {   // the unit's fp16 residual -> normalised x -> digits, in place
+      const uint2 r = reinterpret_cast<uint2*>(xin)[32 * u + lane], w = __ldg(na.nw + 32 * u + lane);
       const float2 a = __half22float2(as_h2(r.x)), b = __half22float2(as_h2(r.y));
       uint2 v;
       v.x = as_u32(__hmul2(as_h2(w.x), __floats2half2_rn(a.x * rinv, a.y * rinv)));
       v.y = as_u32(__hmul2(as_h2(w.y), __floats2half2_rn(b.x * rinv, b.y * rinv)));
-      reinterpret_cast<uint2*>(xin)[i] = v;
-      const float2 c = __half22float2(__habs2(as_h2(v.x))), d = __half22float2(__habs2(as_h2(v.y)));
-      mx = fmaxf(mx, fmaxf(fmaxf(c.x, c.y), fmaxf(d.x, d.y)));
+      __syncwarp();   // every lane has read its granule before the unit's 256 bytes are overwritten
+      put_unit(u, v);
     }
   } else {
-    for (int i = tid; i < (K >> 2); i += kMmaGemvThreads) {
-      const uint2 v = __ldg(X + i);
-      reinterpret_cast<uint2*>(xin)[i] = v;
-      const float2 a = __half22float2(__habs2(as_h2(v.x))), b = __half22float2(__habs2(as_h2(v.y)));
-      mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)));
-    }
-  }
-  mx = warp_max(mx);
-  if (lane == 0) red[warp] = mx;
-  if (tid < 4) zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
-  __syncthreads();
-  float xmax = 0.f;
-#pragma unroll
-  for (int k = 0; k < kMmaGemvWarps; ++k) xmax = fmaxf(xmax, red[k]);
-  const XScale sc = scale_for(xmax);
-  for (int u = warp; u < nunit; u += kMmaGemvWarps) {   // one warp per unit: lane = granule of 4 activations
-    uint2 v = reinterpret_cast<uint2*>(xin)[32 * u + lane];
-    const float2 a = __half22float2(as_h2(v.x)), b = __half22float2(as_h2(v.y));
-    const float sm = warp_sum((a.x + a.y) + (b.x + b.y));
-    if (lane == 0) xsg[u] = sm;
-    v.x = as_u32(__hmul2(as_h2(v.x), sc.lo));
-    v.y = as_u32(__hmul2(as_h2(v.y), sc.hi));
-    reinterpret_cast<uint2*>(xin)[32 * u + lane] = v;
+    for (int u = warp; u < nunit; u += kMmaGemvWarps) put_unit(u, __ldg(X + 32 * u + lane));
   }
   __syncthreads();
-
-  // B operand: lanes with g == 0 walk x (16 pieces of 16 bytes per unit), the others keep reading the zero block
-  const uint4* xbase = g == 0 ? xin + 4 * t : zeros;
-  const int xstride = g == 0 ? 16 : 0;
 
   // ALLRED: the tag of this call (the slot's call counter was last written by the kernel that closed the previous
   // call on this slot, which this stream has waited for)
@@ -552,27 +554,28 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
         for (int i = 0; i < kMmaBatch; ++i) {
           const int u = u0 + i;
           if (u < ue) {   // warp-uniform
-            const uint4* xb = xbase + u * xstride;
-            float c[4];
-            const uint32_t wa[4] = {cur.wa[i].x, cur.wa[i].y, cur.wa[i].z, cur.wa[i].w};
-            const uint32_t wb[4] = {cur.wb[i].x, cur.wb[i].y, cur.wb[i].z, cur.wb[i].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 xv = xb[j];
-              const uint32_t a8 = wa[j] >> 8, b8 = wb[j] >> 8;
-              if (j == 0)
-                mma16816_zero(c, wa[j] & 0x000F000Fu, wb[j] & 0x000F000Fu, wa[j] & 0x00F000F0u, wb[j] & 0x00F000F0u,
-                              xv.x, xv.y);
-              else
-                mma16816_acc(c, wa[j] & 0x000F000Fu, wb[j] & 0x000F000Fu, wa[j] & 0x00F000F0u, wb[j] & 0x00F000F0u,
-                             xv.x, xv.y);
-              mma16816_acc(c, a8 & 0x000F000Fu, b8 & 0x000F000Fu, a8 & 0x00F000F0u, b8 & 0x00F000F0u, xv.z, xv.w);
+            // B: lanes (0, t) carry the hi digits of the 32 activations that match the lane's 32 weights, lanes (1, t)
+            // the lo digits, the other lanes zeros; four integer MMAs in two independent chains
+            uint4 x0 = make_uint4(0u, 0u, 0u, 0u), x1 = x0;
+            if (g < 2) {
+              const uint4* xp = xin + (size_t)u * 16 + (g * 4 + t) * 2;
+              x0 = xp[0];
+              x1 = xp[1];
             }
-            // column 0 of the product sits in c[0] (row g) and c[2] (row g + 8) of the lanes with t == 0
+            const uint4 wa = cur.wa[i], wb = cur.wb[i];
+            constexpr uint32_t kNib = 0x0F0F0F0Fu;
+            int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+            mma16832_u8s8(c0, wa.x & kNib, wb.x & kNib, wa.y & kNib, wb.y & kNib, x0.x, x0.y);
+            mma16832_u8s8(c1, (wa.x >> 4) & kNib, (wb.x >> 4) & kNib, (wa.y >> 4) & kNib, (wb.y >> 4) & kNib, x0.z, x0.w);
+            mma16832_u8s8(c0, wa.z & kNib, wb.z & kNib, wa.w & kNib, wb.w & kNib, x1.x, x1.y);
+            mma16832_u8s8(c1, (wa.z >> 4) & kNib, (wb.z >> 4) & kNib, (wa.w >> 4) & kNib, (wb.w >> 4) & kNib, x1.z, x1.w);
+            // lanes t == 0: C columns 0 (hi digits) and 1 (lo digits) of rows g (c[0], c[1]) and g + 8 (c[2], c[3])
             const float2 sa = __half22float2(cur.sa[i]), sb = __half22float2(cur.sb[i]);
-            const float xs = xsg[u];
-            ya = fmaf(sa.x, fmaf(c[0], sc.resc, -sa.y * xs), ya);
-            yb = fmaf(sb.x, fmaf(c[2], sc.resc, -sb.y * xs), yb);
+            const float xs = xsg[2 * u], resc = xsg[2 * u + 1];
+            const float va = (float)(((c0[0] + c1[0]) << 8) + (c0[1] + c1[1]));
+            const float vb = (float)(((c0[2] + c1[2]) << 8) + (c0[3] + c1[3]));
+            ya = fmaf(sa.x, fmaf(va, resc, -sa.y * xs), ya);
+            yb = fmaf(sb.x, fmaf(vb, resc, -sb.y * xs), yb);
           }
         }
         cur = nxt;
@@ -748,7 +751,7 @@ static cudaError_t launch_mma(int mode, const void* Wp, const void* SZ, const vo
   const int groups = (ntiles + tpr - 1) / tpr;
   const int blocks = groups < want_blocks ? groups : want_blocks;
   const int rounds = (groups + blocks - 1) / blocks;
-  const size_t smem = (size_t)K * 2 + (size_t)nunit * 4 + kMmaGemvWarps * 16 * 4 + 64;
+  const size_t smem = (size_t)K * 2 + (size_t)nunit * 8 + kMmaGemvWarps * 16 * 4 + 64;
   {
     static size_t allowed[kMaxDevices] = {};
     int dev = 0;
