@@ -39,8 +39,9 @@ const char* b200_last_cuda_error(void);
  * K % 32 == 0, group = 2^log2G >= 32 and divides K.
  * stage 0 = plain one-thread-per-weight kernel. stage >= 1 with R in {1,2,4,8} and warps in 1..8 runs
  * that rows-per-warp / warps-per-block configuration on the CUDA cores; R = 16 runs the segmented CUDA-core kernel;
- * any other R (use 0) lets the library choose: the tensor-core kernel (masked nibbles fed to mma.m16n8k16 as fp16
- * subnormals, fp32 accumulation) when K % 128 == 0 and the group size is a multiple of 128, else the segmented one.
+ * any other R (use 0) lets the library choose: the tensor-core kernel (nibbles as unsigned bytes and x as two signed
+ * byte digits per 128-element unit into the integer mma.m16n8k32, exact accumulation, one scale per unit) when
+ * K % 128 == 0 and the group size is a multiple of 128, else the segmented one.
  * pf is accepted for signature compatibility and ignored. */
 int b200_gemv_w4a16(int stage, int R, int warps, int pf, const void* Wp, const void* SZ, const void* x, void* y,
                     int N, int K, int log2G, void* stream);

@@ -1,7 +1,7 @@
-// Device helpers shared by every kernel of the decode step. Target: sm_100a (B200), fp16 storage, fp32
-// accumulation. The GEMV and attention kernels feed warp-level mma.sync.m16n8k16 with operands taken straight from
-// the packed format (see "tensor-core operands" below); nothing here uses the 64-row-and-up tcgen05 MMAs, which a
-// batch-1 step cannot fill.
+// Device helpers shared by the kernels of the library. Target: sm_100a (B200), fp16 storage, fp32 (or exact integer)
+// accumulation. The GEMV and the persistent step feed the warp-level integer mma.sync.m16n8k32 with operands taken
+// straight from the packed format (see "tensor-core operands" below), attention the fp16 m16n8k16; the 64-row-and-up
+// tcgen05 MMAs, which a batch-1 step cannot fill, are used by the prompt's GEMM only (prefill_gemm.cu).
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -201,25 +201,9 @@ DEVI void chunk_two_rows(uint4 wa, uint4 wb, half2 sza, half2 szb, const XChunk&
 }
 
 // ---- tensor-core operands ------------------------------------------------------------------------------------------
-// mma.sync.m16n8k16, fp16 inputs, fp32 accumulators. Lane (g = lane / 4, t = lane % 4) holds
-//   A: a0 = A[g][2t, 2t+1], a1 = A[g+8][2t, 2t+1], a2 = A[g][2t+8, 2t+9], a3 = A[g+8][2t+8, 2t+9]
-//   B: b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g]        C: c0, c1 = C[g][2t, 2t+1], c2, c3 = C[g+8][2t, 2t+1]
-DEVI void mma16816_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// D = A * B (no accumulator input: the first MMA of a unit starts from zero without clearing registers)
-DEVI void mma16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-               : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-}
-
 // mma.sync.m16n8k32, unsigned bytes x signed bytes, int32 accumulators (C += A B). Lane (g, t) holds
 //   A: a0 = A[g][4t .. 4t+3], a1 = A[g+8][4t .. 4t+3], a2 = A[g][16+4t ..], a3 = A[g+8][16+4t ..]   (one byte per k)
-//   B: b0 = B[4t .. 4t+3][g], b1 = B[16+4t ..][g]                       C as for m16n8k16.
+//   B: b0 = B[4t .. 4t+3][g], b1 = B[16+4t ..][g]                       C: c0, c1 = C[g][2t, 2t+1], c2, c3 = C[g+8][2t, 2t+1].
 // Native on this part: it issues every 8 cycles per SM sub-core like the fp16 m16n8k16, for twice the k. (The e4m3
 // form of the same shape is emulated: measured with live operands it is slower than the fp16 one.)
 DEVI void mma16832_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {

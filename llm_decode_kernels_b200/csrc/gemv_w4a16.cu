@@ -324,19 +324,24 @@ static cudaError_t launch_seg(const void* Wp, const void* SZ, const void* x, voi
 
 // ---- tensor-core GEMV: the library's default where the shape allows -------------------------------------------------------
 // The CUDA-core kernels above spend ~3.6 issued instructions per weight (mask, shift, half2 FMA, conversions, shuffles)
-// and are bound by instruction issue at 45-60 % of the HBM bandwidth of this part. The quantization format happens to
-// be a tensor-core operand already: (word & 0x000F000F) is the fp16 pair (q[8j], q[8j+1]) * 2^-24 and
-// (word & 0x00F000F0) the pair (q[8j+2], q[8j+3]) * 2^-20 - two consecutive-k elements of one row, which is what one
-// register of the A fragment of mma.m16n8k16 holds. So a 16-row x 128-weight block of W is 8 MMAs whose A registers
-// are masked words, with x (scaled by 2^s / 2^(s-4) as in the kernels above) in column 0 of B; the accumulators are
-// fp32, and scale and zero point are applied once per group:
-//     y += scale * (2^(24-s) * acc - zero * sum_group(x)).
-// Seven of the eight B columns are zero: the MMA is not used for its FLOPs but because it replaces 128 half2 FMAs,
-// their conversions and the cross-lane reduction by 8 instructions (about 1 issued instruction per weight instead of
-// 3.6), and because its fp32 accumulation removes the fp16 rounding of the half2 chains.
-//   lane (g = lane / 4, t = lane % 4) loads 16 bytes (32 weights: words 4t .. 4t+3 of the group) of row g and of row
-//   g + 8; word j feeds k-steps 2j (low byte's nibbles) and 2j + 1 (after a shift by 8). B's k-slots are dealt to match:
-//   lane (0, t) holds the 32 staged activations of the same 32 columns, other lanes hold zeros.
+// and are bound by instruction issue at 45-60 % of the HBM bandwidth of this part. This kernel does the inner product
+// on the INTEGER tensor cores. (word & 0x0F0F0F0F) and ((word >> 4) & 0x0F0F0F0F) are registers of four unsigned-byte
+// weights each - three integer instructions for 8 weights - so a 16-row x 128-weight block of W is four
+// mma.m16n8k32 (u8 x s8 -> s32) whose A registers are masked words. The activations go in as 15-bit fixed point:
+// staging scales a 128-element unit of x by 2^s (s from the unit's max|x|), rounds to an integer X, |X| < 2^14, and
+// splits it into two signed byte digits, X = 256 hi + lo, which ride in columns 0 and 1 of the B operand (a batch-1
+// GEMV leaves the B columns idle anyway). The accumulation is exact, and scale and zero point are applied once per
+// unit:
+//     y += scale * (2^-s * (256 C[.][0] + C[.][1]) - zero * sum_unit(x)).
+// Rounding x to 2^-14 of its unit's maximum is finer than the fp16 rounding x already carries, except for elements
+// far below the maximum, whose absolute error it bounds by 2^-15 of the maximum. A NaN or infinity in a unit of x
+// turns that unit's factor 2^-s into NaN, so every row's output is NaN as in the reference's arithmetic.
+// An earlier form fed the masked nibbles to mma.m16n8k16 as fp16 subnormals (q * 2^-24, q * 2^-20): five mask/shift
+// instructions per 8 weights on the half-rate integer pipe, which bound it at 0.72 of the copy bandwidth on the 70B
+// gate|up matrix; this form reaches 0.82 there and waits for memory instead.
+//   lane (g = lane / 4, t = lane % 4) loads 16 bytes (32 weights: words 4t .. 4t+3 of the unit) of row g and of row
+//   g + 8; lanes (0, t) carry the hi digits of the matching 32 activations as the B operand, lanes (1, t) the lo
+//   digits, the other lanes zeros.
 // A block of 8 warps stages x once and walks row tiles of 16 rows; `ksplit` warps share a tile by splitting K (small
 // matrices need the parallelism) and meet in shared memory, with ksplit = 1 a warp owns its tile and there is no
 // barrier in the loop. Needs K % 128 == 0 and a group size that is a multiple of 128.
