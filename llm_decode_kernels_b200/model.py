@@ -85,7 +85,8 @@ class DecodeConfig:
                                  # prepared context cap is within PERSISTENT_MAX_CTX
 
 
-PERSISTENT_MAX_CTX = 12288   # beyond this the one-launch-per-operator step, whose attention uses every SM, is faster
+PERSISTENT_MAX_CTX = 10240   # beyond this the one-launch-per-operator step, whose attention uses every SM, is faster
+                             # (measured us per token at 2048 / 8192: persistent 468 / 697, multi-kernel 652 / 755)
 
 
 class Linear:
