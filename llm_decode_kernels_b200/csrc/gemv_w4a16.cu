@@ -627,8 +627,8 @@ gemv_w4a16_mma_kernel(const uint4* __restrict__ Wp, const half2* __restrict__ SZ
       if (!ALLRED) __syncthreads();
     }
     if (ALLRED) {
-      // this round's tile group: tiles [gidx * tpr, (gidx + 1) * tpr), rows from row0 on, `nchunk` pieces of 8 rows:
-      // pushed to every rank now; flags, wait and sum follow once for all rounds of the block
+      // the tile group of pass r: tiles [gidx * tpr, (gidx + 1) * tpr), rows from row0 on, `nchunk` pieces of 8 rows:
+      // pushed to every rank now; the collecting and the sum follow once, after the block's last pass
       const int gidx = r * gridDim.x + blockIdx.x, row0 = 16 * gidx * tiles_per_round;
       const int nrows = max(0, min(N - row0, 16 * tiles_per_round)), nchunk = nrows >> 3;
       __syncthreads();   // rowbuf complete
