@@ -42,6 +42,20 @@ def test_python_signatures_cover_the_header():
         assert len([a for a in m.group(1).split(",") if a.strip() not in ("", "void")]) == len(argtypes), name
 
 
+def test_exchange_sizes_are_host_arithmetic():
+    """Sizes a caller allocates from: the persistent step's exchange area (per layer qkv, J partial attention outputs
+    and their log-sum-exp words, o, act, down; J = min(4, grid / n_q) context slices per query head) and the
+    tensor-parallel GEMV region (control, reserved flag rows, W x N tagged words)."""
+    lib = ext.load_library()
+    L, H, I, n_q, n_kv, D, grid = 22, 2048, 5632, 32, 4, 64, 148           # TinyLlama shape on a B200: J = 4
+    per_layer = (n_q + 2 * n_kv) * D + 4 * n_q * D + n_q * 8 + H + I + H
+    assert lib.b200_decode_step_xchg_bytes(L, H, I, n_q, n_kv, D, grid) == (L * per_layer + grid * 4) * 4
+    per_layer_1 = (64 + 2 * 8) * 128 + 2 * 64 * 128 + 64 * 4 + 8192 + 28672 + 8192      # 64 heads on 148 CTAs: J = 2
+    assert lib.b200_decode_step_xchg_bytes(1, 8192, 28672, 64, 8, 128, grid) == (per_layer_1 + grid * 4) * 4
+    assert lib.b200_decode_step_xchg_bytes(L, H, I, n_q, n_kv, D, 0) == 0
+    assert lib.b200_tp_gemv_slot_bytes(8192, 8) == 256 + 1024 * 16 * 4 + 8 * 8192 * 4
+
+
 def test_bad_arguments_are_refused_on_the_host():
     """Argument checks run before any CUDA call, so they can be exercised without a device."""
     lib = ext.load_library()
